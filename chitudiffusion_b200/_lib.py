@@ -1,0 +1,92 @@
+"""ctypes binding of libchitu_b200.so (the C ABI declared in include/chitu_b200.h).
+
+There is no fallback: if the shared library is missing or a call fails, an
+exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libchitu_b200.so")
+
+OK, E_INVALID, E_UNSUPPORTED, E_CUDA = 0, -1, -2, -3
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
+
+EXPORTS = (
+    "chitu_b200_version",
+    "chitu_b200_caps",
+    "chitu_b200_last_error",
+    "chitu_b200_attn_fwd",
+    "chitu_b200_lse_combine",
+    "chitu_b200_qk_norm_rope",
+    "chitu_b200_strided_copy",
+)
+
+_lib: Optional[ctypes.CDLL] = None
+
+_i64p = ctypes.POINTER(ctypes.c_int64)
+_vp = ctypes.c_void_p
+
+
+class ChituB200Error(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ChituB200Error(
+            f"{LIB_PATH} not found: build it with `python -m chitudiffusion_b200.build` "
+            "(nvcc, sm_100a).  This package has no fallback path."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.chitu_b200_version.restype = ctypes.c_int
+    lib.chitu_b200_caps.restype = ctypes.c_uint
+    lib.chitu_b200_last_error.restype = ctypes.c_char_p
+    lib.chitu_b200_attn_fwd.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd.argtypes = [
+        _vp, _vp, _vp, _vp, _vp,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, _vp,
+    ]
+    lib.chitu_b200_lse_combine.restype = ctypes.c_int
+    lib.chitu_b200_lse_combine.argtypes = [
+        _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int, _vp,
+    ]
+    lib.chitu_b200_qk_norm_rope.restype = ctypes.c_int
+    lib.chitu_b200_qk_norm_rope.argtypes = [
+        _vp, ctypes.c_int, ctypes.c_int64, _vp, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int,
+        _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int64,
+        _vp, ctypes.c_int, _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        ctypes.c_int, _vp,
+    ]
+    lib.chitu_b200_strided_copy.restype = ctypes.c_int
+    lib.chitu_b200_strided_copy.argtypes = [
+        _vp, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _i64p, _vp,
+    ]
+    _lib = lib
+    return lib
+
+
+def i64_array(values: Sequence[int]):
+    return (ctypes.c_int64 * len(values))(*[int(v) for v in values])
+
+
+def check(rc: int, what: str) -> None:
+    """Map a C-ABI return code to the reference's exception conventions."""
+    if rc == OK:
+        return
+    msg = load().chitu_b200_last_error().decode("utf-8", "replace")
+    if rc == E_UNSUPPORTED:
+        raise NotImplementedError(f"{what}: {msg}")
+    if rc == E_INVALID:
+        raise ValueError(f"{what}: {msg}")
+    raise ChituB200Error(f"{what}: {msg}")

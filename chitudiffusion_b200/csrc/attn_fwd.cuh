@@ -1,0 +1,348 @@
+// Dense non-causal attention forward for head_dim 128 on sm_100a.
+//
+// One CTA owns one (batch, head, 256-query-row block): two 128-row query tiles
+// that ping-pong on the tensor core.  Roles (320 threads):
+//   warps 0-3  softmax for query tile 0   (thread = one score row, no shuffles)
+//   warps 4-7  softmax for query tile 1
+//   warp  8    MMA issuer (one thread issues tcgen05.mma, accumulators in TMEM)
+//   warp  9    TMA producer (Q once, then K_j / V_j through a 5-slot ring)
+//
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  The
+// probabilities P are written back as packed 16-bit pairs over the first 64
+// columns of their S buffer and feed the PV MMA straight from tensor memory.
+//
+// Softmax is the online form in base 2 with lazy rescaling: the running maximum
+// used for the exponent only moves when the true maximum has grown by more than
+// 2^8, so O is rescaled rarely.  Because the tensor pipe executes MMAs in issue
+// order and S_{j+1} is committed after PV_j, seeing S_{j+1} implies PV_j is
+// complete and O may be touched.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace chitu {
+
+constexpr int kHeadDim = 128;
+constexpr int kTileM = 128;   // query rows per tile (UMMA M)
+constexpr int kTileN = 128;   // keys per tile (UMMA N of QK^T, K extent of PV)
+constexpr int kQTiles = 2;    // query tiles per CTA
+constexpr int kStages = 5;    // K/V ring slots
+constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32 KiB
+constexpr int kHalfTileBytes = kTileBytes / 2;     // one 64-column swizzle panel
+constexpr int kAttnThreads = 320;
+constexpr int kSmemBarrierBytes = 256;
+constexpr int kAttnSmemBytes = (kQTiles + kStages) * kTileBytes + kSmemBarrierBytes + 1024;  // +1024: manual alignment
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct AttnParams {
+  void* out;        // [B, Sq, H, 128] contiguous, 16-bit
+  float* lse;       // [B, H, Sq] fp32 natural-log, or nullptr
+  int* status;      // device status word, or nullptr
+  int B, H, Sq, Sk;
+  float scale_log2; // softmax_scale * log2(e)
+  int is_fp16;      // 0 = bf16, 1 = fp16
+};
+
+template <bool kFp16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  uint32_t r;
+  if constexpr (kFp16) {
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+template <bool kFp16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t q_smem = smem_base;                          // 2 tiles
+  const uint32_t kv_smem = smem_base + kQTiles * kTileBytes;  // kStages tiles
+  const uint32_t bar_base = kv_smem + kStages * kTileBytes;
+  // barrier map (8 bytes each)
+  const uint32_t bar_q_full = bar_base;                     // [2]
+  const uint32_t bar_kv_full = bar_base + 16;               // [kStages]
+  const uint32_t bar_kv_empty = bar_kv_full + 8 * kStages;  // [kStages]
+  const uint32_t bar_s_full = bar_kv_empty + 8 * kStages;   // [2]
+  const uint32_t bar_p_full = bar_s_full + 16;              // [2]
+  const uint32_t bar_o_final = bar_p_full + 16;             // [2]
+  uint8_t* tail = smem_gen + (kQTiles + kStages) * kTileBytes + (16 + 16 * kStages + 48);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * (kQTiles * kTileM);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int n_kv = (p.Sk + kTileN - 1) / kTileN;
+  const int n_qt = (q0 + kTileM < p.Sq) ? 2 : 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_full + 8, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_kv_full + 8 * s, 1);
+      mbar_init(bar_kv_empty + 8 * s, 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar_s_full + 8 * t, 1);
+      mbar_init(bar_p_full + 8 * t, kTileM);
+      mbar_init(bar_o_final + 8 * t, 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  if (warp == 9 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int t = 0; t < n_qt; ++t) {
+        mbar_arrive_expect_tx(bar_q_full + 8 * t, kTileBytes);
+        tma_load_4d(q_smem + t * kTileBytes, &tm_q, bar_q_full + 8 * t, 0, head, q0 + t * kTileM, batch);
+        tma_load_4d(q_smem + t * kTileBytes + kHalfTileBytes, &tm_q, bar_q_full + 8 * t, 64, head, q0 + t * kTileM,
+                    batch);
+      }
+    }
+    const int n_items = 2 * n_kv;  // K_0, V_0, K_1, V_1, ...
+    for (int i = 0; i < n_items; ++i) {
+      const int slot = i % kStages;
+      const int round = i / kStages;
+      if (round > 0) mbar_wait(bar_kv_empty + 8 * slot, (round - 1) & 1, abort_flag, p.status, kDevTimeoutLoad);
+      if (lane == 0) {
+        const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
+        const int row = (i >> 1) * kTileN;
+        const uint32_t dst = kv_smem + slot * kTileBytes;
+        const uint32_t bar = bar_kv_full + 8 * slot;
+        mbar_arrive_expect_tx(bar, kTileBytes);
+        tma_load_4d(dst, tm, bar, 0, head, row, batch);
+        tma_load_4d(dst + kHalfTileBytes, tm, bar, 64, head, row, batch);
+      }
+      __syncwarp();
+    }
+    if (*abort_flag && lane == 0) {
+      // A role gave up: make sure no bulk copy of ours is still landing in this
+      // CTA's shared memory before the CTA retires (bounded polls).
+      for (int i = max(0, n_items - kStages); i < n_items; ++i) {
+        const uint32_t bar = bar_kv_full + 8 * (i % kStages);
+        const uint32_t par = (i / kStages) & 1;
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, par); ++spin) {
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t kIdescQK = umma_idesc(1, kFp16 ? 0 : 1, kFp16 ? 0 : 1, 0, kTileM, kTileN);
+    constexpr uint32_t kIdescPV = umma_idesc(1, kFp16 ? 0 : 1, kFp16 ? 0 : 1, 1, kTileM, kHeadDim);
+    auto issue_qk = [&](int t, int slot) {
+      // S_t = Q_t K^T : both operands K-major, 8 steps of 16 along head_dim
+      const uint32_t a0 = q_smem + t * kTileBytes;
+      const uint32_t b0 = kv_smem + slot * kTileBytes;
+#pragma unroll
+      for (int k = 0; k < kHeadDim / 16; ++k) {
+        const uint32_t off = (k >> 2) * kHalfTileBytes + (k & 3) * 32;
+        umma_ss_f16(tmem_base + t * kTileN, umma_smem_desc_sw128(a0 + off, 16, 1024),
+                    umma_smem_desc_sw128(b0 + off, 16, 1024), kIdescQK, k > 0);
+      }
+    };
+    auto issue_pv = [&](int t, int slot, bool accumulate) {
+      // O_t += P_t V : A = P from tensor memory (two 16-bit values per column),
+      // B = V tile as loaded ([key][d], d contiguous => MN-major), 8 steps of 16 keys
+      const uint32_t b0 = kv_smem + slot * kTileBytes;
+#pragma unroll
+      for (int k = 0; k < kTileN / 16; ++k) {
+        umma_ts_f16(tmem_base + 2 * kTileN + t * kHeadDim, tmem_base + t * kTileN + k * 8,
+                    umma_smem_desc_sw128(b0 + k * 2048, kHalfTileBytes, 1024), kIdescPV, accumulate || k > 0);
+      }
+    };
+    auto wait_item = [&](int i) {
+      mbar_wait(bar_kv_full + 8 * (i % kStages), (i / kStages) & 1, abort_flag, p.status, kDevTimeoutMma);
+    };
+
+    mbar_wait(bar_q_full, 0, abort_flag, p.status, kDevTimeoutMma);
+    wait_item(0);
+    tc_fence_after_sync();
+    if (lane == 0) {
+      issue_qk(0, 0);
+      umma_commit(bar_s_full);
+    }
+    __syncwarp();
+    if (n_qt > 1) {
+      mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kDevTimeoutMma);
+      tc_fence_after_sync();
+      if (lane == 0) {
+        issue_qk(1, 0);
+        umma_commit(bar_s_full + 8);
+      }
+      __syncwarp();
+    }
+    if (lane == 0) umma_commit(bar_kv_empty);  // K_0 free once both QK^T have run
+    __syncwarp();
+
+    for (int j = 0; j < n_kv; ++j) {
+      const bool more = (j + 1 < n_kv);
+      const int iv = 2 * j + 1;  // V_j
+      const int ik = 2 * j + 2;  // K_{j+1}
+      if (more) wait_item(ik);
+      wait_item(iv);
+      for (int t = 0; t < n_qt; ++t) {
+        mbar_wait(bar_p_full + 8 * t, j & 1, abort_flag, p.status, kDevTimeoutMma);
+        tc_fence_after_sync();
+        if (lane == 0) {
+          issue_pv(t, iv % kStages, j > 0);
+          if (more) {
+            issue_qk(t, ik % kStages);
+            umma_commit(bar_s_full + 8 * t);
+          } else {
+            umma_commit(bar_o_final + 8 * t);
+          }
+        }
+        __syncwarp();
+      }
+      if (lane == 0) {
+        umma_commit(bar_kv_empty + 8 * (iv % kStages));
+        if (more) umma_commit(bar_kv_empty + 8 * (ik % kStages));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int t = warp >> 2;
+    if (t < n_qt) {
+      const int quad = warp & 3;
+      const int row_in_tile = quad * 32 + lane;
+      const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+      const uint32_t t_s = tmem_base + lane_base + t * kTileN;
+      const uint32_t t_o = tmem_base + lane_base + 2 * kTileN + t * kHeadDim;
+      const float sl2 = p.scale_log2;
+      const int tail_valid = p.Sk - (n_kv - 1) * kTileN;  // 1..128 valid keys in the last tile
+      float m_used = -INFINITY;
+      float l_sum = 0.f;
+
+      for (int j = 0; j < n_kv; ++j) {
+        mbar_wait(bar_s_full + 8 * t, j & 1, abort_flag, p.status, kDevTimeoutSoftmax);
+        tc_fence_after_sync();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
+        tmem_wait_ld();
+
+        if (j == n_kv - 1 && tail_valid < kTileN) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+          }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+        if (j == 0) {
+          m_used = mx;
+        } else {
+          const bool need = (mx - m_used) * sl2 > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const float f = need ? fast_exp2((m_used - mx) * sl2) : 1.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_o + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+              tmem_st32(t_o + c * 32, o);
+            }
+            l_sum *= f;
+            if (need) m_used = mx;
+          }
+        }
+
+        const float neg_m = -m_used * sl2;
+        uint32_t pk[2][32];
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), sl2, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), sl2, neg_m));
+            l0 += e0;
+            l1 += e1;
+            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack2<kFp16>(e0, e1);
+          }
+        l_sum += l0 + l1;
+        tmem_st32(t_s, pk[0]);
+        tmem_st32(t_s + 32, pk[1]);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar_p_full + 8 * t);
+      }
+
+      // epilogue: O / l -> 16-bit, row-contiguous 256-byte stores; LSE in natural log
+      mbar_wait(bar_o_final + 8 * t, 0, abort_flag, p.status, kDevTimeoutEpilogue);
+      tc_fence_after_sync();
+      const int row = q0 + t * kTileM + row_in_tile;
+      const float inv_l = 1.0f / l_sum;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) +
+                                            ((static_cast<size_t>(batch) * p.Sq + row) * p.H + head) * (kHeadDim * 2));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + c * 32, o);
+        tmem_wait_ld();
+        if (row < p.Sq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack2<kFp16>(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+            v.y = pack2<kFp16>(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+            v.z = pack2<kFp16>(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+            v.w = pack2<kFp16>(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+            dst[c * 4 + (i >> 3)] = v;
+          }
+        }
+      }
+      if (p.lse != nullptr && row < p.Sq) {
+        p.lse[(static_cast<size_t>(batch) * p.H + head) * p.Sq + row] =
+            (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace chitu

@@ -1,0 +1,266 @@
+// extern "C" boundary of libchitu_b200.so: argument checks, tensor-map
+// construction and kernel launches.  Nothing here allocates device memory,
+// synchronises the device or throws.
+#include "../../include/chitu_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "attn_fwd.cuh"
+#include "elementwise.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(CHITU_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+  });
+  return fn;
+}
+
+// Tensor map over a [B, S, H, 128] 16-bit tensor with element strides {b, s, h, 1}:
+// dims (innermost first) d, h, s, b; box = 64 x 1 x 128 x 1 with 128-byte swizzle,
+// i.e. one 128-row x 128-byte panel per copy; rows past S read as zero.
+int make_qkv_map(CUtensorMap* map, const void* base, int B, int S, int H, const int64_t* st, const char* name) {
+  auto encode = get_encode_fn();
+  if (!encode) return fail(CHITU_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  if (reinterpret_cast<uintptr_t>(base) & 15) return fail(CHITU_E_INVALID, "%s: base must be 16-byte aligned", name);
+  if (st[3] != 1) return fail(CHITU_E_INVALID, "%s: head_dim stride must be 1 (got %lld)", name, (long long)st[3]);
+  for (int i = 0; i < 3; ++i) {
+    const bool degenerate = (i == 0 && B == 1) || (i == 1 && S == 1) || (i == 2 && H == 1);
+    if (!degenerate && (st[i] <= 0 || (st[i] & 7)))
+      return fail(CHITU_E_INVALID, "%s: stride[%d] = %lld must be a positive multiple of 8 elements", name, i,
+                  (long long)st[i]);
+  }
+  auto stride_bytes = [&](int i, int extent) -> cuuint64_t {
+    // a dimension of extent 1 never advances; give it any legal stride
+    return (extent == 1 || st[i] <= 0 || (st[i] & 7)) ? 256 : static_cast<cuuint64_t>(st[i]) * 2;
+  };
+  cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[3] = {stride_bytes(2, H), stride_bytes(1, S), stride_bytes(0, B)};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CHITU_E_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", name, (int)r);
+  return CHITU_OK;
+}
+
+int grid_for(long long work_items, int per_block, int max_blocks) {
+  long long g = (work_items + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  if (g > max_blocks) g = max_blocks;
+  return static_cast<int>(g);
+}
+
+int elem_size(int dtype) { return dtype == CHITU_DTYPE_FP32 ? 4 : 2; }
+
+}  // namespace
+
+extern "C" {
+
+int chitu_b200_version(void) { return 100; }
+
+unsigned chitu_b200_caps(void) {
+  return CHITU_CAP_ATTN_BF16 | CHITU_CAP_ATTN_FP16 | CHITU_CAP_NORM_ROPE | CHITU_CAP_LSE_COMBINE | CHITU_CAP_A2A_LAYOUT;
+}
+
+const char* chitu_b200_last_error(void) { return g_err; }
+
+int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                        int H, int D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                        float softmax_scale, int dtype, int* status, void* stream) {
+  if (!q || !k || !v || !out || !q_strides || !k_strides || !v_strides)
+    return fail(CHITU_E_INVALID, "attn_fwd: null pointer argument");
+  if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0)
+    return fail(CHITU_E_INVALID, "attn_fwd: B, H, Sq, Sk must be positive (got %d, %d, %d, %d)", B, H, Sq, Sk);
+  if (D != chitu::kHeadDim) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: head_dim %d not supported (only 128)", D);
+  if (dtype != CHITU_DTYPE_BF16 && dtype != CHITU_DTYPE_FP16)
+    return fail(CHITU_E_UNSUPPORTED, "attn_fwd: dtype must be bf16 or fp16");
+  if (!(softmax_scale > 0.f)) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: softmax_scale must be positive");
+  if (reinterpret_cast<uintptr_t>(out) & 15) return fail(CHITU_E_INVALID, "attn_fwd: out must be 16-byte aligned");
+  if (H > 65535 || B > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: H and B must be below 65536");
+
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_qkv_map(&tq, q, B, Sq, H, q_strides, "q")) != CHITU_OK) return rc;
+  if ((rc = make_qkv_map(&tk, k, B, Sk, H, k_strides, "k")) != CHITU_OK) return rc;
+  if ((rc = make_qkv_map(&tv, v, B, Sk, H, v_strides, "v")) != CHITU_OK) return rc;
+
+  chitu::AttnParams p;
+  p.out = out;
+  p.lse = lse;
+  p.status = status;
+  p.B = B;
+  p.H = H;
+  p.Sq = Sq;
+  p.Sk = Sk;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.is_fp16 = dtype == CHITU_DTYPE_FP16;
+
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute(chitu::attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    chitu::kAttnSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(chitu::attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      chitu::kAttnSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
+
+  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p.is_fp16)
+    chitu::attn_fwd_kernel<true><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
+  else
+    chitu::attn_fwd_kernel<false><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attn_fwd: launch");
+  return CHITU_OK;
+}
+
+int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out, const float* block_lse, int B, int S,
+                           int H, int D, int block_dtype, int first, void* final_out, int final_dtype, void* stream) {
+  if (!acc_out || !acc_lse || !block_out || !block_lse) return fail(CHITU_E_INVALID, "lse_combine: null pointer");
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0 || (D & 3))
+    return fail(CHITU_E_INVALID, "lse_combine: bad shape (D must be a multiple of 4)");
+  if (block_dtype < 0 || block_dtype > 2 || (final_out && (final_dtype < 0 || final_dtype > 2)))
+    return fail(CHITU_E_INVALID, "lse_combine: bad dtype");
+  if ((reinterpret_cast<uintptr_t>(acc_out) | reinterpret_cast<uintptr_t>(block_out) |
+       reinterpret_cast<uintptr_t>(final_out)) & 15)
+    return fail(CHITU_E_INVALID, "lse_combine: buffers must be 16-byte aligned");
+  const long long rows = static_cast<long long>(B) * S * H;
+  const int grid = grid_for(rows, 8, 148 * 16);
+  chitu::lse_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      acc_out, acc_lse, block_out, block_lse, B, S, H, D, block_dtype, first, final_out, final_dtype);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "lse_combine: launch");
+  return CHITU_OK;
+}
+
+int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype,
+                            float eps, int norm_mode, int rope_mode, const float* rope_table, int table_rows, int gf,
+                            int gh, int gw, const int* axis_split, int64_t pos_offset, void* out, int out_dtype,
+                            const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D, int round_mid,
+                            void* stream) {
+  if (!x || !out || !out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: bad shape");
+  if (D & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: head_dim must be a multiple of 8");
+  const long long C = static_cast<long long>(H) * D;
+  if (C > chitu::kNormThreads * 8 * chitu::kNormMaxVec)
+    return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: at most %d channels per token", chitu::kNormThreads * 8 * chitu::kNormMaxVec);
+  if (in_dtype < 0 || in_dtype > 2 || (out_dtype != CHITU_DTYPE_BF16 && out_dtype != CHITU_DTYPE_FP16))
+    return fail(CHITU_E_INVALID, "qk_norm_rope: bad dtype");
+  if (weight && w_dtype != CHITU_DTYPE_BF16 && w_dtype != CHITU_DTYPE_FP32 && w_dtype != CHITU_DTYPE_FP16)
+    return fail(CHITU_E_INVALID, "qk_norm_rope: bad weight dtype");
+  if (norm_mode < 0 || norm_mode > 2 || rope_mode < 0 || rope_mode > 2)
+    return fail(CHITU_E_INVALID, "qk_norm_rope: bad mode");
+  if (norm_mode == 1) {
+    const int vph = D >> 3;
+    if (vph > 32 || (vph & (vph - 1))) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: per-head norm needs D in {8..256} power of two");
+  }
+  if (x_row_stride < C || (x_row_stride * elem_size(in_dtype)) % 16)
+    return fail(CHITU_E_INVALID, "qk_norm_rope: x_row_stride must cover H*D and keep rows 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(CHITU_E_INVALID, "qk_norm_rope: x and out must be 16-byte aligned");
+  if (heads_per_group <= 0 || H % heads_per_group) return fail(CHITU_E_INVALID, "qk_norm_rope: heads_per_group must divide H");
+  for (int i = 0; i < 4; ++i)
+    if (out_strides[i] & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: out_strides must be multiples of 8 elements");
+  chitu::NormRopeParams p;
+  p.n_t = p.n_h = 0;
+  if (rope_mode != 0) {
+    if (!rope_table || table_rows <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: rope table missing");
+    if (rope_mode == 1) {
+      if (!axis_split || gf <= 0 || gh <= 0 || gw <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: grid / axis_split missing");
+      if (axis_split[0] < 0 || axis_split[1] < 0 || axis_split[0] + axis_split[1] > D / 2)
+        return fail(CHITU_E_INVALID, "qk_norm_rope: axis_split out of range");
+      if (gf > table_rows || gh > table_rows || gw > table_rows)
+        return fail(CHITU_E_INVALID, "qk_norm_rope: rope table has fewer rows than the grid extent");
+      p.n_t = axis_split[0];
+      p.n_h = axis_split[1];
+    }
+  }
+  p.x = x;
+  p.in_dtype = in_dtype;
+  p.x_row_stride = x_row_stride;
+  p.weight = weight;
+  p.w_dtype = w_dtype;
+  p.eps = eps;
+  p.norm_mode = norm_mode;
+  p.rope_mode = rope_mode;
+  p.table = reinterpret_cast<const float2*>(rope_table);
+  p.table_rows = table_rows;
+  p.gf = gf;
+  p.gh = gh;
+  p.gw = gw;
+  p.pos_offset = pos_offset;
+  p.out = out;
+  p.out_dtype = out_dtype;
+  p.os_b = out_strides[0];
+  p.os_s = out_strides[1];
+  p.os_g = out_strides[2];
+  p.os_h = out_strides[3];
+  p.heads_per_group = heads_per_group;
+  p.B = B;
+  p.S = S;
+  p.H = H;
+  p.D = D;
+  p.round_mid = round_mid;
+  const long long tokens = static_cast<long long>(B) * S;
+  if (tokens > 2147483647LL) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: too many tokens");
+  chitu::qk_norm_rope_kernel<<<static_cast<unsigned>(tokens), chitu::kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "qk_norm_rope: launch");
+  return CHITU_OK;
+}
+
+int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t n3,
+                            int64_t row_bytes, const int64_t* src_strides_bytes, void* stream) {
+  if (!src || !dst || !src_strides_bytes) return fail(CHITU_E_INVALID, "strided_copy: null pointer");
+  if (n0 <= 0 || n1 <= 0 || n2 <= 0 || n3 <= 0 || row_bytes <= 0 || (row_bytes & 15))
+    return fail(CHITU_E_INVALID, "strided_copy: extents must be positive and row_bytes a multiple of 16");
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)
+    return fail(CHITU_E_INVALID, "strided_copy: src and dst must be 16-byte aligned");
+  for (int i = 0; i < 4; ++i)
+    if (src_strides_bytes[i] & 15) return fail(CHITU_E_INVALID, "strided_copy: strides must be multiples of 16 bytes");
+  const long long row_vecs = row_bytes / 16;
+  const long long total = n0 * n1 * n2 * n3 * row_vecs;
+  const int grid = grid_for(total, 256 * 4, 148 * 8);
+  chitu::strided_copy_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint4*>(dst), n1, n2, n3, row_vecs, src_strides_bytes[0],
+      src_strides_bytes[1], src_strides_bytes[2], src_strides_bytes[3], total);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "strided_copy: launch");
+  return CHITU_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,269 @@
+// HBM-bound kernels around the attention core: LSE combine of partial results,
+// the pre-attention RMSNorm + rotary transform, and the 16-byte strided copy
+// used for all-to-all send/receive layouts.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace chitu {
+
+enum : int { kBF16 = 0, kFP16 = 1, kFP32 = 2 };
+
+__device__ __forceinline__ float ld_as_float(const void* p, int dtype, size_t i) {
+  if (dtype == kFP32) return static_cast<const float*>(p)[i];
+  if (dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ float round_to(float x, int dtype) {
+  if (dtype == kBF16) return __bfloat162float(__float2bfloat16_rn(x));
+  if (dtype == kFP16) return __half2float(__float2half_rn(x));
+  return x;
+}
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int dtype) {
+  if (dtype == kBF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Load 4 consecutive elements starting at element index i (i % 4 == 0).
+__device__ __forceinline__ float4 ld4(const void* p, int dtype, size_t i) {
+  if (dtype == kFP32) return *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p) + i);
+  float4 r;
+  if (dtype == kBF16) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    r = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  } else {
+    const __half2 a = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 b = *reinterpret_cast<const __half2*>(&raw.y);
+    r = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  return r;
+}
+__device__ __forceinline__ void st4(void* p, int dtype, size_t i, float4 v) {
+  if (dtype == kFP32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(p) + i) = v;
+  } else {
+    uint2 raw;
+    raw.x = pack16(v.x, v.y, dtype);
+    raw.y = pack16(v.z, v.w, dtype);
+    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p) + i) = raw;
+  }
+}
+
+// ----------------------------------------------------------------------------
+// LSE combine: one warp per (b, s, h) row of D values.
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+lse_combine_kernel(float* __restrict__ acc_out, float* __restrict__ acc_lse, const void* __restrict__ blk_out,
+                   const float* __restrict__ blk_lse, int B, int S, int H, int D, int blk_dtype, int first,
+                   void* __restrict__ final_out, int final_dtype) {
+  const int lane = threadIdx.x & 31;
+  const long long warps_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const long long rows = static_cast<long long>(B) * S * H;
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += warps_total) {
+    const int h = static_cast<int>(row % H);
+    const long long bs = row / H;
+    const int s = static_cast<int>(bs % S);
+    const int b = static_cast<int>(bs / S);
+    const float lb = blk_lse[(static_cast<size_t>(b) * H + h) * S + s];
+    float w = 0.f, new_lse = lb;
+    if (!first) {
+      const float la = acc_lse[row];
+      const float x = lb - la;  // weight of the block = sigmoid(lse_b - lse)
+      w = 1.0f / (1.0f + expf(-x));
+      // lse - logsigmoid(lse - lse_b), logsigmoid(y) = min(y, 0) - log1p(exp(-|y|))
+      const float y = -x;
+      new_lse = la - (fminf(y, 0.f) - log1pf(expf(-fabsf(y))));
+    }
+    const size_t base = static_cast<size_t>(row) * D;
+    for (int d = lane * 4; d < D; d += 128) {
+      const float4 ob = ld4(blk_out, blk_dtype, base + d);
+      float4 r = ob;
+      if (!first) {
+        const float4 oa = *reinterpret_cast<const float4*>(acc_out + base + d);
+        r.x = oa.x - w * (oa.x - ob.x);
+        r.y = oa.y - w * (oa.y - ob.y);
+        r.z = oa.z - w * (oa.z - ob.z);
+        r.w = oa.w - w * (oa.w - ob.w);
+      }
+      *reinterpret_cast<float4*>(acc_out + base + d) = r;
+      if (final_out != nullptr) st4(final_out, final_dtype, base + d, r);
+    }
+    if (lane == 0) acc_lse[row] = new_lse;
+  }
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm + rotary + cast: one CTA per token, 8-element vectors in registers.
+// ----------------------------------------------------------------------------
+struct NormRopeParams {
+  const void* x;
+  int in_dtype;
+  long long x_row_stride;
+  const void* weight;
+  int w_dtype;
+  float eps;
+  int norm_mode;  // 0 full channel dim, 1 per head, 2 none
+  int rope_mode;  // 0 none, 1 three-axis grid, 2 per-token table
+  const float2* table;
+  int table_rows;
+  int gf, gh, gw, n_t, n_h;
+  long long pos_offset;
+  void* out;
+  int out_dtype;
+  long long os_b, os_s, os_g, os_h;
+  int heads_per_group;
+  int B, S, H, D;
+  int round_mid;
+};
+
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;  // up to 256 * 8 * 4 = 8192 channels per token
+
+__global__ void __launch_bounds__(kNormThreads) qk_norm_rope_kernel(const NormRopeParams p) {
+  __shared__ float red[kNormThreads / 32];
+  const int C = p.H * p.D;
+  const int nvec = C >> 3;
+  const long long token = blockIdx.x;
+  const int b = static_cast<int>(token / p.S);
+  const int s = static_cast<int>(token % p.S);
+  const size_t row = static_cast<size_t>(token) * p.x_row_stride;
+
+  float v[kNormMaxVec][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormMaxVec; ++k) {
+    const int vi = threadIdx.x + k * kNormThreads;
+    if (vi < nvec) {
+      const float4 a = ld4(p.x, p.in_dtype, row + vi * 8);
+      const float4 c = ld4(p.x, p.in_dtype, row + vi * 8 + 4);
+      v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
+      v[k][4] = c.x; v[k][5] = c.y; v[k][6] = c.z; v[k][7] = c.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[k][e] = 0.f;
+    }
+  }
+
+  float rstd_full = 1.f;
+  if (p.norm_mode == 0) {
+#pragma unroll
+    for (int k = 0; k < kNormMaxVec; ++k)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(v[k][e], v[k][e], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
+    rstd_full = rsqrtf(tot / static_cast<float>(C) + p.eps);
+  }
+
+  // token position for the rotary table
+  const long long n = p.pos_offset + s;
+  int pf = 0, ph = 0, pw = 0;
+  bool rotate = p.rope_mode != 0;
+  if (p.rope_mode == 1) {
+    const long long grid = static_cast<long long>(p.gf) * p.gh * p.gw;
+    if (n >= grid) {
+      rotate = false;
+    } else {
+      pf = static_cast<int>(n / (static_cast<long long>(p.gh) * p.gw));
+      ph = static_cast<int>((n / p.gw) % p.gh);
+      pw = static_cast<int>(n % p.gw);
+    }
+  } else if (p.rope_mode == 2) {
+    if (n >= p.table_rows) rotate = false;
+  }
+  const int half_d = p.D >> 1;
+  const int vec_per_head = p.D >> 3;
+
+#pragma unroll
+  for (int k = 0; k < kNormMaxVec; ++k) {
+    const int vi = threadIdx.x + k * kNormThreads;
+    float rstd = rstd_full;
+    if (p.norm_mode == 1) {
+      float hs = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) hs = fmaf(v[k][e], v[k][e], hs);
+      for (int o = vec_per_head >> 1; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
+      rstd = rsqrtf(hs / static_cast<float>(p.D) + p.eps);
+    }
+    if (vi >= nvec) continue;
+    const int c0 = vi * 8;
+    const int h = c0 / p.D;
+    const int d0 = c0 - h * p.D;
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float t = v[k][e];
+      if (p.norm_mode != 2) {
+        t *= rstd;
+        if (p.round_mid) t = round_to(t, p.in_dtype);
+        if (p.weight != nullptr) {
+          const int wi = (p.norm_mode == 0) ? (c0 + e) : (d0 + e);
+          t *= ld_as_float(p.weight, p.w_dtype, wi);
+          if (p.round_mid && p.w_dtype != kFP32 && p.in_dtype != kFP32) t = round_to(t, p.w_dtype);
+        }
+      }
+      y[e] = t;
+    }
+    if (rotate) {
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const int j = (d0 + e) >> 1;
+        long long trow;
+        if (p.rope_mode == 1) {
+          trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
+        } else {
+          trow = n;
+        }
+        const float2 cs = p.table[trow * half_d + j];
+        const float re = y[e] * cs.x - y[e + 1] * cs.y;
+        const float im = y[e] * cs.y + y[e + 1] * cs.x;
+        y[e] = re;
+        y[e + 1] = im;
+      }
+    }
+    uint4 o;
+    o.x = pack16(y[0], y[1], p.out_dtype);
+    o.y = pack16(y[2], y[3], p.out_dtype);
+    o.z = pack16(y[4], y[5], p.out_dtype);
+    o.w = pack16(y[6], y[7], p.out_dtype);
+    const long long off = b * p.os_b + s * p.os_s + (h / p.heads_per_group) * p.os_g +
+                          (h % p.heads_per_group) * p.os_h + d0;
+    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + off) = o;
+  }
+}
+
+// ----------------------------------------------------------------------------
+// strided copy of 16-byte vectors: dst contiguous [n0, n1, n2, n3, row_vecs]
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+strided_copy_kernel(const uint8_t* __restrict__ src, uint4* __restrict__ dst, long long n1, long long n2, long long n3,
+                    long long row_vecs, long long st0, long long st1, long long st2, long long st3, long long total) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    long long r = i / row_vecs;
+    const long long vec = i - r * row_vecs;
+    const long long i3 = r % n3; r /= n3;
+    const long long i2 = r % n2; r /= n2;
+    const long long i1 = r % n1;
+    const long long i0 = r / n1;
+    const uint4* sp = reinterpret_cast<const uint4*>(src + i0 * st0 + i1 * st1 + i2 * st2 + i3 * st3) + vec;
+    dst[i] = *sp;
+  }
+}
+
+}  // namespace chitu

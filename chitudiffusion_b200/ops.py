@@ -1,0 +1,217 @@
+"""Operator-level Python entry points: torch tensors in, C-ABI calls out.
+
+Torch is used for device memory and the current stream only; all arithmetic
+happens inside libchitu_b200.so.  Every function raises if the tensors are not
+on a CUDA device - there is no CPU path.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}
+
+_STATUS_NAMES = {
+    1: "TMA producer waited too long for a free K/V stage",
+    2: "MMA issuer waited too long for operands",
+    3: "softmax warps waited too long for scores",
+    4: "epilogue waited too long for the last MMA",
+    5: "a bounded flag wait ran out",
+}
+
+_status_words = {}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("chitudiffusion_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 status word that kernels with bounded waits report into."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    word = _status_words.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+        _status_words[key] = word
+    return word
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel on `device` reported a timed-out wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = status_word(dev)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise _lib.ChituB200Error(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+
+
+def attn_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``softmax(scale * q k^T) v`` for ``[B,S,H,128]`` bf16/fp16 tensors of any (16-byte aligned) strides.
+
+    Returns ``(out [B,Sq,H,D] contiguous, lse [B,H,Sq] fp32 | None)``.
+    """
+    _require_cuda(q, k, v)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be [B, S, H, D]")
+    B, Sq, H, D = q.shape
+    if k.shape != v.shape or k.shape[0] != B or k.shape[2] != H or k.shape[3] != D:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError("attention kernel takes bf16 or fp16 q/k/v of one dtype")
+    Sk = k.shape[1]
+    if Sq == 0 or Sk == 0:
+        raise ValueError("empty sequence")
+
+    def usable(t):
+        return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+
+    q, k, v = (t if usable(t) else t.contiguous() for t in (q, k, v))
+    if out is None:
+        out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    elif out.shape != (B, Sq, H, D) or not out.is_contiguous() or out.dtype != q.dtype:
+        raise ValueError("out must be a contiguous [B,Sq,H,D] tensor of q's dtype")
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if return_lse else None
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        rc = lib.chitu_b200_attn_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+            B, Sq, Sk, H, D, _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()),
+            scale, _DTYPES[q.dtype], status_word(q.device).data_ptr(), _stream_ptr(q.device),
+        )
+    _lib.check(rc, "attn_fwd")
+    return out, lse
+
+
+def lse_combine(
+    acc_out: torch.Tensor,
+    acc_lse: torch.Tensor,
+    block_out: torch.Tensor,
+    block_lse: torch.Tensor,
+    first: bool,
+    final_out: Optional[torch.Tensor] = None,
+) -> None:
+    """In-place fold of one partial result; see ``chitu_b200_lse_combine``.
+
+    ``acc_out [B,S,H,D] fp32``, ``acc_lse [B,S,H]`` (or ``[B,S,H,1]``) fp32, ``block_out [B,S,H,D]``,
+    ``block_lse [B,H,S] fp32``; all contiguous.
+    """
+    _require_cuda(acc_out, acc_lse, block_out, block_lse, final_out)
+    B, S, H, D = block_out.shape
+    if acc_out.shape != block_out.shape or acc_out.dtype != torch.float32 or not acc_out.is_contiguous():
+        raise ValueError("acc_out must be contiguous fp32 [B,S,H,D]")
+    if acc_lse.numel() != B * S * H or acc_lse.dtype != torch.float32 or not acc_lse.is_contiguous():
+        raise ValueError("acc_lse must be contiguous fp32 [B,S,H] or [B,S,H,1]")
+    if tuple(block_lse.shape) != (B, H, S) or block_lse.dtype != torch.float32:
+        raise ValueError("block_lse must be fp32 [B,H,S]")
+    block_out = block_out.contiguous()
+    block_lse = block_lse.contiguous()
+    if final_out is not None and (final_out.shape != block_out.shape or not final_out.is_contiguous()):
+        raise ValueError("final_out must be contiguous [B,S,H,D]")
+    lib = _lib.load()
+    with torch.cuda.device(acc_out.device):
+        rc = lib.chitu_b200_lse_combine(
+            acc_out.data_ptr(), acc_lse.data_ptr(), block_out.data_ptr(), block_lse.data_ptr(), B, S, H, D,
+            _DTYPES[block_out.dtype], 1 if first else 0,
+            final_out.data_ptr() if final_out is not None else None,
+            _DTYPES[final_out.dtype] if final_out is not None else 0, _stream_ptr(acc_out.device),
+        )
+    _lib.check(rc, "lse_combine")
+
+
+def qk_norm_rope(
+    x: torch.Tensor,
+    num_heads: int,
+    weight: Optional[torch.Tensor],
+    eps: float,
+    norm_mode: int,
+    rope_mode: int,
+    rope_table: Optional[torch.Tensor],
+    grid: Sequence[int] = (0, 0, 0),
+    axis_split: Sequence[int] = (0, 0),
+    pos_offset: int = 0,
+    out: Optional[torch.Tensor] = None,
+    out_strides: Optional[Sequence[int]] = None,
+    heads_per_group: Optional[int] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    round_mid: bool = True,
+) -> torch.Tensor:
+    """RMSNorm + rotary + 16-bit cast of a projection output ``[B,S,H*D]``; see ``chitu_b200_qk_norm_rope``.
+
+    Without ``out`` a contiguous ``[B,S,H,D]`` tensor is returned.  With ``out`` and ``out_strides``
+    ``(b, s, head_group, head_in_group)`` the result is scattered into a caller-owned buffer.
+    """
+    _require_cuda(x, weight, rope_table, out)
+    if x.dim() != 3:
+        raise ValueError("x must be [B, S, C]")
+    B, S, C = x.shape
+    if C % num_heads:
+        raise ValueError("channels not divisible by num_heads")
+    D = C // num_heads
+    if x.stride(2) != 1 or (B > 1 and x.stride(0) != S * x.stride(1)):
+        x = x.contiguous()
+    if weight is not None:
+        weight = weight.contiguous()
+        if weight.dtype not in _DTYPES:
+            raise ValueError("weight dtype must be bf16, fp16 or fp32")
+    if rope_mode != 0:
+        if rope_table is None or rope_table.dtype != torch.float32 or not rope_table.is_contiguous():
+            raise ValueError("rope_table must be a contiguous fp32 [rows, D/2, 2] tensor")
+        if rope_table.shape[-2:] != (D // 2, 2):
+            raise ValueError(f"rope_table must be [rows, {D // 2}, 2]")
+    if out is None:
+        out = torch.empty((B, S, num_heads, D), dtype=out_dtype, device=x.device)
+        out_strides = (S * C, C, 0, D)
+        heads_per_group = num_heads
+    elif out_strides is None or heads_per_group is None:
+        raise ValueError("out needs out_strides and heads_per_group")
+    lib = _lib.load()
+    import ctypes
+
+    split = (ctypes.c_int * 2)(int(axis_split[0]), int(axis_split[1]))
+    with torch.cuda.device(x.device):
+        rc = lib.chitu_b200_qk_norm_rope(
+            x.data_ptr(), _DTYPES[x.dtype], x.stride(1), weight.data_ptr() if weight is not None else None,
+            _DTYPES[weight.dtype] if weight is not None else _lib.DTYPE_FP32, float(eps), int(norm_mode),
+            int(rope_mode), rope_table.data_ptr() if rope_table is not None else None,
+            int(rope_table.shape[0]) if rope_table is not None else 0, int(grid[0]), int(grid[1]), int(grid[2]),
+            split, int(pos_offset), out.data_ptr(), _DTYPES[out.dtype], _lib.i64_array(out_strides),
+            int(heads_per_group), B, S, num_heads, D, 1 if round_mid else 0, _stream_ptr(x.device),
+        )
+    _lib.check(rc, "qk_norm_rope")
+    return out
+
+
+def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """Copy a 5-d view ``src [n0,n1,n2,n3,row]`` (last dim contiguous) into contiguous ``dst``."""
+    _require_cuda(src, dst)
+    if src.dim() != 5 or dst.shape != src.shape or not dst.is_contiguous() or src.stride(4) != 1:
+        raise ValueError("strided_copy: src must be 5-d with a contiguous last dim, dst contiguous of the same shape")
+    es = src.element_size()
+    lib = _lib.load()
+    with torch.cuda.device(src.device):
+        rc = lib.chitu_b200_strided_copy(
+            src.data_ptr(), dst.data_ptr(), *[int(n) for n in src.shape[:4]], int(src.shape[4]) * es,
+            _lib.i64_array([s * es for s in src.stride()[:4]]), _stream_ptr(src.device),
+        )
+    _lib.check(rc, "strided_copy")
+    return dst

@@ -1,0 +1,131 @@
+/*
+ * chitu_b200.h - C ABI of the B200-native attention hot path.
+ *
+ * A shared library (libchitu_b200.so) with plain-C entry points: raw device
+ * pointers, integer shapes and element strides, a CUDA stream handle passed as
+ * void*.  No entry point allocates device memory, synchronises the device or
+ * throws; each returns 0 on success or a negative CHITU_E_* code, and
+ * chitu_b200_last_error() gives the message for the calling thread.  Kernels
+ * that can wait on another agent take an optional device status word
+ * (int32, zero-initialised by the caller) which they set to a positive code if
+ * a bounded wait ran out; the launch itself still returns 0.
+ *
+ * Tensors follow the reference's layouts: q/k/v/out are [B, S, H, D]
+ * (D = 128 contiguous), the block log-sum-exp is [B, H, S] fp32 (natural log,
+ * softmax scale included).
+ *
+ * Each declaration names the reference interface it stands in for
+ * (file:line inside the ChituDiffusion tree).
+ */
+#ifndef CHITU_B200_H_
+#define CHITU_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CHITU_OK 0
+#define CHITU_E_INVALID (-1)     /* bad argument (shape, stride, alignment, null) */
+#define CHITU_E_UNSUPPORTED (-2) /* valid request this library does not implement */
+#define CHITU_E_CUDA (-3)        /* a CUDA runtime / driver call failed */
+
+#define CHITU_DTYPE_BF16 0
+#define CHITU_DTYPE_FP16 1
+#define CHITU_DTYPE_FP32 2
+
+/* Library version (major*10000 + minor*100 + patch) and capability bits. */
+int chitu_b200_version(void);
+#define CHITU_CAP_ATTN_BF16 1u
+#define CHITU_CAP_ATTN_FP16 2u
+#define CHITU_CAP_NORM_ROPE 4u
+#define CHITU_CAP_LSE_COMBINE 8u
+#define CHITU_CAP_A2A_LAYOUT 16u
+unsigned chitu_b200_caps(void);
+const char* chitu_b200_last_error(void);
+
+/*
+ * Dense non-causal attention forward, softmax(scale * q k^T) v.
+ * Replaces the per-rank kernel call behind DiffusionAttnBackend.__call__
+ * (chitu_diffusion/modules/attention/diffusion_attn_backend.py:131-207, the
+ * torch-SDPA form at :270-315 and the flash form at :404-447).
+ *
+ *   q            [B, Sq, H, 128], element strides q_strides[4] = {b, s, h, d}; d stride must be 1,
+ *                the others multiples of 8 elements; base 16-byte aligned.  Same for k, v ([B, Sk, H, 128]).
+ *   out          [B, Sq, H, 128] contiguous, same dtype as q.
+ *   lse          [B, H, Sq] fp32 or NULL.
+ *   dtype        CHITU_DTYPE_BF16 or CHITU_DTYPE_FP16.
+ *   status       optional device int32, see above.
+ */
+int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                        int H, int D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                        float softmax_scale, int dtype, int* status, void* stream);
+
+/*
+ * Fold one partial attention result into the running (out, lse) pair:
+ *   out <- out - sigmoid(lse_b - lse) * (out - out_b),  lse <- lse - logsigmoid(lse - lse_b)
+ * or, when `first` is non-zero, initialise them from the block.
+ * Replaces update_out_and_lse (chitu_diffusion/runtime/parallel_utils.py:59-97).
+ *
+ *   acc_out      [B, S, H, D] fp32 contiguous (read-modify-write)
+ *   acc_lse      [B, S, H] fp32 contiguous (the reference's [B, S, H, 1])
+ *   block_out    [B, S, H, D] contiguous, block_dtype in {BF16, FP16, FP32}
+ *   block_lse    [B, H, S] fp32 contiguous
+ *   final_out    optional [B, S, H, D] contiguous of final_dtype: also written with the merged result
+ */
+int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out, const float* block_lse, int B, int S,
+                           int H, int D, int block_dtype, int first, void* final_out, int final_dtype, void* stream);
+
+/*
+ * Pre-attention transform for one of q / k: RMSNorm, rotary embedding on
+ * interleaved pairs, cast to 16 bit, written with arbitrary output placement
+ * (so the result can land directly in an all-to-all send buffer).
+ * Replaces WanRMSNorm.forward + rope_apply / rope_apply_with_cp + half()
+ * (chitu_diffusion/models/model_wan.py:49-65,83-110,80-81;
+ *  chitu_diffusion/modules/utils/wan/__init__.py:31-67) and, with
+ * norm_mode = 1, the per-head RMSNorm + rotary embedding of the Flux / Qwen
+ * processors (chitu_diffusion/modules/attention/flux_attention.py:96-171).
+ *
+ *   x            [B, S, H*D] rows, element row stride x_row_stride (batch stride = S * x_row_stride)
+ *   in_dtype     BF16 / FP16 / FP32
+ *   weight       [H*D] (norm_mode 0) or [D] (norm_mode 1) or NULL (unit weight); w_dtype BF16 / FP32
+ *   norm_mode    0 = statistics over all H*D channels of a token, 1 = per head over D, 2 = no norm
+ *   rope_mode    0 = none,
+ *                1 = three-axis grid: token n (global index pos_offset + local index) sits at
+ *                    (n / (gh*gw), (n / gw) % gh, n % gw); pair j uses axis 0 for j < D/2 - 2*(D/6... see
+ *                    axis_split), rope_table is [max_pos, D/2] float2 (cos, sin) indexed by that axis' position;
+ *                    tokens with n >= gf*gh*gw pass through unrotated,
+ *                2 = per-token table: rope_table is [S_table, D/2] float2 indexed by pos_offset + local index.
+ *   axis_split   {n_t, n_h} pairs for rope_mode 1 (n_w = D/2 - n_t - n_h)
+ *   out          16-bit; element (b, s, h, d) is written at
+ *                out + b*out_strides[0] + s*out_strides[1] + (h / heads_per_group)*out_strides[2]
+ *                    + (h % heads_per_group)*out_strides[3] + d
+ *   round_mid    non-zero: round the normalised value to in_dtype before the weight multiply and round the
+ *                product to w_dtype when that is 16-bit (the reference's type_as / promotion order)
+ */
+int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype,
+                            float eps, int norm_mode, int rope_mode, const float* rope_table, int table_rows,
+                            int gf, int gh, int gw, const int* axis_split, int64_t pos_offset, void* out,
+                            int out_dtype, const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                            int round_mid, void* stream);
+
+/*
+ * Layout shuffles either side of the Ulysses all-to-all (packed single-buffer form).
+ * Replace the permute + contiguous() pairs in CommGroup._all_to_all_single
+ * (chitu_diffusion/core/distributed/comm_group.py:350-384).
+ *
+ *   pack_heads:    x [B, s, U*hc, D] (strided)      -> send [U, B, s, hc, D]
+ *   unpack_seq:    recv [U, B, s, hc, D]            -> y [B, U*s, hc, D]
+ *   pack_seq:      x [B, U*sc, h, D] (strided)      -> send [U, B, sc, h, D]
+ *   unpack_heads:  recv [U, B, sc, h, D]            -> y [B, sc, U*h, D]
+ * All are one generic 5-d strided copy of 16-byte vectors: dst is contiguous
+ * [n0, n1, n2, n3, row_bytes]; src strides are given in bytes per index.
+ */
+int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t n3,
+                            int64_t row_bytes, const int64_t* src_strides_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHITU_B200_H_ */
