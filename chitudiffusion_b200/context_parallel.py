@@ -1,0 +1,347 @@
+"""Context-parallel attention: Ulysses all-to-all, ring K/V rotation, all-gather-KV.
+
+Mirrors the surface of ``DiffusionAttention_with_CP``
+(chitu_diffusion/modules/attention/diffusion_attn_backend.py:449-1203): same
+constructor, same ``__call__`` signature returning ``(out_local, None, None)``,
+``uses_agcp()``, ``supports_fused_overlap()``, ``attention_fused()``,
+``cp_attn_with_full_txt()`` and ``cp_attn_with_full_txt_fused()``, the ``attn``,
+``ulysses_limit``, ``group``, ``cp_size`` and ``cp_backend`` attributes.
+
+What differs is the schedule, not the result:
+
+* the ring K/V exchange is posted on a side stream before the attention kernel
+  of the current block is enqueued, into double-buffered receive tensors, so
+  the NVLink transfer runs under the tensor-core work;
+* partial results are merged by one fused kernel per step, in the Ulysses
+  layout, and exchanged back ONCE after the last ring step (the reference
+  exchanges and merges in fp32 after every step; the merge is element-wise per
+  (token, head), so merging before the exchange gives the same numbers);
+* all-gather-KV lands directly in the ``[B, P*s, H, D]`` buffer.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .comm import CommGroup, get_cp_group, get_up_group
+
+
+class _KernelMerger:
+    """Running (out, lse) accumulator backed by the fused LSE-combine kernel."""
+
+    def __init__(self):
+        self.out: Optional[torch.Tensor] = None
+        self.lse: Optional[torch.Tensor] = None
+
+    def add(self, block_out: torch.Tensor, block_lse: torch.Tensor) -> None:
+        from . import ops
+
+        first = self.out is None
+        if first:
+            self.out = torch.empty(block_out.shape, dtype=torch.float32, device=block_out.device)
+            B, S, H, _ = block_out.shape
+            self.lse = torch.empty((B, S, H, 1), dtype=torch.float32, device=block_out.device)
+        ops.lse_combine(self.out, self.lse, block_out, block_lse, first=first)
+
+    def result(self) -> torch.Tensor:
+        return self.out
+
+
+class B200ContextParallel:
+    """Drop-in for ``DiffusionAttention_with_CP`` built on the b200 backend and NCCL over NVLink."""
+
+    def __init__(
+        self,
+        attn,
+        ulysses_limit: int,
+        ring_cudagraph: bool = False,
+        cp_backend: str = "ucp",
+        group: Optional[CommGroup] = None,
+        up_group_lookup: Optional[Callable[[int], CommGroup]] = None,
+        merger_factory: Optional[Callable[[], object]] = None,
+    ):
+        self.attn = attn
+        self.ulysses_limit = ulysses_limit
+        self.group = group if group is not None else get_cp_group()
+        self.cp_size = self.group.group_size
+        self.global_rank = dist.get_rank() if dist.is_initialized() else 0
+        self.local_chunk_id = self.group.rank_in_group
+        self.use_ring_cudagraph = bool(ring_cudagraph)
+        self.cp_backend = self._validate_cp_backend(cp_backend)
+        self._up_group_lookup = up_group_lookup or get_up_group
+        self._merger_factory = merger_factory or _KernelMerger
+        self._comm_stream: Optional[torch.cuda.Stream] = None
+        self._graph_cache: dict = {}
+
+    # ------------------------------------------------------------------ knobs
+    @staticmethod
+    def _validate_cp_backend(cp_backend: str) -> str:
+        mode = str(cp_backend or "ucp").strip().lower()
+        if mode not in {"agcp", "ucp"}:
+            raise ValueError(f"Resolved CP backend must be one of agcp, ucp; got {cp_backend!r}.")
+        return mode
+
+    def uses_agcp(self) -> bool:
+        return self.cp_backend == "agcp"
+
+    def _split(self) -> Tuple[int, int]:
+        """``(ulysses_size, ring_steps)`` as at diffusion_attn_backend.py:571-572."""
+        u = self.cp_size if self.cp_size <= self.ulysses_limit else self.ulysses_limit
+        return u, self.cp_size // u
+
+    def supports_fused_overlap(self, *, use_varlen: bool = False, return_attn_probs: bool = False,
+                               num_heads: Optional[int] = None) -> bool:
+        u, r = self._split()
+        return (
+            self.cp_size > 1 and self.cp_size % u == 0 and not self.uses_agcp() and not use_varlen and r == 1
+            and u > 1 and not return_attn_probs and torch.cuda.is_available()
+            and (num_heads is None or num_heads % u == 0)
+        )
+
+    def _side_stream(self, device) -> Optional["torch.cuda.Stream"]:
+        if device.type != "cuda":
+            return None
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=device)
+        return self._comm_stream
+
+    # ------------------------------------------------------------------ main entry
+    def __call__(
+        self,
+        q: torch.Tensor,
+        k: torch.Tensor,
+        v: torch.Tensor,
+        cu_seqlens_q: Optional[torch.Tensor] = None,
+        cu_seqlens_k: Optional[torch.Tensor] = None,
+        max_seqlen_q: Optional[int] = None,
+        max_seqlen_k: Optional[int] = None,
+        dropout_p: float = 0,
+        softmax_scale: Optional[float] = None,
+        causal: bool = False,
+        window_size: Tuple[int, int] = (-1, -1),
+        deterministic: bool = False,
+        return_attn_probs: bool = False,
+    ):
+        u, r = self._split()
+        if r > 1 and getattr(self.attn, "impl", "") in {"sage", "sparge", "b200_q8"}:
+            raise NotImplementedError(
+                f"{self.attn.impl} context parallelism currently supports Ulysses only; "
+                f"set infer.diffusion.up equal to cp_size ({self.cp_size})."
+            )
+        if cu_seqlens_q is not None or cu_seqlens_k is not None:
+            raise NotImplementedError("b200 context parallelism does not support varlen attention.")
+        kw = dict(dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal, window_size=window_size,
+                  deterministic=deterministic)
+        if self.uses_agcp():
+            k_full = self.group.all_gather_sequence(k)
+            v_full = self.group.all_gather_sequence(v)
+            out = self.attn(q, k_full, v_full, return_attn_probs=False, **kw)[0]
+            return out, None, None
+        return self._cp_forward(q, k, v, u, r, kw), None, None
+
+    # ------------------------------------------------------------------ Ulysses x ring
+    def _ring_peers(self, u: int) -> Tuple[int, int]:
+        """(destination, source) inside the CP group: send to ``(r-U) % P``, receive from ``(r+U) % P``."""
+        r = self.local_chunk_id
+        return (r - u) % self.cp_size, (r + u) % self.cp_size
+
+    def _post_ring_exchange(self, k, v, u, side):
+        """Post the K/V rotation; returns ``(next_k, next_v, done)``, ``done()`` makes them usable."""
+        dst, src = self._ring_peers(u)
+        k, v = k.contiguous(), v.contiguous()
+        nk, nv = torch.empty_like(k), torch.empty_like(v)
+        g = self.group
+        if side is not None:
+            side.wait_stream(torch.cuda.current_stream(k.device))
+            with torch.cuda.stream(side):
+                g.p2p_isend(k, dst)
+                g.p2p_irecv(None, None, src, out=nk)
+                g.p2p_isend(v, dst)
+                g.p2p_irecv(None, None, src, out=nv)
+                g.p2p_commit()
+                g.p2p_wait()
+            for t in (k, v, nk, nv):
+                t.record_stream(side)
+
+            def done():
+                torch.cuda.current_stream(k.device).wait_stream(side)
+        else:
+            g.p2p_isend(k, dst)
+            g.p2p_irecv(None, None, src, out=nk)
+            g.p2p_isend(v, dst)
+            g.p2p_irecv(None, None, src, out=nv)
+            g.p2p_commit()
+
+            def done():
+                g.p2p_wait()
+        return nk, nv, done
+
+    def _cp_forward(self, q, k, v, u: int, r: int, kw: dict) -> torch.Tensor:
+        up_group = self._up_group_lookup(u) if u > 1 else None
+        if up_group is not None:
+            q = up_group.all_to_all(q, 2, 1)
+            k = up_group.all_to_all(k, 2, 1)
+            v = up_group.all_to_all(v, 2, 1)
+        if r == 1:
+            out = self.attn(q, k, v, return_attn_probs=False, **kw)[0]
+        else:
+            side = self._side_stream(q.device)
+            merger = self._merger_factory()
+            for step in range(r):
+                pending = None
+                if step + 1 != r:
+                    pending = self._post_ring_exchange(k, v, u, side)
+                block_out, block_lse, _ = self.attn(q, k, v, return_attn_probs=True, **kw)
+                merger.add(block_out, block_lse)
+                if pending is not None:
+                    k, v, done = pending
+                    done()
+            out = merger.result()  # fp32, like the reference's merged result
+        if up_group is not None:
+            out = up_group.all_to_all(out, 1, 2)
+        return out
+
+    # ------------------------------------------------------------------ producer-callback form
+    @torch.compiler.disable
+    def attention_fused(self, *, produce_q, produce_k, produce_v, dropout_p: float = 0.0,
+                        softmax_scale: Optional[float] = None, causal: bool = False,
+                        window_size: Tuple[int, int] = (-1, -1), deterministic: bool = False,
+                        return_attn_probs: bool = False, num_heads: Optional[int] = None):
+        """Pure-Ulysses schedule with projection/exchange overlap.
+
+        Same contract as diffusion_attn_backend.py:638-737: the three callables each return a
+        contiguous ``[B,s,H,D]`` tensor; K's exchange runs on the side stream while V is produced,
+        V's while Q is produced.
+        """
+        if not self.supports_fused_overlap(return_attn_probs=return_attn_probs, num_heads=num_heads):
+            q, k, v = produce_q(), produce_k(), produce_v()
+            return self(q, k, v, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+                        window_size=window_size, deterministic=deterministic, return_attn_probs=return_attn_probs)
+        u, _ = self._split()
+        up_group = self._up_group_lookup(u)
+        kw = dict(dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal, window_size=window_size,
+                  deterministic=deterministic)
+        k = produce_k()
+        side = self._side_stream(k.device)
+        cur = torch.cuda.current_stream(k.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            k_x = up_group.all_to_all(k, 2, 1)
+        k.record_stream(side)
+        v = produce_v()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            v_x = up_group.all_to_all(v, 2, 1)
+        v.record_stream(side)
+        q = produce_q()
+        q_x = up_group.all_to_all(q, 2, 1)
+        cur.wait_stream(side)
+        for t in (k_x, v_x):
+            t.record_stream(cur)
+        out = self.attn(q_x, k_x, v_x, return_attn_probs=False, **kw)[0]
+        return up_group.all_to_all(out, 1, 2), None, None
+
+    # ------------------------------------------------------------------ replicated text + sharded image
+    @torch.compiler.disable
+    def cp_attn_with_full_txt(self, txt_q, txt_k, txt_v, img_q, img_k, img_v, *, image_seq_len: Optional[int] = None,
+                              dropout_p: float = 0.0, softmax_scale: Optional[float] = None, causal: bool = False,
+                              window_size: Tuple[int, int] = (-1, -1), deterministic: bool = False):
+        """Qwen-Image layout: text replicated on every rank, image tokens sharded.
+
+        Same contract as diffusion_attn_backend.py:839-984; returns ``(text output for all heads,
+        local image output)``.  ``image_seq_len`` is the unpadded image length: keys past it are
+        dropped, never attended.
+        """
+        if causal:
+            raise NotImplementedError("Qwen full-text CP attention only supports non-causal attention.")
+        kw = dict(dropout_p=dropout_p, softmax_scale=softmax_scale, causal=False, window_size=window_size,
+                  deterministic=deterministic)
+        txt_len = txt_q.shape[1]
+        if self.cp_size <= 1:
+            out = self.attn(torch.cat([txt_q, img_q], 1), torch.cat([txt_k, img_k], 1), torch.cat([txt_v, img_v], 1),
+                            return_attn_probs=False, **kw)[0]
+            return out[:, :txt_len], out[:, txt_len:]
+        if self.uses_agcp():
+            n_img = int(image_seq_len if image_seq_len is not None else img_k.shape[1] * self.cp_size)
+            k_img = self.group.all_gather_sequence(img_k)[:, :n_img]
+            v_img = self.group.all_gather_sequence(img_v)[:, :n_img]
+            out = self.attn(torch.cat([txt_q, img_q], 1), torch.cat([txt_k, k_img], 1), torch.cat([txt_v, v_img], 1),
+                            return_attn_probs=False, **kw)[0]
+            return out[:, :txt_len], out[:, txt_len:]
+
+        u, r = self._split()
+        if r > 1 and getattr(self.attn, "impl", "") in {"sage", "sparge", "torch_sdpa_math", "b200_q8"}:
+            raise NotImplementedError(f"{self.attn.impl} cannot provide LSE for Qwen full-text ring attention.")
+        up_group = None
+        if u > 1:
+            up_group = self._up_group_lookup(u)
+            ur = up_group.rank_in_group
+            txt_q, txt_k, txt_v = (torch.tensor_split(t, u, 2)[ur].contiguous() for t in (txt_q, txt_k, txt_v))
+            img_q = up_group.all_to_all(img_q, 2, 1)
+            img_k = up_group.all_to_all(img_k, 2, 1)
+            img_v = up_group.all_to_all(img_v, 2, 1)
+        n_img = int(image_seq_len if image_seq_len is not None else img_k.shape[1] * self.cp_size)
+        local0 = img_q.shape[1] // u if u > 1 else img_q.shape[1]
+        block_seq = img_k.shape[1]
+        local_img_len = img_q.shape[1]
+        q = torch.cat([txt_q, img_q], dim=1)
+        side = self._side_stream(q.device)
+        merger = self._merger_factory() if r > 1 else None
+        out = None
+        cur_k, cur_v = img_k, img_v
+        ring_block = self.local_chunk_id // u
+        for step in range(r):
+            owner = (ring_block + step) % r
+            valid = max(0, min(cur_k.shape[1], n_img - owner * block_seq))
+            pending = None
+            if step + 1 != r:
+                pending = self._post_ring_exchange(cur_k, cur_v, u, side)
+            if step == 0:
+                bk = torch.cat([txt_k, cur_k[:, :valid]], dim=1)
+                bv = torch.cat([txt_v, cur_v[:, :valid]], dim=1)
+            else:
+                bk, bv = cur_k[:, :valid], cur_v[:, :valid]
+            if bk.shape[1] > 0:
+                bo, bl, _ = self.attn(q, bk, bv, return_attn_probs=r > 1, **kw)
+                if r == 1:
+                    out = bo
+                else:
+                    merger.add(bo, bl)
+            if pending is not None:
+                cur_k, cur_v, done = pending
+                done()
+        if merger is not None:
+            out = merger.result()
+        if out is None:
+            raise RuntimeError("Qwen full-text CP attention produced no output blocks.")
+        txt_out = out[:, :txt_len]
+        img_out = out[:, txt_len : txt_len + local_img_len]
+        if up_group is not None:
+            img_out = up_group.all_to_all(img_out.contiguous(), 1, 2)[:, :local0]
+            txt_c = txt_out.contiguous()
+            gathered = torch.empty((u * txt_c.shape[0],) + tuple(txt_c.shape[1:]), dtype=txt_c.dtype,
+                                   device=txt_c.device)
+            dist.all_gather_into_tensor(gathered, txt_c, group=up_group.gpu_group)
+            gathered = gathered.view((u,) + tuple(txt_c.shape))
+            txt_out = gathered.permute(1, 2, 0, 3, 4).reshape(txt_c.shape[0], txt_c.shape[1], -1, txt_c.shape[3])
+        return txt_out, img_out
+
+    @torch.compiler.disable
+    def cp_attn_with_full_txt_fused(self, *, produce_txt_q, produce_txt_k, produce_txt_v, produce_img_q,
+                                    produce_img_k, produce_img_v, image_seq_len: Optional[int] = None,
+                                    dropout_p: float = 0.0, softmax_scale: Optional[float] = None,
+                                    causal: bool = False, window_size: Tuple[int, int] = (-1, -1),
+                                    deterministic: bool = False, num_heads: Optional[int] = None):
+        """Producer-callback form of :meth:`cp_attn_with_full_txt` (diffusion_attn_backend.py:987-1065)."""
+        return self.cp_attn_with_full_txt(
+            produce_txt_q(), produce_txt_k(), produce_txt_v(), produce_img_q(), produce_img_k(), produce_img_v(),
+            image_seq_len=image_seq_len, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+            window_size=window_size, deterministic=deterministic,
+        )
+
+
+# The name models and adapters of the reference import.
+DiffusionAttention_with_CP = B200ContextParallel

@@ -1,0 +1,109 @@
+"""Worker for the multi-process context-parallel tests (launched by tests/test_cp_gloo.py).
+
+Each rank builds the same seeded global problem, shards it the way the runtime does, runs the
+context-parallel wrapper over gloo with an oracle-backed attention callable (the CUDA backend is
+not needed to check rank maps, chunk order, valid-length handling and merge order), and compares
+its local result with single-process attention over the full sequence.
+"""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402
+from chitudiffusion_b200 import comm  # noqa: E402
+from chitudiffusion_b200.context_parallel import B200ContextParallel  # noqa: E402
+
+
+class OracleBackend:
+    """Duck-typed backend: ``impl`` attribute + ``(q,k,v,...) -> (out, lse, None)``."""
+
+    impl = "torch_sdpa"
+
+    def __call__(self, q, k, v, *_, softmax_scale=None, return_attn_probs=False, **__):
+        out, lse = oracle.sdpa_fp32(q, k, v, softmax_scale, return_lse=True)
+        return out, (lse if return_attn_probs else None), None
+
+
+class OracleMerger:
+    def __init__(self):
+        self.out, self.lse = None, None
+
+    def add(self, block_out, block_lse):
+        self.out, self.lse = oracle.update_out_and_lse(self.out, self.lse, block_out, block_lse)
+
+    def result(self):
+        return self.out
+
+
+def main():
+    cfg_size, up, cp_backend, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cp_size = world // cfg_size
+    comm.initialize_diffusion_parallel_groups(cfg_size, cp_size, up)
+    group = comm.get_cp_group()
+    assert group.rank_list == oracle.cp_rank_lists(world, cfg_size)[rank // cp_size if cfg_size == 2 else 0]
+    assert comm.get_cfg_group().rank_list in oracle.cfg_rank_lists(world, cfg_size)
+    wrapper = B200ContextParallel(OracleBackend(), up, cp_backend=cp_backend, merger_factory=OracleMerger)
+    r = group.rank_in_group
+    # each CP group (cond / uncond under CFG parallelism) works on its own seeded problem
+    gen = torch.Generator().manual_seed(100 + group.rank_list[0])
+    B, H, D = (2 if mode == "batch2" else 1), 8, 16
+    s = 6
+    ok = True
+    if mode in ("plain", "batch2"):
+        S = s * cp_size
+        q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))
+        full = oracle.sdpa_fp32(q, k, v)
+        sl = slice(r * s, (r + 1) * s)
+        out, lse, probs = wrapper(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous())
+        assert lse is None and probs is None
+        err = (out.float() - full[:, sl]).abs().max().item()
+        ok = err < 2e-6 and tuple(out.shape) == (B, s, H, D)
+        # the single-process layout simulator agrees too
+        sim = (oracle.simulate_agcp if cp_backend == "agcp" else
+               (lambda a, b, c: oracle.simulate_ucp(a, b, c, up)))(
+            [q[:, i * s:(i + 1) * s] for i in range(cp_size)], [k[:, i * s:(i + 1) * s] for i in range(cp_size)],
+            [v[:, i * s:(i + 1) * s] for i in range(cp_size)])
+        err2 = (out.float() - sim[r].float()).abs().max().item()
+        ok = ok and err2 < 2e-6
+        print(f"rank {rank} mode {mode} err {err:.2e} sim {err2:.2e}", flush=True)
+    elif mode == "fulltxt":
+        n_img = s * cp_size - 3  # not divisible: zero-padded tail that must never be attended
+        txt_len = 5
+        tq, tk, tv = (torch.randn(1, txt_len, H, D, generator=gen) for _ in range(3))
+        iq, ik, iv = (torch.randn(1, n_img, H, D, generator=gen) for _ in range(3))
+        full = oracle.sdpa_fp32(torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1))
+        shards = [oracle.split_sequence_padding(t, cp_size, 1) for t in (iq, ik, iv)]
+        t_out, i_out = wrapper.cp_attn_with_full_txt(tq, tk, tv, shards[0][r], shards[1][r], shards[2][r],
+                                                     image_seq_len=n_img)
+        ls = shards[0][r].shape[1]  # padded shard length
+        assert tuple(t_out.shape) == (1, txt_len, H, D) and tuple(i_out.shape) == (1, ls, H, D)
+        err_t = (t_out.float() - full[:, :txt_len]).abs().max().item()
+        valid = max(0, min(ls, n_img - r * ls))
+        err_i = (i_out[:, :valid].float() - full[:, txt_len + r * ls: txt_len + r * ls + valid]).abs().max().item()
+        ok = err_t < 2e-6 and err_i < 2e-6
+        print(f"rank {rank} fulltxt err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
+    elif mode == "fused":
+        S = s * cp_size
+        q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))
+        full = oracle.sdpa_fp32(q, k, v)
+        sl = slice(r * s, (r + 1) * s)
+        out = wrapper.attention_fused(produce_q=lambda: q[:, sl].contiguous(), produce_k=lambda: k[:, sl].contiguous(),
+                                      produce_v=lambda: v[:, sl].contiguous(), num_heads=H)[0]
+        err = (out.float() - full[:, sl]).abs().max().item()
+        ok = err < 2e-6
+    flag = torch.tensor([1 if ok else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
