@@ -1,0 +1,435 @@
+"""Benchmark of the attention hot path: pre-attention norm+rotary, attention kernel, CP exchange.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A "step" is the attention work of ONE denoising step of the named DiT: for every transformer
+block, the QK-RMSNorm + rotary pre-pass on that block's q/k projections followed by the attention
+kernel (and, on N > 1 GPUs, the context-parallel exchanges around it).  The default workload is the
+Flux1-dev 1024x1024 joint attention (4096 image + 512 text tokens, 24 heads of 128, 19 double +
+38 single blocks = 57 attention calls per step).  Inputs are seeded synthetic projection outputs.
+Rank 0 prints one JSON line.
+
+`value`   device-resident throughput: algorithmic attention FLOPs (4*S^2*D*H per block) of all
+          ranks / max-over-ranks device time, inputs already in HBM.
+`e2e`     the same step driven from pinned HOST buffers through the public backend API: two
+          input sets copied host->device and the last block's output copied device->host inside
+          the timed region.
+With --impl reference the CPU restatement of the reference's torch-SDPA path (oracle/) is timed on
+the host cores instead, one block per step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # BASELINE config 2: Flux1-dev joint attention, 1024x1024
+    "flux1-dev-1024-joint-attn": dict(kind="joint", s_img=4096, s_txt=512, img_hw=(64, 64), H=24, D=128, blocks=57,
+                                      axes=(16, 56, 56)),
+    # BASELINE config 1: one Wan2.1-1.3B self-attention layer at 480p x 17 frames
+    "wan1.3b-480p-17f-layer": dict(kind="wan", grid=(5, 30, 52), H=12, D=128, blocks=1),
+    # BASELINE config 3 / 4: Wan2.1 1.3B 480p x 81 frames, Wan2.1 14B 720p x 81 frames
+    "wan1.3b-480p-81f": dict(kind="wan", grid=(21, 30, 52), H=12, D=128, blocks=30),
+    "wan14b-720p-81f": dict(kind="wan", grid=(21, 45, 80), H=40, D=128, blocks=40),
+}
+DEFAULT_WORKLOAD = "flux1-dev-1024-joint-attn"
+INPUT_SETS = 4  # distinct q/k/v projection sets cycled over the blocks: 4 x 85 MB > the 126 MB L2
+
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+# DRAM bytes per attention launch of the default workload, from the ncu capture summarised in
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured for a workload.
+NCU_TRAFFIC_BYTES = {"flux1-dev-1024-joint-attn": None}
+
+
+def seq_len(w):
+    if w["kind"] == "joint":
+        return w["s_img"] + w["s_txt"]
+    g = w["grid"]
+    return g[0] * g[1] * g[2]
+
+
+def flops_per_block(w):
+    S = seq_len(w)
+    return 4.0 * S * S * w["D"] * w["H"]
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------- #
+# clocks sampled during the timed region
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, smax, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+# synthetic inputs
+# --------------------------------------------------------------------------- #
+def local_positions(w, rank, world):
+    """Global token indices owned by this rank (contiguous shards; joint: text shard then image shard)."""
+    if w["kind"] == "joint":
+        st, si = w["s_txt"] // world, w["s_img"] // world
+        txt = torch.arange(rank * st, (rank + 1) * st)
+        img = w["s_txt"] + torch.arange(rank * si, (rank + 1) * si)
+        return torch.cat([txt, img])
+    s = seq_len(w) // world
+    return torch.arange(rank * s, (rank + 1) * s)
+
+
+def joint_ids(w):
+    """Flux position ids: text tokens all zero, image tokens (0, row, col)."""
+    hh, ww = w["img_hw"]
+    ids = torch.zeros(seq_len(w), 3, dtype=torch.long)
+    n = torch.arange(w["s_img"])
+    ids[w["s_txt"]:, 1] = n // ww
+    ids[w["s_txt"]:, 2] = n % ww
+    return ids
+
+
+def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
+    """Seeded q/k/v projection outputs [1, s_local, H*D] bf16 (the same global tensors on every rank)."""
+    S, C = seq_len(w), w["H"] * w["D"]
+    pos = local_positions(w, rank, world)
+    sets = []
+    for i in range(n_sets):
+        gen = torch.Generator().manual_seed(seed * 1000 + i)
+        trip = []
+        for _ in range(3):
+            full = torch.randn(1, S, C, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+            t = full[:, pos].contiguous()
+            if pinned:
+                t = t.pin_memory()
+            elif device is not None:
+                t = t.to(device)
+            trip.append(t)
+        sets.append(tuple(trip))
+    return sets
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+class Pipeline:
+    """Per-rank block function: pre-attention pass + (context-parallel) attention."""
+
+    def __init__(self, w, rank, world, device):
+        from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
+        from chitudiffusion_b200.context_parallel import B200ContextParallel
+
+        self.w, self.rank, self.world, self.device = w, rank, world, device
+        self.H, self.D = w["H"], w["D"]
+        self.backend = B200AttnBackend("b200")
+        self.attn = self.backend
+        if world > 1:
+            up = max(u for u in (8, 4, 2, 1) if u <= world and self.H % u == 0 and world % u == 0)
+            comm.initialize_diffusion_parallel_groups(1, world, up)
+            self.attn = B200ContextParallel(self.backend, up, cp_backend="ucp")
+            self.parallelism = f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else "")
+        else:
+            self.parallelism = "single"
+        if w["kind"] == "joint":
+            table = pre_attention.axis_rope_table(joint_ids(w), w["axes"])[local_positions(w, rank, world)]
+            self.pre = pre_attention.JointPreAttention(self.H, self.D, table.contiguous().to(device))
+            self.nq = torch.ones(self.D, device=device)
+            self.nk = torch.ones(self.D, device=device)
+        else:
+            self.pre = pre_attention.WanPreAttention(self.H, self.D, cp_size=world, cp_rank=rank, device=device)
+            self.nq = torch.ones(self.H * self.D, device=device)
+            self.nk = torch.ones(self.H * self.D, device=device)
+        self.launches = 0
+        self.attn_events = []
+
+    def block(self, qp, kp, vp, timed=False):
+        if self.w["kind"] == "joint":
+            q, k, v = self.pre(qp, kp, vp, self.nq, self.nk)
+        else:
+            q, k, v = self.pre(qp, kp, vp, self.nq, self.nk, self.w["grid"])
+        self.launches += 2
+        if timed and self.world == 1:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = self.attn(q, k, v)[0]
+            e1.record()
+            self.attn_events.append((e0, e1))
+        else:
+            out = self.attn(q, k, v)[0]
+        self.launches += 1
+        return out
+
+    def step(self, sets, timed=False):
+        out = None
+        for b in range(self.w["blocks"]):
+            qp, kp, vp = sets[b % len(sets)]
+            out = self.block(qp, kp, vp, timed)
+        return out
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+    w = WORKLOADS[args.workload]
+    if seq_len(w) % world or (w["kind"] == "joint" and (w["s_txt"] % world or w["s_img"] % world)):
+        raise ValueError("sequence not divisible by the number of GPUs")
+    pipe = Pipeline(w, rank, world, device)
+    dev_sets = make_inputs(w, rank, world, seed=1, n_sets=INPUT_SETS, device=device)
+    host_sets = make_inputs(w, rank, world, seed=1, n_sets=2, device=None, pinned=True)
+    e2e_dev = [tuple(torch.empty_like(t, device=device) for t in trip) for trip in host_sets]
+    s_local = dev_sets[0][0].shape[1]
+    out_host = torch.empty((1, s_local, w["H"], w["D"]), dtype=torch.bfloat16).pin_memory()
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed_region(fn, steps):
+        sync()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        sync()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def e2e_step():
+        for trip_h, trip_d in zip(host_sets, e2e_dev):
+            for h, d in zip(trip_h, trip_d):
+                d.copy_(h, non_blocking=True)
+        out = pipe.step(e2e_dev)
+        out_host.copy_(out.view(out_host.shape) if out.dtype == out_host.dtype else out.to(torch.bfloat16),
+                       non_blocking=True)
+
+    for _ in range(args.warmup):
+        pipe.step(dev_sets)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    pipe.launches = 0
+    pipe.attn_events = []
+    total_ms = timed_region(lambda: pipe.step(dev_sets, timed=True), args.steps)
+    launches = pipe.launches
+    clocks = sampler.stop() if rank == 0 else None
+    attn_ms = [a.elapsed_time(b) for a, b in pipe.attn_events]
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        e2e_step()
+    e2e_ms = timed_region(e2e_step, args.steps)
+
+    from chitudiffusion_b200 import ops
+
+    ops.check_status(device)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks, peak_kind = load_peaks()
+    flops_step = flops_per_block(w) * w["blocks"]
+    ms_per_step = total_ms / args.steps
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+    e2e_value = flops_step / (e2e_ms / args.steps * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for trip in host_sets for t in trip)
+    d2h = out_host.numel() * out_host.element_size()
+    roof = None
+    if attn_ms:
+        avg_ms = sum(attn_ms) / len(attn_ms)
+        achieved = flops_per_block(w) / (avg_ms * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        roof = {
+            "bound": "tensor", "kernel": "attn_fwd_kernel", "achieved": round(achieved, 2), "peak": peak,
+            "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+            "peak_source": f"{peak_kind} bf16_tflops_sustained (kernel timed inside a long back-to-back loop)",
+            "frac_of_burst": round(achieved / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), 4),
+            "frac_of_nominal_2250": round(achieved / 2250.0, 4),
+            "avg_launch_ms": round(avg_ms, 5), "launches_timed": len(attn_ms),
+            "algorithmic_flops_per_launch": flops_per_block(w),
+        }
+    line = {
+        "metric": "attention_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": args.workload, "seq_len": seq_len(w), "heads": w["H"], "head_dim": w["D"],
+            "attention_calls_per_step": w["blocks"], "parallelism": pipe.parallelism, "batch": 1,
+            "l2_hygiene": f"{INPUT_SETS} distinct input sets ({INPUT_SETS * 3 * seq_len(w) * w['H'] * w['D'] * 2 // world >> 20} MiB per GPU) cycled over blocks: larger than the 126 MB L2",
+        },
+        "per_gpu_tflops": round(value / world, 2),
+        "attention_step_latency_ms": round(ms_per_step, 4),
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(e2e_ms / args.steps, 4)},
+        "gpu_launches": launches,
+        "roofline": roof,
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(w, repeats=3)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- #
+# CPU arm: the oracle's restatement of the reference torch-SDPA path on host cores
+# --------------------------------------------------------------------------- #
+def cpu_block_fn(w):
+    """Returns (fn, flops): one block of the workload through the CPU oracle (fp32)."""
+    import oracle
+
+    S, H, D = seq_len(w), w["H"], w["D"]
+    gen = torch.Generator().manual_seed(1000)
+    qp, kp, vp = (torch.randn(1, S, H * D, generator=gen) for _ in range(3))
+    if w["kind"] == "joint":
+        cos, sin = oracle.axis_rope_table(joint_ids(w), w["axes"])
+
+        def fn():
+            q = oracle.apply_rope_interleaved(oracle.per_head_rms_norm(qp.view(1, S, H, D), None), cos, sin)
+            k = oracle.apply_rope_interleaved(oracle.per_head_rms_norm(kp.view(1, S, H, D), None), cos, sin)
+            return oracle.sdpa_reference_call(q, k, vp.view(1, S, H, D))
+    else:
+        freqs = oracle.wan_rope_table(D)
+        ones = torch.ones(H * D)
+
+        def fn():
+            q, k, v = oracle.wan_self_attention_pre(qp, kp, vp, ones, ones, H, [list(w["grid"])], freqs,
+                                                    round_bf16=False)
+            return oracle.sdpa_reference_call(q, k, v)
+    return fn, flops_per_block(w)
+
+
+def cpu_baseline(w, repeats=3):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    fn, flops = cpu_block_fn(w)
+    fn()
+    best = math.inf
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+    return {"value": round(flops / best / 1e12, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"one attention block of the workload (norm + rotary + fp32 SDPA), best of {repeats}: {best:.3f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    fn, flops = cpu_block_fn(w)
+    for _ in range(args.warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = round(flops / dt / 1e12, 4)
+    sample = "each step = one attention block of the workload (norm + rotary + fp32 SDPA) through the CPU oracle"
+    line = {
+        "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "seq_len": seq_len(w), "heads": w["H"], "head_dim": w["D"],
+                   "attention_calls_per_step": 1, "parallelism": f"cpu-threads{cores}", "batch": 1},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -19,6 +19,7 @@ unpinned.
 
 from .reference_math import (  # noqa: F401
     sdpa_fp32,
+    sdpa_reference_call,
     wan_rms_norm,
     wan_rope_params,
     wan_rope_table,

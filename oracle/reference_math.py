@@ -66,6 +66,22 @@ def sdpa_fp32(
     return out
 
 
+def sdpa_reference_call(q, k, v, softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """The exact library call the reference's torch-SDPA backend makes, on CPU tensors.
+
+    Follows chitu_diffusion/modules/attention/diffusion_attn_backend.py:283-285,305-315:
+    ``[B,S,H,D]`` -> ``transpose(1, 2)`` views -> ``F.scaled_dot_product_attention(attn_mask=None,
+    dropout_p=0, is_causal=False, scale=softmax_scale)`` -> ``transpose(1, 2).contiguous()``.  This is
+    the form timed as the CPU baseline (torch's fused CPU kernel); :func:`sdpa_fp32` is the explicit
+    form that also yields the log-sum-exp.
+    """
+    out = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=None, dropout_p=0.0, is_causal=False,
+        scale=softmax_scale,
+    )
+    return out.transpose(1, 2).contiguous()
+
+
 # --------------------------------------------------------------------------- #
 # Wan pre-attention: full-width RMSNorm + 3-axis complex RoPE
 # --------------------------------------------------------------------------- #
