@@ -1,11 +1,13 @@
 // Dense non-causal attention forward for head_dim 128 on sm_100a.
 //
 // One CTA owns one (batch, head, 256-query-row block): two 128-row query tiles
-// that ping-pong on the tensor core.  Roles (320 threads):
+// that ping-pong on the tensor core.  Roles (384 threads):
 //   warps 0-3  softmax for query tile 0   (thread = one score row, no shuffles)
 //   warps 4-7  softmax for query tile 1
 //   warp  8    MMA issuer (one thread issues tcgen05.mma, accumulators in TMEM)
 //   warp  9    TMA producer (Q once, then K_j / V_j through a 5-slot ring)
+//   warps 10-11 idle (they complete the third warpgroup so that registers can be
+//              re-assigned per warpgroup: 48 for warps 8-11, 224 for the softmax warps)
 //
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  The
 // probabilities P are written back as packed 16-bit pairs over the first 64
@@ -29,7 +31,7 @@ constexpr int kQTiles = 2;    // query tiles per CTA
 constexpr int kStages = 5;    // K/V ring slots
 constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32 KiB
 constexpr int kHalfTileBytes = kTileBytes / 2;     // one 64-column swizzle panel
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;  // 8 softmax warps + MMA warp + TMA warp + 2 idle warps completing the warpgroup
 constexpr int kSmemBarrierBytes = 256;
 constexpr int kAttnSmemBytes = (kQTiles + kStages) * kTileBytes + kSmemBarrierBytes + 1024;  // +1024: manual alignment
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -41,6 +43,9 @@ struct AttnParams {
   int B, H, Sq, Sk;
   float scale_log2; // softmax_scale * log2(e)
   int is_fp16;      // 0 = bf16, 1 = fp16
+#ifdef CHITU_ATTN_TIMING
+  long long* dbg;   // per-phase clock totals of CTA 0 (development builds only)
+#endif
 };
 
 template <bool kFp16>
@@ -52,6 +57,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   }
   return r;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 template <bool kFp16>
@@ -113,6 +124,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Registers move from the warpgroup holding the two single-thread roles to the softmax warps.
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -224,8 +238,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       __syncwarp();
     }
+  }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int t = warp >> 2;
     if (t < n_qt) {
       const int quad = warp & 3;
@@ -238,32 +254,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float m_used = -INFINITY;
       float l_sum = 0.f;
 
+#ifdef CHITU_ATTN_TIMING
+      long long tw = 0, tl = 0, tm = 0, ts = 0, c0, c1;
+#define TICK(acc) c1 = clock64(); acc += c1 - c0; c0 = c1;
+#else
+#define TICK(acc)
+#endif
       for (int j = 0; j < n_kv; ++j) {
+#ifdef CHITU_ATTN_TIMING
+        c0 = clock64();
+#endif
         mbar_wait(bar_s_full + 8 * t, j & 1, abort_flag, p.status, kDevTimeoutSoftmax);
         tc_fence_after_sync();
+        TICK(tw)
+        // Row of 128 scores into registers, 32 columns per load; the load of chunk
+        // c+1 is in flight while the running maximum of chunk c is taken.
         uint32_t s[4][32];
+        const bool last_tile = (j == n_kv - 1 && tail_valid < kTileN);
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        tmem_ld32(t_s, s[0]);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, s[c]);
-        tmem_wait_ld();
-
-        if (j == n_kv - 1 && tail_valid < kTileN) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) {
+          tmem_wait_ld();
+          if (c < 3) tmem_ld32(t_s + (c + 1) * 32, s[c + 1]);
+          if (last_tile) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (c * 32 + i >= tail_valid) s[c][i] = 0xff800000u;  // -inf
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+            mx0 = max3(mx0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
           }
-        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        }
+        TICK(tl)
+        const float mx = fmaxf(mx0, mx1);
 
         if (j == 0) {
           m_used = mx;
@@ -285,26 +311,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
 
+        // p = 2^(s*scale - m*scale): packed two-wide FMA / add, one MUFU per element
+        const float2 sl2_2 = make_float2(sl2, sl2);
         const float neg_m = -m_used * sl2;
+        const float2 neg_m2 = make_float2(neg_m, neg_m);
         uint32_t pk[2][32];
-        float l0 = 0.f, l1 = 0.f;
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), sl2, neg_m));
-            const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), sl2, neg_m));
-            l0 += e0;
-            l1 += e1;
-            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack2<kFp16>(e0, e1);
+          for (int i = 0; i < 32; i += 4) {
+            float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sl2_2, neg_m2);
+            float2 x1 =
+                __ffma2_rn(make_float2(__uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3])), sl2_2, neg_m2);
+            x0.x = fast_exp2(x0.x);
+            x0.y = fast_exp2(x0.y);
+            x1.x = fast_exp2(x1.x);
+            x1.y = fast_exp2(x1.y);
+            la = __fadd2_rn(la, x0);
+            lb = __fadd2_rn(lb, x1);
+            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack2<kFp16>(x0.x, x0.y);
+            pk[c >> 1][(c & 1) * 16 + (i >> 1) + 1] = pack2<kFp16>(x1.x, x1.y);
           }
-        l_sum += l0 + l1;
+        l_sum += (la.x + la.y) + (lb.x + lb.y);
+        TICK(tm)
         tmem_st32(t_s, pk[0]);
         tmem_st32(t_s + 32, pk[1]);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar_p_full + 8 * t);
+        TICK(ts)
       }
+#ifdef CHITU_ATTN_TIMING
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
+        p.dbg[t * 4 + 0] = tw; p.dbg[t * 4 + 1] = tl; p.dbg[t * 4 + 2] = tm; p.dbg[t * 4 + 3] = ts;
+      }
+#endif
 
       // epilogue: O / l -> 16-bit, row-contiguous 256-byte stores; LSE in natural log
       mbar_wait(bar_o_final + 8 * t, 0, abort_flag, p.status, kDevTimeoutEpilogue);

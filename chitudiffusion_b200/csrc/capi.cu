@@ -85,6 +85,11 @@ int elem_size(int dtype) { return dtype == CHITU_DTYPE_FP32 ? 4 : 2; }
 
 }  // namespace
 
+#ifdef CHITU_ATTN_TIMING
+static long long* g_dbg = nullptr;
+extern "C" void chitu_b200_set_dbg(long long* ptr) { g_dbg = ptr; }
+#endif
+
 extern "C" {
 
 int chitu_b200_version(void) { return 100; }
@@ -125,6 +130,9 @@ int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, 
   p.Sk = Sk;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.is_fp16 = dtype == CHITU_DTYPE_FP16;
+#ifdef CHITU_ATTN_TIMING
+  p.dbg = g_dbg;
+#endif
 
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
