@@ -167,25 +167,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t kIdescQK = umma_idesc(1, kFp16 ? 0 : 1, kFp16 ? 0 : 1, 0, kTileM, kTileN);
     constexpr uint32_t kIdescPV = umma_idesc(1, kFp16 ? 0 : 1, kFp16 ? 0 : 1, 1, kTileM, kHeadDim);
+    // One elected thread issues every MMA and every commit.  Operand descriptors are built
+    // once; inside the loops only their start-address field moves.
+    const bool leader = elect_one();
+    const uint64_t q_desc0 = umma_smem_desc_sw128(q_smem, 16, 1024);
+    const uint64_t k_desc0 = umma_smem_desc_sw128(kv_smem, 16, 1024);
+    const uint64_t v_desc0 = umma_smem_desc_sw128(kv_smem, kHalfTileBytes, 1024);
     auto issue_qk = [&](int t, int slot) {
       // S_t = Q_t K^T : both operands K-major, 8 steps of 16 along head_dim
-      const uint32_t a0 = q_smem + t * kTileBytes;
-      const uint32_t b0 = kv_smem + slot * kTileBytes;
+      const uint64_t a0 = q_desc0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
+      const uint64_t b0 = k_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
+      const uint32_t d = tmem_base + t * kTileN;
 #pragma unroll
       for (int k = 0; k < kHeadDim / 16; ++k) {
-        const uint32_t off = (k >> 2) * kHalfTileBytes + (k & 3) * 32;
-        umma_ss_f16(tmem_base + t * kTileN, umma_smem_desc_sw128(a0 + off, 16, 1024),
-                    umma_smem_desc_sw128(b0 + off, 16, 1024), kIdescQK, k > 0);
+        const uint64_t off = static_cast<uint64_t>(((k >> 2) * kHalfTileBytes + (k & 3) * 32) >> 4);
+        umma_ss_f16(d, a0 + off, b0 + off, kIdescQK, k > 0);
       }
     };
     auto issue_pv = [&](int t, int slot, bool accumulate) {
       // O_t += P_t V : A = P from tensor memory (two 16-bit values per column),
       // B = V tile as loaded ([key][d], d contiguous => MN-major), 8 steps of 16 keys
-      const uint32_t b0 = kv_smem + slot * kTileBytes;
+      const uint64_t b0 = v_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
+      const uint32_t d = tmem_base + 2 * kTileN + t * kHeadDim;
+      const uint32_t a = tmem_base + t * kTileN;
+      const uint32_t acc0 = accumulate ? 1u : 0u;
 #pragma unroll
       for (int k = 0; k < kTileN / 16; ++k) {
-        umma_ts_f16(tmem_base + 2 * kTileN + t * kHeadDim, tmem_base + t * kTileN + k * 8,
-                    umma_smem_desc_sw128(b0 + k * 2048, kHalfTileBytes, 1024), kIdescPV, accumulate || k > 0);
+        umma_ts_f16(d, a + k * 8, b0 + static_cast<uint64_t>((k * 2048) >> 4), kIdescPV, k > 0 ? 1u : acc0);
       }
     };
     auto wait_item = [&](int i) {
@@ -195,7 +203,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_wait(bar_q_full, 0, abort_flag, p.status, kDevTimeoutMma);
     wait_item(0);
     tc_fence_after_sync();
-    if (lane == 0) {
+    if (leader) {
       issue_qk(0, 0);
       umma_commit(bar_s_full);
     }
@@ -203,13 +211,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (n_qt > 1) {
       mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kDevTimeoutMma);
       tc_fence_after_sync();
-      if (lane == 0) {
+      if (leader) {
         issue_qk(1, 0);
         umma_commit(bar_s_full + 8);
       }
       __syncwarp();
     }
-    if (lane == 0) umma_commit(bar_kv_empty);  // K_0 free once both QK^T have run
+    if (leader) umma_commit(bar_kv_empty);  // K_0 free once both QK^T have run
     __syncwarp();
 
     for (int j = 0; j < n_kv; ++j) {
@@ -221,7 +229,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int t = 0; t < n_qt; ++t) {
         mbar_wait(bar_p_full + 8 * t, j & 1, abort_flag, p.status, kDevTimeoutMma);
         tc_fence_after_sync();
-        if (lane == 0) {
+        if (leader) {
           issue_pv(t, iv % kStages, j > 0);
           if (more) {
             issue_qk(t, ik % kStages);
@@ -232,7 +240,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         __syncwarp();
       }
-      if (lane == 0) {
+      if (leader) {
         umma_commit(bar_kv_empty + 8 * (iv % kStages));
         if (more) umma_commit(bar_kv_empty + 8 * (ik % kStages));
       }
