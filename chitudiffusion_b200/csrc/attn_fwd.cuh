@@ -35,6 +35,10 @@ constexpr int kAttnThreads = 384;  // 8 softmax warps + MMA warp + TMA warp + 2 
 constexpr int kSmemBarrierBytes = 256;
 constexpr int kAttnSmemBytes = (kQTiles + kStages) * kTileBytes + kSmemBarrierBytes + 1024;  // +1024: manual alignment
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef CHITU_POLY_PAIRS
+#define CHITU_POLY_PAIRS 3
+#endif
+constexpr int kPolyPairs = CHITU_POLY_PAIRS;  // of every 8 score pairs, how many take the polynomial 2^x
 
 struct AttnParams {
   void* out;        // [B, Sq, H, 128] contiguous, 16-bit
@@ -65,6 +69,24 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// 2^x for a pair of values on the FMA pipe (no MUFU): split x = n + f with a round-down magic
+// add, evaluate a cubic minimax polynomial for 2^f on [0, 1) (max relative error 7.5e-5, far
+// below the 16-bit rounding of the probabilities) and add n to the exponent field.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23: x + kMagic rounded down holds floor(x) in its low mantissa bits
+  x.x = fmaxf(x.x, -126.f);  // keeps the exponent field non-negative (the polynomial can dip just below 1)
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rd(x, make_float2(kMagic, kMagic));
+  const float2 nf = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+  const float2 f = __fadd2_rn(x, make_float2(-nf.x, -nf.y));
+  float2 r = __ffma2_rn(make_float2(0.07802403f, 0.07802403f), f, make_float2(0.22606707f, 0.22606707f));
+  r = __ffma2_rn(r, f, make_float2(0.69583399f, 0.69583399f));
+  r = __ffma2_rn(r, f, make_float2(0.99992513f, 0.99992513f));
+  r.x = __uint_as_float(__float_as_uint(r.x) + (__float_as_uint(t.x) << 23));
+  r.y = __uint_as_float(__float_as_uint(r.y) + (__float_as_uint(t.y) << 23));
+  return r;
+}
+
 template <bool kFp16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -81,9 +103,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bar_kv_full = bar_base + 16;               // [kStages]
   const uint32_t bar_kv_empty = bar_kv_full + 8 * kStages;  // [kStages]
   const uint32_t bar_s_full = bar_kv_empty + 8 * kStages;   // [2]
-  const uint32_t bar_p_full = bar_s_full + 16;              // [2]
-  const uint32_t bar_o_final = bar_p_full + 16;             // [2]
-  uint8_t* tail = smem_gen + (kQTiles + kStages) * kTileBytes + (16 + 16 * kStages + 48);
+  const uint32_t bar_p_full = bar_s_full + 16;              // [2][2]  (tile, key half): P half stored
+  const uint32_t bar_o_final = bar_p_full + 32;             // [2]
+  uint8_t* tail = smem_gen + (kQTiles + kStages) * kTileBytes + (16 + 16 * kStages + 64);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
 
@@ -105,7 +127,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1);
-      mbar_init(bar_p_full + 8 * t, kTileM);
+      mbar_init(bar_p_full + 16 * t, kTileM);
+      mbar_init(bar_p_full + 16 * t + 8, kTileM);
       mbar_init(bar_o_final + 8 * t, 1);
     }
     mbar_fence_init();
@@ -184,15 +207,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_ss_f16(d, a0 + off, b0 + off, kIdescQK, k > 0);
       }
     };
-    auto issue_pv = [&](int t, int slot, bool accumulate) {
-      // O_t += P_t V : A = P from tensor memory (two 16-bit values per column),
-      // B = V tile as loaded ([key][d], d contiguous => MN-major), 8 steps of 16 keys
-      const uint64_t b0 = v_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
+    auto issue_pv_half = [&](int t, int slot, int h, bool accumulate) {
+      // O_t += P_t[:, 64h .. 64h+64) V[64h .. 64h+64) : A = P from tensor memory (two 16-bit values
+      // per column), B = V tile as loaded ([key][d], d contiguous => MN-major), 4 steps of 16 keys
+      const uint64_t b0 = v_desc0 + static_cast<uint64_t>((slot * kTileBytes + h * 8192) >> 4);
       const uint32_t d = tmem_base + 2 * kTileN + t * kHeadDim;
-      const uint32_t a = tmem_base + t * kTileN;
+      const uint32_t a = tmem_base + t * kTileN + h * 32;
       const uint32_t acc0 = accumulate ? 1u : 0u;
 #pragma unroll
-      for (int k = 0; k < kTileN / 16; ++k) {
+      for (int k = 0; k < 4; ++k) {
         umma_ts_f16(d, a + k * 8, b0 + static_cast<uint64_t>((k * 2048) >> 4), kIdescPV, k > 0 ? 1u : acc0);
       }
     };
@@ -227,10 +250,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (more) wait_item(ik);
       wait_item(iv);
       for (int t = 0; t < n_qt; ++t) {
-        mbar_wait(bar_p_full + 8 * t, j & 1, abort_flag, p.status, kDevTimeoutMma);
+        // the PV MMAs of the first 64 keys start while the softmax warps still work on the rest
+        mbar_wait(bar_p_full + 16 * t, j & 1, abort_flag, p.status, kDevTimeoutMma);
+        tc_fence_after_sync();
+        if (leader) issue_pv_half(t, iv % kStages, 0, j > 0);
+        __syncwarp();
+        mbar_wait(bar_p_full + 16 * t + 8, j & 1, abort_flag, p.status, kDevTimeoutMma);
         tc_fence_after_sync();
         if (leader) {
-          issue_pv(t, iv % kStages, j > 0);
+          issue_pv_half(t, iv % kStages, 1, true);
           if (more) {
             issue_qk(t, ik % kStages);
             umma_commit(bar_s_full + 8 * t);
@@ -240,9 +268,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         __syncwarp();
       }
-      if (leader) {
+      // the last step releases nothing: its o_final commits stay the CTA's final barrier arrivals
+      if (leader && more) {
         umma_commit(bar_kv_empty + 8 * (iv % kStages));
-        if (more) umma_commit(bar_kv_empty + 8 * (ik % kStages));
+        umma_commit(bar_kv_empty + 8 * (ik % kStages));
       }
       __syncwarp();
     }
@@ -332,23 +361,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sl2_2, neg_m2);
             float2 x1 =
                 __ffma2_rn(make_float2(__uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3])), sl2_2, neg_m2);
-            x0.x = fast_exp2(x0.x);
-            x0.y = fast_exp2(x0.y);
-            x1.x = fast_exp2(x1.x);
-            x1.y = fast_exp2(x1.y);
+            // kPolyPairs of every 8 pairs take the FMA-pipe polynomial, the rest the MUFU unit, so
+            // that both pipes stay busy (this iteration handles pairs 2g and 2g+1, g = i / 4)
+            constexpr int kPolyOdd = kPolyPairs < 4 ? kPolyPairs : 4;
+            constexpr int kPolyEven = kPolyPairs > 4 ? kPolyPairs - 4 : 0;
+            if (((i >> 2) & 3) < kPolyEven) {
+              x0 = exp2_poly2(x0);
+            } else {
+              x0.x = fast_exp2(x0.x);
+              x0.y = fast_exp2(x0.y);
+            }
+            if (((i >> 2) & 3) < kPolyOdd) {
+              x1 = exp2_poly2(x1);
+            } else {
+              x1.x = fast_exp2(x1.x);
+              x1.y = fast_exp2(x1.y);
+            }
             la = __fadd2_rn(la, x0);
             lb = __fadd2_rn(lb, x1);
             pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack2<kFp16>(x0.x, x0.y);
             pk[c >> 1][(c & 1) * 16 + (i >> 1) + 1] = pack2<kFp16>(x1.x, x1.y);
+            if ((c & 1) == 1 && i == 28) {
+              // 64 probabilities done: hand this half to the MMA warp
+              TICK(tm)
+              tmem_st32(t_s + (c >> 1) * 32, pk[c >> 1]);
+              tmem_wait_st();
+              tc_fence_before_sync();
+              mbar_arrive(bar_p_full + 16 * t + 8 * (c >> 1));
+              TICK(ts)
+            }
           }
         l_sum += (la.x + la.y) + (lb.x + lb.y);
-        TICK(tm)
-        tmem_st32(t_s, pk[0]);
-        tmem_st32(t_s + 32, pk[1]);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(bar_p_full + 8 * t);
-        TICK(ts)
       }
 #ifdef CHITU_ATTN_TIMING
       if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
