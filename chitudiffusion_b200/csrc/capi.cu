@@ -184,8 +184,8 @@ int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, c
   if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: bad shape");
   if (D & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: head_dim must be a multiple of 8");
   const long long C = static_cast<long long>(H) * D;
-  if (C > chitu::kNormThreads * 8 * chitu::kNormMaxVec)
-    return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: at most %d channels per token", chitu::kNormThreads * 8 * chitu::kNormMaxVec);
+  if (C > chitu::kNormMaxThreads * 8)
+    return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: at most %d channels per token", chitu::kNormMaxThreads * 8);
   if (in_dtype < 0 || in_dtype > 2 || (out_dtype != CHITU_DTYPE_BF16 && out_dtype != CHITU_DTYPE_FP16))
     return fail(CHITU_E_INVALID, "qk_norm_rope: bad dtype");
   if (weight && w_dtype != CHITU_DTYPE_BF16 && w_dtype != CHITU_DTYPE_FP32 && w_dtype != CHITU_DTYPE_FP16)
@@ -245,7 +245,32 @@ int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, c
   p.round_mid = round_mid;
   const long long tokens = static_cast<long long>(B) * S;
   if (tokens > 2147483647LL) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: too many tokens");
-  chitu::qk_norm_rope_kernel<<<static_cast<unsigned>(tokens), chitu::kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  // one 8-channel vector per thread, whole warps; the grid fills the 148 SMs a few CTAs deep
+  const int threads = static_cast<int>(((C / 8) + 31) / 32 * 32);
+  const int per_sm = threads <= 256 ? 8 : (threads <= 512 ? 4 : 2);
+  const unsigned grid = static_cast<unsigned>(tokens < 148LL * per_sm ? tokens : 148LL * per_sm);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define CHITU_NR_LAUNCH(IN, NM, RM) chitu::qk_norm_rope_kernel<IN, NM, RM><<<grid, threads, 0, st>>>(p)
+#define CHITU_NR_ROPE(IN, NM)                     \
+  switch (rope_mode) {                            \
+    case 0: CHITU_NR_LAUNCH(IN, NM, 0); break;    \
+    case 1: CHITU_NR_LAUNCH(IN, NM, 1); break;    \
+    default: CHITU_NR_LAUNCH(IN, NM, 2); break;   \
+  }
+#define CHITU_NR_NORM(IN)                         \
+  switch (norm_mode) {                            \
+    case 0: CHITU_NR_ROPE(IN, 0); break;          \
+    case 1: CHITU_NR_ROPE(IN, 1); break;          \
+    default: CHITU_NR_ROPE(IN, 2); break;         \
+  }
+  switch (in_dtype) {
+    case CHITU_DTYPE_BF16: CHITU_NR_NORM(0); break;
+    case CHITU_DTYPE_FP16: CHITU_NR_NORM(1); break;
+    default: CHITU_NR_NORM(2); break;
+  }
+#undef CHITU_NR_NORM
+#undef CHITU_NR_ROPE
+#undef CHITU_NR_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "qk_norm_rope: launch");
   return CHITU_OK;

@@ -126,124 +126,129 @@ struct NormRopeParams {
   int round_mid;
 };
 
-constexpr int kNormThreads = 256;
-constexpr int kNormMaxVec = 4;  // up to 256 * 8 * 4 = 8192 channels per token
+constexpr int kNormMaxThreads = 1024;  // one 8-channel vector per thread: up to 8192 channels per token
 
-__global__ void __launch_bounds__(kNormThreads) qk_norm_rope_kernel(const NormRopeParams p) {
-  __shared__ float red[kNormThreads / 32];
+// 8 consecutive input elements of a token row as floats (16-byte loads)
+template <int kInDtype>
+__device__ __forceinline__ void ld8(const void* p, size_t i, float (&v)[8]) {
+  const float4 a = ld4(p, kInDtype, i);
+  const float4 c = ld4(p, kInDtype, i + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+}
+
+// Persistent kernel: thread i of the CTA owns channels [8i, 8i+8) of every token the CTA
+// visits, so the norm weights live in registers; the next token's vector is loaded before the
+// current one is transformed.  Full-width statistics need one block reduction per token,
+// per-head statistics only warp shuffles.
+template <int kInDtype, int kNormMode, int kRopeMode>
+__global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const NormRopeParams p) {
+  __shared__ float red[2][kNormMaxThreads / 32];
   const int C = p.H * p.D;
-  const int nvec = C >> 3;
-  const long long token = blockIdx.x;
-  const int b = static_cast<int>(token / p.S);
-  const int s = static_cast<int>(token % p.S);
-  const size_t row = static_cast<size_t>(token) * p.x_row_stride;
-
-  float v[kNormMaxVec][8];
-  float ss = 0.f;
-#pragma unroll
-  for (int k = 0; k < kNormMaxVec; ++k) {
-    const int vi = threadIdx.x + k * kNormThreads;
-    if (vi < nvec) {
-      const float4 a = ld4(p.x, p.in_dtype, row + vi * 8);
-      const float4 c = ld4(p.x, p.in_dtype, row + vi * 8 + 4);
-      v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
-      v[k][4] = c.x; v[k][5] = c.y; v[k][6] = c.z; v[k][7] = c.w;
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[k][e] = 0.f;
-    }
-  }
-
-  float rstd_full = 1.f;
-  if (p.norm_mode == 0) {
-#pragma unroll
-    for (int k = 0; k < kNormMaxVec; ++k)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) ss = fmaf(v[k][e], v[k][e], ss);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
-    rstd_full = rsqrtf(tot / static_cast<float>(C) + p.eps);
-  }
-
-  // token position for the rotary table
-  const long long n = p.pos_offset + s;
-  int pf = 0, ph = 0, pw = 0;
-  bool rotate = p.rope_mode != 0;
-  if (p.rope_mode == 1) {
-    const long long grid = static_cast<long long>(p.gf) * p.gh * p.gw;
-    if (n >= grid) {
-      rotate = false;
-    } else {
-      pf = static_cast<int>(n / (static_cast<long long>(p.gh) * p.gw));
-      ph = static_cast<int>((n / p.gw) % p.gh);
-      pw = static_cast<int>(n % p.gw);
-    }
-  } else if (p.rope_mode == 2) {
-    if (n >= p.table_rows) rotate = false;
-  }
+  const int c0 = threadIdx.x * 8;
+  const bool active = c0 < C;
+  const int h = active ? c0 / p.D : 0;
+  const int d0 = c0 - h * p.D;
   const int half_d = p.D >> 1;
   const int vec_per_head = p.D >> 3;
+  const int n_warps = blockDim.x >> 5;
+  const long long tokens = static_cast<long long>(p.B) * p.S;
 
+  float wgt[8];
 #pragma unroll
-  for (int k = 0; k < kNormMaxVec; ++k) {
-    const int vi = threadIdx.x + k * kNormThreads;
-    float rstd = rstd_full;
-    if (p.norm_mode == 1) {
-      float hs = 0.f;
+  for (int e = 0; e < 8; ++e) wgt[e] = 1.f;
+  const bool has_w = (kNormMode != 2) && p.weight != nullptr;
+  if (has_w && active) {
+    const int w0 = (kNormMode == 0) ? c0 : d0;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) hs = fmaf(v[k][e], v[k][e], hs);
-      for (int o = vec_per_head >> 1; o > 0; o >>= 1) hs += __shfl_xor_sync(0xffffffffu, hs, o);
-      rstd = rsqrtf(hs / static_cast<float>(p.D) + p.eps);
-    }
-    if (vi >= nvec) continue;
-    const int c0 = vi * 8;
-    const int h = c0 / p.D;
-    const int d0 = c0 - h * p.D;
-    float y[8];
+    for (int e = 0; e < 8; ++e) wgt[e] = ld_as_float(p.weight, p.w_dtype, w0 + e);
+  }
+  const bool round_w = p.round_mid && p.w_dtype != kFP32 && kInDtype != kFP32;
+  const long long out_h = (h / p.heads_per_group) * p.os_g + (h % p.heads_per_group) * p.os_h + d0;
+
+  long long token = blockIdx.x;
+  float v[8], nxt[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float t = v[k][e];
-      if (p.norm_mode != 2) {
-        t *= rstd;
-        if (p.round_mid) t = round_to(t, p.in_dtype);
-        if (p.weight != nullptr) {
-          const int wi = (p.norm_mode == 0) ? (c0 + e) : (d0 + e);
-          t *= ld_as_float(p.weight, p.w_dtype, wi);
-          if (p.round_mid && p.w_dtype != kFP32 && p.in_dtype != kFP32) t = round_to(t, p.w_dtype);
-        }
-      }
-      y[e] = t;
-    }
-    if (rotate) {
+  for (int e = 0; e < 8; ++e) v[e] = nxt[e] = 0.f;
+  if (active && token < tokens) ld8<kInDtype>(p.x, static_cast<size_t>(token) * p.x_row_stride + c0, v);
+  int phase = 0;
+  for (; token < tokens; token += gridDim.x, phase ^= 1) {
+    const long long t_next = token + gridDim.x;
+    if (active && t_next < tokens) ld8<kInDtype>(p.x, static_cast<size_t>(t_next) * p.x_row_stride + c0, nxt);
+
+    float rstd = 1.f;
+    if (kNormMode != 2) {
+      float ss = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const int j = (d0 + e) >> 1;
-        long long trow;
-        if (p.rope_mode == 1) {
-          trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
-        } else {
-          trow = n;
-        }
-        const float2 cs = p.table[trow * half_d + j];
-        const float re = y[e] * cs.x - y[e + 1] * cs.y;
-        const float im = y[e] * cs.y + y[e + 1] * cs.x;
-        y[e] = re;
-        y[e + 1] = im;
+      for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+      if (kNormMode == 0) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31) == 0) red[phase][threadIdx.x >> 5] = ss;
+        __syncthreads();  // red[phase] is rewritten two tokens later, after the next barrier
+        float tot = 0.f;
+        for (int i = 0; i < n_warps; ++i) tot += red[phase][i];
+        rstd = rsqrtf(tot / static_cast<float>(C) + p.eps);
+      } else {
+        for (int o = vec_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        rstd = rsqrtf(ss / static_cast<float>(p.D) + p.eps);
       }
     }
-    uint4 o;
-    o.x = pack16(y[0], y[1], p.out_dtype);
-    o.y = pack16(y[2], y[3], p.out_dtype);
-    o.z = pack16(y[4], y[5], p.out_dtype);
-    o.w = pack16(y[6], y[7], p.out_dtype);
-    const long long off = b * p.os_b + s * p.os_s + (h / p.heads_per_group) * p.os_g +
-                          (h % p.heads_per_group) * p.os_h + d0;
-    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + off) = o;
+    if (active) {
+      const int b = static_cast<int>(token / p.S);
+      const int s = static_cast<int>(token - static_cast<long long>(b) * p.S);
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float t = v[e];
+        if (kNormMode != 2) {
+          t *= rstd;
+          if (p.round_mid) t = round_to(t, kInDtype);
+          if (has_w) {
+            t *= wgt[e];
+            if (round_w) t = round_to(t, p.w_dtype);
+          }
+        }
+        y[e] = t;
+      }
+      if (kRopeMode != 0) {
+        const long long n = p.pos_offset + s;
+        bool rotate = true;
+        int pf = 0, ph = 0, pw = 0;
+        if (kRopeMode == 1) {
+          if (n >= static_cast<long long>(p.gf) * p.gh * p.gw) {
+            rotate = false;  // padding tokens past the grid pass through
+          } else {
+            pf = static_cast<int>(n / (static_cast<long long>(p.gh) * p.gw));
+            ph = static_cast<int>((n / p.gw) % p.gh);
+            pw = static_cast<int>(n % p.gw);
+          }
+        } else if (n >= p.table_rows) {
+          rotate = false;
+        }
+        if (rotate) {
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const int j = (d0 + e) >> 1;
+            long long trow = n;
+            if (kRopeMode == 1) trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
+            const float2 cs = __ldg(&p.table[trow * half_d + j]);
+            const float re = y[e] * cs.x - y[e + 1] * cs.y;
+            const float im = y[e] * cs.y + y[e + 1] * cs.x;
+            y[e] = re;
+            y[e + 1] = im;
+          }
+        }
+      }
+      uint4 o;
+      o.x = pack16(y[0], y[1], p.out_dtype);
+      o.y = pack16(y[2], y[3], p.out_dtype);
+      o.z = pack16(y[4], y[5], p.out_dtype);
+      o.w = pack16(y[6], y[7], p.out_dtype);
+      *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + b * p.os_b + s * p.os_s + out_h) = o;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = nxt[e];
   }
 }
 
