@@ -173,7 +173,7 @@ def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
 class Pipeline:
     """Per-rank block function: pre-attention pass + (context-parallel) attention."""
 
-    def __init__(self, w, rank, world, device):
+    def __init__(self, w, rank, world, device, exchange="peer"):
         from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
         from chitudiffusion_b200.context_parallel import B200ContextParallel
 
@@ -186,8 +186,19 @@ class Pipeline:
             comm.initialize_diffusion_parallel_groups(1, world, up)
             self.attn = B200ContextParallel(self.backend, up, cp_backend="ucp")
             self.parallelism = f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else "")
+            self.peer = None
+            if exchange == "peer" and up == world:
+                # pure Ulysses: exchange fused into the pre-attention stores and the attention epilogue
+                from chitudiffusion_b200.peer import PeerUlysses
+
+                self.peer = PeerUlysses(comm.get_up_group(up), 1, seq_len(w) // world, self.H, self.D,
+                                        torch.bfloat16, device)
+                self.parallelism += "-peer-stores"
+            else:
+                self.parallelism += "-nccl"
         else:
             self.parallelism = "single"
+            self.peer = None
         if w["kind"] == "joint":
             table = pre_attention.axis_rope_table(joint_ids(w), w["axes"])[local_positions(w, rank, world)]
             self.pre = pre_attention.JointPreAttention(self.H, self.D, table.contiguous().to(device))
@@ -201,6 +212,19 @@ class Pipeline:
         self.attn_events = []
 
     def block(self, qp, kp, vp, timed=False):
+        if self.peer is not None:
+            px = self.peer
+            place = dict(out_strides=px.gather_strides, heads_per_group=px.hc)
+            if self.w["kind"] == "joint":
+                self.pre.one(qp, self.nq, out_ptrs=px.dest_ptrs("q"), **place)
+                self.pre.one(kp, self.nk, out_ptrs=px.dest_ptrs("k"), **place)
+            else:
+                self.pre.one(qp, self.nq, self.w["grid"], out_ptrs=px.dest_ptrs("q"), **place)
+                self.pre.one(kp, self.nk, self.w["grid"], out_ptrs=px.dest_ptrs("k"), **place)
+            px.scatter_plain(vp, "v")
+            out = px.attention()
+            self.launches += 6  # 3 scatter stores, attention, 2 barriers
+            return out
         if self.w["kind"] == "joint":
             q, k, v = self.pre(qp, kp, vp, self.nq, self.nk)
         else:
@@ -242,7 +266,7 @@ def run_ours(args):
     w = WORKLOADS[args.workload]
     if seq_len(w) % world or (w["kind"] == "joint" and (w["s_txt"] % world or w["s_img"] % world)):
         raise ValueError("sequence not divisible by the number of GPUs")
-    pipe = Pipeline(w, rank, world, device)
+    pipe = Pipeline(w, rank, world, device, exchange=args.exchange)
     dev_sets = make_inputs(w, rank, world, seed=1, n_sets=INPUT_SETS, device=device)
     host_sets = make_inputs(w, rank, world, seed=1, n_sets=2, device=None, pinned=True)
     e2e_dev = [tuple(torch.empty_like(t, device=device) for t in trip) for trip in host_sets]
@@ -429,6 +453,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: Ulysses exchange by peer stores fused into the kernels, or by NCCL all-to-all")
     ap.add_argument("--profile", action="store_true",
                     help="short run for ncu: device-resident leg only (no host-buffer leg, no CPU baseline)")
     args = ap.parse_args()

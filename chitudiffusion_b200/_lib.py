@@ -24,6 +24,9 @@ EXPORTS = (
     "chitu_b200_lse_combine",
     "chitu_b200_qk_norm_rope",
     "chitu_b200_strided_copy",
+    "chitu_b200_qk_norm_rope_scatter",
+    "chitu_b200_attn_fwd_scatter",
+    "chitu_b200_peer_barrier",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -72,8 +75,28 @@ def load() -> ctypes.CDLL:
     lib.chitu_b200_strided_copy.argtypes = [
         _vp, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _i64p, _vp,
     ]
+    _vpp = ctypes.POINTER(ctypes.c_void_p)
+    lib.chitu_b200_qk_norm_rope_scatter.restype = ctypes.c_int
+    lib.chitu_b200_qk_norm_rope_scatter.argtypes = [
+        _vp, ctypes.c_int, ctypes.c_int64, _vp, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int,
+        _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int64,
+        _vpp, ctypes.c_int, ctypes.c_int, _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        ctypes.c_int, ctypes.c_int, _vp,
+    ]
+    lib.chitu_b200_attn_fwd_scatter.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_scatter.argtypes = [
+        _vp, _vp, _vp, _vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, _vp,
+    ]
+    lib.chitu_b200_peer_barrier.restype = ctypes.c_int
+    lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp]
     _lib = lib
     return lib
+
+
+def ptr_array(ptrs: Sequence[int]):
+    return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
 
 
 def i64_array(values: Sequence[int]):

@@ -47,6 +47,14 @@ struct AttnParams {
   int B, H, Sq, Sk;
   float scale_log2; // softmax_scale * log2(e)
   int is_fp16;      // 0 = bf16, 1 = fp16
+  // Scattered output (sequence-to-head exchange fused into the epilogue): when n_dest > 0, query
+  // row r goes to destination r / rows_per_dest (its own or a peer GPU's buffer) at local row
+  // r % rows_per_dest, byte address
+  //   out_ptrs[dest] + batch * dest_batch_bytes + local_row * dest_row_bytes + dest_head_bytes + head * 256
+  void* out_ptrs[8];
+  int n_dest;
+  int rows_per_dest;
+  long long dest_batch_bytes, dest_row_bytes, dest_head_bytes;
 #ifdef CHITU_ATTN_TIMING
   long long* dbg;   // per-phase clock totals of CTA 0 (development builds only)
 #endif
@@ -404,8 +412,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after_sync();
       const int row = q0 + t * kTileM + row_in_tile;
       const float inv_l = 1.0f / l_sum;
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) +
-                                            ((static_cast<size_t>(batch) * p.Sq + row) * p.H + head) * (kHeadDim * 2));
+      uint4* dst;
+      if (p.n_dest == 0) {
+        dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) +
+                                       ((static_cast<size_t>(batch) * p.Sq + row) * p.H + head) * (kHeadDim * 2));
+      } else {
+        const int dest = min(row / p.rows_per_dest, p.n_dest - 1);
+        const long long local_row = row - static_cast<long long>(dest) * p.rows_per_dest;
+        dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_ptrs[dest]) + batch * p.dest_batch_bytes +
+                                       local_row * p.dest_row_bytes + p.dest_head_bytes + head * (kHeadDim * 2));
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];

@@ -95,23 +95,46 @@ extern "C" {
 int chitu_b200_version(void) { return 100; }
 
 unsigned chitu_b200_caps(void) {
-  return CHITU_CAP_ATTN_BF16 | CHITU_CAP_ATTN_FP16 | CHITU_CAP_NORM_ROPE | CHITU_CAP_LSE_COMBINE | CHITU_CAP_A2A_LAYOUT;
+  return CHITU_CAP_ATTN_BF16 | CHITU_CAP_ATTN_FP16 | CHITU_CAP_NORM_ROPE | CHITU_CAP_LSE_COMBINE | CHITU_CAP_A2A_LAYOUT |
+         CHITU_CAP_PEER_EXCHANGE;
 }
 
 const char* chitu_b200_last_error(void) { return g_err; }
 
-int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
-                        int H, int D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
-                        float softmax_scale, int dtype, int* status, void* stream) {
-  if (!q || !k || !v || !out || !q_strides || !k_strides || !v_strides)
+}  // extern "C"
+
+namespace {
+
+struct OutScatter {
+  void* const* ptrs = nullptr;
+  int n_dest = 0;
+  int rows_per_dest = 0;
+  int64_t batch_stride = 0, row_stride = 0, head_offset = 0;  // elements
+};
+
+int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const OutScatter& sc, float* lse, int B,
+                  int Sq, int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
+                  const int64_t* v_strides, float softmax_scale, int dtype, int* status, void* stream) {
+  if (!q || !k || !v || (!out && sc.n_dest == 0) || !q_strides || !k_strides || !v_strides)
     return fail(CHITU_E_INVALID, "attn_fwd: null pointer argument");
+  if (sc.n_dest != 0) {
+    if (sc.n_dest < 0 || sc.n_dest > 8 || !sc.ptrs) return fail(CHITU_E_INVALID, "attn_fwd: 1..8 destinations");
+    if (sc.rows_per_dest <= 0 || static_cast<int64_t>(sc.rows_per_dest) * sc.n_dest < Sq)
+      return fail(CHITU_E_INVALID, "attn_fwd: destinations do not cover the query rows");
+    if ((sc.batch_stride | sc.row_stride | sc.head_offset) & 7)
+      return fail(CHITU_E_INVALID, "attn_fwd: destination strides must be multiples of 8 elements");
+    for (int i = 0; i < sc.n_dest; ++i)
+      if (!sc.ptrs[i] || (reinterpret_cast<uintptr_t>(sc.ptrs[i]) & 15))
+        return fail(CHITU_E_INVALID, "attn_fwd: destination %d null or not 16-byte aligned", i);
+  }
   if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0)
     return fail(CHITU_E_INVALID, "attn_fwd: B, H, Sq, Sk must be positive (got %d, %d, %d, %d)", B, H, Sq, Sk);
   if (D != chitu::kHeadDim) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: head_dim %d not supported (only 128)", D);
   if (dtype != CHITU_DTYPE_BF16 && dtype != CHITU_DTYPE_FP16)
     return fail(CHITU_E_UNSUPPORTED, "attn_fwd: dtype must be bf16 or fp16");
   if (!(softmax_scale > 0.f)) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: softmax_scale must be positive");
-  if (reinterpret_cast<uintptr_t>(out) & 15) return fail(CHITU_E_INVALID, "attn_fwd: out must be 16-byte aligned");
+  if (sc.n_dest == 0 && (reinterpret_cast<uintptr_t>(out) & 15))
+    return fail(CHITU_E_INVALID, "attn_fwd: out must be 16-byte aligned");
   if (H > 65535 || B > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: H and B must be below 65536");
 
   CUtensorMap tq, tk, tv;
@@ -130,6 +153,12 @@ int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, 
   p.Sk = Sk;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.is_fp16 = dtype == CHITU_DTYPE_FP16;
+  p.n_dest = sc.n_dest;
+  p.rows_per_dest = sc.rows_per_dest;
+  p.dest_batch_bytes = sc.batch_stride * 2;
+  p.dest_row_bytes = sc.row_stride * 2;
+  p.dest_head_bytes = sc.head_offset * 2;
+  for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < sc.n_dest ? sc.ptrs[i] : nullptr;
 #ifdef CHITU_ATTN_TIMING
   p.dbg = g_dbg;
 #endif
@@ -156,6 +185,34 @@ int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, 
   return CHITU_OK;
 }
 
+}  // namespace
+
+extern "C" {
+
+int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                        int H, int D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                        float softmax_scale, int dtype, int* status, void* stream) {
+  return attn_fwd_impl(q, k, v, out, OutScatter{}, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides,
+                       softmax_scale, dtype, status, stream);
+}
+
+int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
+                                int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
+                                int64_t dest_head_offset, float* lse, int B, int Sq, int Sk, int H, int D,
+                                const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                float softmax_scale, int dtype, int* status, void* stream) {
+  OutScatter sc;
+  sc.ptrs = out_ptrs;
+  sc.n_dest = n_dest;
+  sc.rows_per_dest = rows_per_dest;
+  sc.batch_stride = dest_batch_stride;
+  sc.row_stride = dest_row_stride;
+  sc.head_offset = dest_head_offset;
+  if (n_dest <= 0) return fail(CHITU_E_INVALID, "attn_fwd_scatter: n_dest must be positive");
+  return attn_fwd_impl(q, k, v, nullptr, sc, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides, softmax_scale,
+                       dtype, status, stream);
+}
+
 int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out, const float* block_lse, int B, int S,
                            int H, int D, int block_dtype, int first, void* final_out, int final_dtype, void* stream) {
   if (!acc_out || !acc_lse || !block_out || !block_lse) return fail(CHITU_E_INVALID, "lse_combine: null pointer");
@@ -175,12 +232,23 @@ int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out
   return CHITU_OK;
 }
 
-int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype,
-                            float eps, int norm_mode, int rope_mode, const float* rope_table, int table_rows, int gf,
-                            int gh, int gw, const int* axis_split, int64_t pos_offset, void* out, int out_dtype,
-                            const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D, int round_mid,
-                            void* stream) {
-  if (!x || !out || !out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+}  // extern "C"
+
+namespace {
+
+int qk_norm_rope_impl(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype, float eps,
+                      int norm_mode, int rope_mode, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                      const int* axis_split, int64_t pos_offset, void* out, void* const* out_ptrs, int n_out_ptrs,
+                      int out_dtype, const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                      int round_mid, void* stream) {
+  if (!x || (!out && n_out_ptrs == 0) || !out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+  if (n_out_ptrs != 0) {
+    if (n_out_ptrs < 0 || n_out_ptrs > 8 || !out_ptrs || heads_per_group <= 0 || n_out_ptrs * heads_per_group != H)
+      return fail(CHITU_E_INVALID, "qk_norm_rope: need one destination per head group (at most 8)");
+    for (int i = 0; i < n_out_ptrs; ++i)
+      if (!out_ptrs[i] || (reinterpret_cast<uintptr_t>(out_ptrs[i]) & 15))
+        return fail(CHITU_E_INVALID, "qk_norm_rope: destination %d null or not 16-byte aligned", i);
+  }
   if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: bad shape");
   if (D & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: head_dim must be a multiple of 8");
   const long long C = static_cast<long long>(H) * D;
@@ -243,6 +311,8 @@ int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, c
   p.H = H;
   p.D = D;
   p.round_mid = round_mid;
+  p.n_out_ptrs = n_out_ptrs;
+  for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < n_out_ptrs ? out_ptrs[i] : nullptr;
   const long long tokens = static_cast<long long>(B) * S;
   if (tokens > 2147483647LL) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: too many tokens");
   // one 8-channel vector per thread, whole warps; the grid fills the 148 SMs a few CTAs deep
@@ -273,6 +343,49 @@ int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, c
 #undef CHITU_NR_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "qk_norm_rope: launch");
+  return CHITU_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype,
+                            float eps, int norm_mode, int rope_mode, const float* rope_table, int table_rows, int gf,
+                            int gh, int gw, const int* axis_split, int64_t pos_offset, void* out, int out_dtype,
+                            const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D, int round_mid,
+                            void* stream) {
+  return qk_norm_rope_impl(x, in_dtype, x_row_stride, weight, w_dtype, eps, norm_mode, rope_mode, rope_table,
+                           table_rows, gf, gh, gw, axis_split, pos_offset, out, nullptr, 0, out_dtype, out_strides,
+                           heads_per_group, B, S, H, D, round_mid, stream);
+}
+
+int chitu_b200_qk_norm_rope_scatter(const void* x, int in_dtype, int64_t x_row_stride, const void* weight,
+                                    int w_dtype, float eps, int norm_mode, int rope_mode, const float* rope_table,
+                                    int table_rows, int gf, int gh, int gw, const int* axis_split, int64_t pos_offset,
+                                    void* const* out_ptrs, int n_out_ptrs, int out_dtype, const int64_t* out_strides,
+                                    int heads_per_group, int B, int S, int H, int D, int round_mid, void* stream) {
+  if (n_out_ptrs <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope_scatter: n_out_ptrs must be positive");
+  return qk_norm_rope_impl(x, in_dtype, x_row_stride, weight, w_dtype, eps, norm_mode, rope_mode, rope_table,
+                           table_rows, gf, gh, gw, axis_split, pos_offset, nullptr, out_ptrs, n_out_ptrs, out_dtype,
+                           out_strides, heads_per_group, B, S, H, D, round_mid, stream);
+}
+
+int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int epoch, int* status, void* stream) {
+  if (!flag_ptrs || world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(CHITU_E_INVALID, "peer_barrier: need 1..8 ranks and a rank inside the group");
+  chitu::PeerBarrierParams p;
+  for (int i = 0; i < 8; ++i) p.flags[i] = i < world ? flag_ptrs[i] : nullptr;
+  for (int i = 0; i < world; ++i)
+    if (!p.flags[i]) return fail(CHITU_E_INVALID, "peer_barrier: null flag array for rank %d", i);
+  p.rank = rank;
+  p.world = world;
+  p.epoch = epoch;
+  p.status = status;
+  p.timeout_cycles = 1ll << 31;  // about a second
+  chitu::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "peer_barrier: launch");
   return CHITU_OK;
 }
 

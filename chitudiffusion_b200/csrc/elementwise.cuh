@@ -124,6 +124,11 @@ struct NormRopeParams {
   int heads_per_group;
   int B, S, H, D;
   int round_mid;
+  // Scattered output (head-to-sequence exchange fused into the store): when n_out_ptrs > 0,
+  // head group g = h / heads_per_group is written to out_ptrs[g] (its own or a peer GPU's
+  // buffer) instead of out + g * os_g.
+  void* out_ptrs[8];
+  int n_out_ptrs;
 };
 
 constexpr int kNormMaxThreads = 1024;  // one 8-channel vector per thread: up to 8192 channels per token
@@ -164,7 +169,9 @@ __global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const Nor
     for (int e = 0; e < 8; ++e) wgt[e] = ld_as_float(p.weight, p.w_dtype, w0 + e);
   }
   const bool round_w = p.round_mid && p.w_dtype != kFP32 && kInDtype != kFP32;
-  const long long out_h = (h / p.heads_per_group) * p.os_g + (h % p.heads_per_group) * p.os_h + d0;
+  const int grp = h / p.heads_per_group;
+  const long long out_h = (p.n_out_ptrs > 0 ? 0 : grp * p.os_g) + (h % p.heads_per_group) * p.os_h + d0;
+  uint16_t* const out_base = static_cast<uint16_t*>(p.n_out_ptrs > 0 ? p.out_ptrs[grp] : p.out);
 
   long long token = blockIdx.x;
   float v[8], nxt[8];
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const Nor
       o.y = pack16(y[2], y[3], p.out_dtype);
       o.z = pack16(y[4], y[5], p.out_dtype);
       o.w = pack16(y[6], y[7], p.out_dtype);
-      *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + b * p.os_b + s * p.os_s + out_h) = o;
+      *reinterpret_cast<uint4*>(out_base + b * p.os_b + s * p.os_s + out_h) = o;
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = nxt[e];
@@ -268,6 +275,39 @@ strided_copy_kernel(const uint8_t* __restrict__ src, uint4* __restrict__ dst, lo
     const long long i0 = r / n1;
     const uint4* sp = reinterpret_cast<const uint4*>(src + i0 * st0 + i1 * st1 + i2 * st2 + i3 * st3) + vec;
     dst[i] = *sp;
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Barrier among the GPUs of one exchange group over peer-mapped flag arrays.
+// Thread i tells peer i "rank `rank` has reached `epoch`" (release store, system scope) and
+// then waits until peer i has said the same to us.  The wait is bounded; on timeout the
+// status word is set and the kernel returns.
+// ----------------------------------------------------------------------------
+struct PeerBarrierParams {
+  int* flags[8];  // flags[i]: base of rank i's flag array (world ints), mapped into this process
+  int rank, world, epoch;
+  int* status;
+  long long timeout_cycles;
+};
+
+__global__ void peer_barrier_kernel(const PeerBarrierParams p) {
+  const int i = threadIdx.x;
+  if (i >= p.world) return;
+  __threadfence_system();  // order this stream's earlier peer stores before the flag
+  int* remote = p.flags[i] + p.rank;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
+  const int* mine = p.flags[p.rank] + i;
+  const long long t0 = clock64();
+  int seen;
+  unsigned spins = 0;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (seen - p.epoch >= 0) break;  // epochs only grow (wrap-safe comparison)
+    if ((++spins & 0xff) == 0 && clock64() - t0 > p.timeout_cycles) {
+      if (p.status) atomicCAS(p.status, 0, 5);
+      break;
+    }
   }
 }
 

@@ -154,7 +154,8 @@ def qk_norm_rope(
     heads_per_group: Optional[int] = None,
     out_dtype: torch.dtype = torch.bfloat16,
     round_mid: bool = True,
-) -> torch.Tensor:
+    out_ptrs: Optional[Sequence[int]] = None,
+) -> Optional[torch.Tensor]:
     """RMSNorm + rotary + 16-bit cast of a projection output ``[B,S,H*D]``; see ``chitu_b200_qk_norm_rope``.
 
     Without ``out`` a contiguous ``[B,S,H,D]`` tensor is returned.  With ``out`` and ``out_strides``
@@ -178,7 +179,10 @@ def qk_norm_rope(
             raise ValueError("rope_table must be a contiguous fp32 [rows, D/2, 2] tensor")
         if rope_table.shape[-2:] != (D // 2, 2):
             raise ValueError(f"rope_table must be [rows, {D // 2}, 2]")
-    if out is None:
+    if out_ptrs is not None:
+        if out is not None or out_strides is None or heads_per_group is None:
+            raise ValueError("out_ptrs needs out_strides and heads_per_group, and excludes out")
+    elif out is None:
         out = torch.empty((B, S, num_heads, D), dtype=out_dtype, device=x.device)
         out_strides = (S * C, C, 0, D)
         heads_per_group = num_heads
@@ -188,15 +192,21 @@ def qk_norm_rope(
     import ctypes
 
     split = (ctypes.c_int * 2)(int(axis_split[0]), int(axis_split[1]))
+    common = (
+        x.data_ptr(), _DTYPES[x.dtype], x.stride(1), weight.data_ptr() if weight is not None else None,
+        _DTYPES[weight.dtype] if weight is not None else _lib.DTYPE_FP32, float(eps), int(norm_mode),
+        int(rope_mode), rope_table.data_ptr() if rope_table is not None else None,
+        int(rope_table.shape[0]) if rope_table is not None else 0, int(grid[0]), int(grid[1]), int(grid[2]),
+        split, int(pos_offset),
+    )
+    tail = (_lib.i64_array(out_strides), int(heads_per_group), B, S, num_heads, D, 1 if round_mid else 0,
+            _stream_ptr(x.device))
     with torch.cuda.device(x.device):
-        rc = lib.chitu_b200_qk_norm_rope(
-            x.data_ptr(), _DTYPES[x.dtype], x.stride(1), weight.data_ptr() if weight is not None else None,
-            _DTYPES[weight.dtype] if weight is not None else _lib.DTYPE_FP32, float(eps), int(norm_mode),
-            int(rope_mode), rope_table.data_ptr() if rope_table is not None else None,
-            int(rope_table.shape[0]) if rope_table is not None else 0, int(grid[0]), int(grid[1]), int(grid[2]),
-            split, int(pos_offset), out.data_ptr(), _DTYPES[out.dtype], _lib.i64_array(out_strides),
-            int(heads_per_group), B, S, num_heads, D, 1 if round_mid else 0, _stream_ptr(x.device),
-        )
+        if out_ptrs is not None:
+            rc = lib.chitu_b200_qk_norm_rope_scatter(*common, _lib.ptr_array(out_ptrs), len(out_ptrs),
+                                                     _DTYPES[out_dtype], *tail)
+        else:
+            rc = lib.chitu_b200_qk_norm_rope(*common, out.data_ptr(), _DTYPES[out.dtype], *tail)
     _lib.check(rc, "qk_norm_rope")
     return out
 
@@ -215,3 +225,41 @@ def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
         )
     _lib.check(rc, "strided_copy")
     return dst
+
+
+def attn_fwd_scatter(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out_ptrs: Sequence[int],
+    rows_per_dest: int,
+    dest_batch_stride: int,
+    dest_row_stride: int,
+    dest_head_offset: int,
+    softmax_scale: Optional[float] = None,
+) -> None:
+    """Attention whose query row ``r`` is stored to ``out_ptrs[r // rows_per_dest]``; see ``chitu_b200_attn_fwd_scatter``."""
+    _require_cuda(q, k, v)
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError("attention kernel takes bf16 or fp16 q/k/v of one dtype")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        rc = lib.chitu_b200_attn_fwd_scatter(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr_array(out_ptrs), len(out_ptrs), int(rows_per_dest),
+            int(dest_batch_stride), int(dest_row_stride), int(dest_head_offset), None, B, Sq, Sk, H, D,
+            _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale,
+            _DTYPES[q.dtype], status_word(q.device).data_ptr(), _stream_ptr(q.device),
+        )
+    _lib.check(rc, "attn_fwd_scatter")
+
+
+def peer_barrier(flag_ptrs: Sequence[int], rank: int, world: int, epoch: int, device: torch.device) -> None:
+    """Enqueue the bounded cross-GPU barrier on the current stream; see ``chitu_b200_peer_barrier``."""
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        rc = lib.chitu_b200_peer_barrier(_lib.ptr_array(flag_ptrs), int(rank), int(world), int(epoch),
+                                         status_word(device).data_ptr(), _stream_ptr(device))
+    _lib.check(rc, "peer_barrier")

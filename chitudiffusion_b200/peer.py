@@ -1,0 +1,105 @@
+"""Ulysses sequence/head exchange over peer-mapped GPU memory (one node, NVLink).
+
+Replaces, for the pure-Ulysses layout, the three all-to-all calls before the attention kernel and
+the one after it (chitu_diffusion/modules/attention/diffusion_attn_backend.py:778-781,825-828)
+together with their pack/unpack copies (chitu_diffusion/core/distributed/comm_group.py:350-384):
+
+* the pre-attention kernel stores q and k (and a plain scatter stores v) straight into every
+  rank's ``[B, U*s, H/U, D]`` buffer - rank r's rows land at ``[r*s, (r+1)*s)`` of each peer;
+* one bounded barrier kernel;
+* the attention kernel's epilogue stores each output row into its owner's ``[B, s, H, D]`` buffer
+  (head columns ``[r*H/U, (r+1)*H/U)``);
+* a second barrier, after which every rank's output is complete and the exchange buffers may be
+  reused.
+
+Buffers come from ``torch.distributed._symmetric_memory`` (device memory mapped into every process
+of the group); the data path is plain peer stores from this library's kernels - no NCCL call, no
+TMA from or to peer memory.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .comm import CommGroup
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class PeerUlysses:
+    """Exchange buffers and per-layer schedule for one ``(B, s, H, D, dtype)`` problem shape."""
+
+    def __init__(self, group: CommGroup, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        U = group.group_size
+        if H % U:
+            raise ValueError(f"head dim {H} must be divisible by CP size {U}")
+        if U > 8:
+            raise NotImplementedError("peer exchange supports at most 8 GPUs")
+        self.group, self.U, self.rank = group, U, group.rank_in_group
+        self.B, self.s, self.H, self.D, self.hc = B, s, H, D, H // U
+        self.dtype, self.device = dtype, device
+        es = torch.empty((), dtype=dtype).element_size()
+        self.es = es
+        tile = B * U * s * self.hc * D * es  # one of q / k / v in the gathered layout
+        self.off_q = 0
+        self.off_k = _align(tile)
+        self.off_v = self.off_k + _align(tile)
+        self.off_out = self.off_v + _align(tile)
+        self.off_flags = self.off_out + _align(B * s * H * D * es)
+        total = self.off_flags + 256
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.gpu_group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group.gpu_group)  # every flag array is zero before anyone signals
+        self.epoch = 0
+
+        def view(off, shape):
+            n = 1
+            for d in shape:
+                n *= d
+            return self.buf[off : off + n * es].view(dtype).view(shape)
+
+        gathered = (B, U * s, self.hc, D)
+        self.q, self.k, self.v = view(self.off_q, gathered), view(self.off_k, gathered), view(self.off_v, gathered)
+        self.out = view(self.off_out, (B, s, H, D))
+        self.flag_ptrs = [p + self.off_flags for p in self.ptrs]
+        # element strides (b, s, -, h) of the gathered layout; this rank's rows start at rank * s
+        self.gather_strides = (U * s * self.hc * D, self.hc * D, 0, D)
+        self._row0 = self.rank * s * self.hc * D * es
+
+    def dest_ptrs(self, which: str):
+        """Per-destination base addresses for this rank's rows of q / k / v."""
+        off = {"q": self.off_q, "k": self.off_k, "v": self.off_v}[which]
+        return [p + off + self._row0 for p in self.ptrs]
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        ops.peer_barrier(self.flag_ptrs, self.rank, self.U, self.epoch, self.device)
+
+    def scatter_plain(self, x: torch.Tensor, which: str = "v") -> None:
+        """``x [B, s, H*D]`` (or ``[B,s,H,D]``) 16-bit: copy each head group to its owner."""
+        flat = x.reshape(self.B, self.s, self.H * self.D)
+        ops.qk_norm_rope(flat, self.H, None, 0.0, norm_mode=2, rope_mode=0, rope_table=None,
+                         out_ptrs=self.dest_ptrs(which), out_strides=self.gather_strides,
+                         heads_per_group=self.hc, out_dtype=self.dtype)
+
+    def attention(self, softmax_scale: Optional[float] = None) -> torch.Tensor:
+        """Barrier, attention over the gathered q/k/v with the output scattered to its owners, barrier."""
+        self.barrier()
+        ops.attn_fwd_scatter(
+            self.q, self.k, self.v, [p + self.off_out for p in self.ptrs], rows_per_dest=self.s,
+            dest_batch_stride=self.s * self.H * self.D, dest_row_stride=self.H * self.D,
+            dest_head_offset=self.rank * self.hc * self.D, softmax_scale=softmax_scale,
+        )
+        self.barrier()
+        return self.out

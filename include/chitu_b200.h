@@ -42,6 +42,7 @@ int chitu_b200_version(void);
 #define CHITU_CAP_NORM_ROPE 4u
 #define CHITU_CAP_LSE_COMBINE 8u
 #define CHITU_CAP_A2A_LAYOUT 16u
+#define CHITU_CAP_PEER_EXCHANGE 32u
 unsigned chitu_b200_caps(void);
 const char* chitu_b200_last_error(void);
 
@@ -124,6 +125,36 @@ int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, c
  */
 int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t n3,
                             int64_t row_bytes, const int64_t* src_strides_bytes, void* stream);
+
+/*
+ * Ulysses exchange fused into the kernels either side of it, over peer-mapped memory of the GPUs
+ * of one node (NVLink).  Together they replace the three all-to-all calls before and the one after
+ * the attention kernel in DiffusionAttention_with_CP._cp_forward
+ * (chitu_diffusion/modules/attention/diffusion_attn_backend.py:778-781,825-828) and the pack /
+ * unpack copies of CommGroup._all_to_all_single (chitu_diffusion/core/distributed/comm_group.py:350-384).
+ *
+ * chitu_b200_qk_norm_rope_scatter: as chitu_b200_qk_norm_rope, but head group g = h / heads_per_group
+ *   is written to out_ptrs[g] (rank g's buffer, mapped into this process) at
+ *   b*out_strides[0] + s*out_strides[1] + (h % heads_per_group)*out_strides[3] + d; out_strides[2] is ignored.
+ *   With norm_mode 2 and rope_mode 0 it is the plain scatter used for v.
+ * chitu_b200_attn_fwd_scatter: as chitu_b200_attn_fwd, but query row r is written to
+ *   out_ptrs[r / rows_per_dest] at element offset
+ *   batch*dest_batch_stride + (r % rows_per_dest)*dest_row_stride + dest_head_offset + head*128 + d.
+ * chitu_b200_peer_barrier: every rank enqueues it with the same, growing epoch; flag_ptrs[i] is
+ *   rank i's array of `world` int32 flags (zero-initialised) mapped into this process.  The wait is
+ *   bounded (about a second); on timeout *status is set to 5 and the kernel returns.
+ */
+int chitu_b200_qk_norm_rope_scatter(const void* x, int in_dtype, int64_t x_row_stride, const void* weight,
+                                    int w_dtype, float eps, int norm_mode, int rope_mode, const float* rope_table,
+                                    int table_rows, int gf, int gh, int gw, const int* axis_split, int64_t pos_offset,
+                                    void* const* out_ptrs, int n_out_ptrs, int out_dtype, const int64_t* out_strides,
+                                    int heads_per_group, int B, int S, int H, int D, int round_mid, void* stream);
+int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
+                                int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
+                                int64_t dest_head_offset, float* lse, int B, int Sq, int Sk, int H, int D,
+                                const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                float softmax_scale, int dtype, int* status, void* stream);
+int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int epoch, int* status, void* stream);
 
 #ifdef __cplusplus
 }

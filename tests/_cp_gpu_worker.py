@@ -1,0 +1,84 @@
+"""Multi-GPU worker (launched by tests/test_gpu_cp.py under torchrun, one rank per GPU, NCCL).
+
+Checks, against single-process fp32 attention from the CPU oracle on the same seeded tensors:
+the NCCL context-parallel layouts (Ulysses, ring, Ulysses x ring, all-gather-KV) through
+``B200ContextParallel`` with the b200 kernel, and the peer-store Ulysses exchange (``PeerUlysses``).
+"""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+sys.path.insert(0, ROOT)
+
+import oracle  # noqa: E402
+from chitudiffusion_b200 import B200AttnBackend, comm, ops  # noqa: E402
+from chitudiffusion_b200.context_parallel import B200ContextParallel  # noqa: E402
+from chitudiffusion_b200.peer import PeerUlysses  # noqa: E402
+from chitudiffusion_b200.pre_attention import WanPreAttention  # noqa: E402
+
+REL = 2e-2
+
+
+def rel_err(a, ref):
+    return (a.float().cpu() - ref).abs().max().item() / ref.abs().max().item()
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    H, D, s = 8, 128, 200
+    S = s * world
+    gen = torch.Generator().manual_seed(7)
+    q, k, v = ((torch.randn(1, S, H, D, generator=gen)).to(torch.bfloat16) for _ in range(3))
+    full = oracle.sdpa_fp32(q, k, v)
+    sl = slice(rank * s, (rank + 1) * s)
+    ql, kl, vl = (t[:, sl].contiguous().to(dev) for t in (q, k, v))
+    backend = B200AttnBackend("b200")
+    results = {}
+    layouts = [("ulysses", world, "ucp"), ("ring", 1, "ucp"), ("agcp", world, "agcp")]
+    if world >= 4:
+        layouts.append(("usp", world // 2, "ucp"))
+    for name, up, cpb in layouts:
+        comm.destroy_diffusion_parallel_groups()
+        comm.initialize_diffusion_parallel_groups(1, world, up)
+        wrapper = B200ContextParallel(backend, up, cp_backend=cpb)
+        out = wrapper(ql, kl, vl)[0]
+        results[name] = rel_err(out, full[:, sl])
+
+    # peer-store exchange: norm + rotary pre-pass scattered to the owners, attention scattered back
+    comm.destroy_diffusion_parallel_groups()
+    comm.initialize_diffusion_parallel_groups(1, world, world)
+    grid = (2, 10, S // 20)
+    C = H * D
+    xq, xk, xv = ((torch.randn(1, S, C, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(3))
+    wq, wk = (1.0 + 0.05 * torch.randn(C, generator=gen) for _ in range(2))
+    freqs = oracle.wan_rope_table(D)
+    rq, rk, rv = oracle.wan_self_attention_pre(xq, xk, xv, wq, wk, H, [list(grid)], freqs)
+    ref2 = oracle.sdpa_fp32(rq, rk, rv)
+    px = PeerUlysses(comm.get_up_group(world), 1, s, H, D, torch.bfloat16, dev)
+    pre = WanPreAttention(H, D, cp_size=world, cp_rank=rank, device=dev)
+    place = dict(out_strides=px.gather_strides, heads_per_group=px.hc)
+    for rep in range(3):  # buffers and barriers are reused call after call
+        pre.one(xq[:, sl].contiguous().to(dev), wq.to(dev), grid, out_ptrs=px.dest_ptrs("q"), **place)
+        pre.one(xk[:, sl].contiguous().to(dev), wk.to(dev), grid, out_ptrs=px.dest_ptrs("k"), **place)
+        px.scatter_plain(xv[:, sl].contiguous().to(dev), "v")
+        out = px.attention()
+        results[f"peer{rep}"] = rel_err(out, ref2[:, sl])
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    ok = all(e <= REL for e in results.values())
+    print(f"rank {rank}: " + " ".join(f"{n}={e:.2e}" for n, e in results.items()), flush=True)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
