@@ -296,19 +296,42 @@ def run_ours(args):
         for trip_h, trip_d in zip(host_sets, e2e_dev):
             for h, d in zip(trip_h, trip_d):
                 d.copy_(h, non_blocking=True)
-        out = pipe.step(e2e_dev)
+        if e2e_graph is not None:
+            e2e_graph.replay()
+            out = e2e_out[0]
+        else:
+            out = pipe.step(e2e_dev)
         out_host.copy_(out.view(out_host.shape) if out.dtype == out_host.dtype else out.to(torch.bfloat16),
                        non_blocking=True)
 
     for _ in range(args.warmup):
         pipe.step(dev_sets)
+    # On several GPUs a step is a few hundred short launches: capture it once in a CUDA graph and
+    # replay it (every kernel of the peer-store path, the barrier included, is replayable).
+    use_graph = world > 1 and pipe.peer is not None and not args.no_graph
+    step_graph = e2e_graph = None
+    e2e_out = [None]
+    if use_graph:
+        sync()
+        step_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(step_graph):
+            pipe.step(dev_sets)
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph):
+            e2e_out[0] = pipe.step(e2e_dev)
+        sync()
+    pipe.launches = 0
+    pipe.step(dev_sets)
+    launches_per_step = pipe.launches
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    pipe.launches = 0
     pipe.attn_events = []
-    total_ms = timed_region(lambda: pipe.step(dev_sets, timed=True), args.steps)
-    launches = pipe.launches
+    if use_graph:
+        total_ms = timed_region(step_graph.replay, args.steps)
+    else:
+        total_ms = timed_region(lambda: pipe.step(dev_sets, timed=True), args.steps)
+    launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     attn_ms = [a.elapsed_time(b) for a, b in pipe.attn_events]
 
@@ -355,6 +378,7 @@ def run_ours(args):
         "config": {
             "workload": args.workload, "seq_len": seq_len(w), "heads": w["H"], "head_dim": w["D"],
             "attention_calls_per_step": w["blocks"], "parallelism": pipe.parallelism, "batch": 1,
+            "cuda_graph": bool(use_graph),
             "l2_hygiene": f"{INPUT_SETS} distinct input sets ({INPUT_SETS * 3 * seq_len(w) * w['H'] * w['D'] * 2 // world >> 20} MiB per GPU) cycled over blocks: larger than the 126 MB L2",
         },
         "per_gpu_tflops": round(value / world, 2),
@@ -455,6 +479,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: Ulysses exchange by peer stores fused into the kernels, or by NCCL all-to-all")
+    ap.add_argument("--no-graph", action="store_true", help="N > 1: launch kernel by kernel instead of replaying a graph")
     ap.add_argument("--profile", action="store_true",
                     help="short run for ncu: device-resident leg only (no host-buffer leg, no CPU baseline)")
     args = ap.parse_args()

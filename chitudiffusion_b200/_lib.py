@@ -90,7 +90,7 @@ def load() -> ctypes.CDLL:
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, _vp,
     ]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
-    lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp]
+    lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]
     _lib = lib
     return lib
 

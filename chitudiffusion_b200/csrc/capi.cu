@@ -371,7 +371,7 @@ int chitu_b200_qk_norm_rope_scatter(const void* x, int in_dtype, int64_t x_row_s
                            out_strides, heads_per_group, B, S, H, D, round_mid, stream);
 }
 
-int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int epoch, int* status, void* stream) {
+int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream) {
   if (!flag_ptrs || world < 1 || world > 8 || rank < 0 || rank >= world)
     return fail(CHITU_E_INVALID, "peer_barrier: need 1..8 ranks and a rank inside the group");
   chitu::PeerBarrierParams p;
@@ -380,7 +380,6 @@ int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int epoc
     if (!p.flags[i]) return fail(CHITU_E_INVALID, "peer_barrier: null flag array for rank %d", i);
   p.rank = rank;
   p.world = world;
-  p.epoch = epoch;
   p.status = status;
   p.timeout_cycles = 1ll << 31;  // about a second
   chitu::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -285,30 +285,39 @@ strided_copy_kernel(const uint8_t* __restrict__ src, uint4* __restrict__ dst, lo
 // status word is set and the kernel returns.
 // ----------------------------------------------------------------------------
 struct PeerBarrierParams {
-  int* flags[8];  // flags[i]: base of rank i's flag array (world ints), mapped into this process
-  int rank, world, epoch;
+  int* flags[8];  // flags[i]: base of rank i's flag array (world + 1 ints), mapped into this process
+  int rank, world;
   int* status;
   long long timeout_cycles;
 };
 
+// The epoch lives on the device (slot `world` of the local flag array) and advances by one per
+// barrier on every rank, so the kernel takes no per-call argument and can be replayed from a
+// CUDA graph.
 __global__ void peer_barrier_kernel(const PeerBarrierParams p) {
   const int i = threadIdx.x;
-  if (i >= p.world) return;
-  __threadfence_system();  // order this stream's earlier peer stores before the flag
-  int* remote = p.flags[i] + p.rank;
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(p.epoch) : "memory");
-  const int* mine = p.flags[p.rank] + i;
-  const long long t0 = clock64();
-  int seen;
-  unsigned spins = 0;
-  while (true) {
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-    if (seen - p.epoch >= 0) break;  // epochs only grow (wrap-safe comparison)
-    if ((++spins & 0xff) == 0 && clock64() - t0 > p.timeout_cycles) {
-      if (p.status) atomicCAS(p.status, 0, 5);
-      break;
+  int* counter = p.flags[p.rank] + p.world;
+  const int epoch = *counter + 1;
+  __syncwarp();
+  if (i < p.world) {
+    __threadfence_system();  // order this stream's earlier peer stores before the flag
+    int* remote = p.flags[i] + p.rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const int* mine = p.flags[p.rank] + i;
+    const long long t0 = clock64();
+    int seen;
+    unsigned spins = 0;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (seen - epoch >= 0) break;  // epochs only grow (wrap-safe comparison)
+      if ((++spins & 0xff) == 0 && clock64() - t0 > p.timeout_cycles) {
+        if (p.status) atomicCAS(p.status, 0, 5);
+        break;
+      }
     }
   }
+  __syncwarp();
+  if (i == 0) *counter = epoch;
 }
 
 }  // namespace chitu

@@ -256,10 +256,10 @@ def attn_fwd_scatter(
     _lib.check(rc, "attn_fwd_scatter")
 
 
-def peer_barrier(flag_ptrs: Sequence[int], rank: int, world: int, epoch: int, device: torch.device) -> None:
+def peer_barrier(flag_ptrs: Sequence[int], rank: int, world: int, device: torch.device) -> None:
     """Enqueue the bounded cross-GPU barrier on the current stream; see ``chitu_b200_peer_barrier``."""
     lib = _lib.load()
     with torch.cuda.device(device):
-        rc = lib.chitu_b200_peer_barrier(_lib.ptr_array(flag_ptrs), int(rank), int(world), int(epoch),
+        rc = lib.chitu_b200_peer_barrier(_lib.ptr_array(flag_ptrs), int(rank), int(world),
                                          status_word(device).data_ptr(), _stream_ptr(device))
     _lib.check(rc, "peer_barrier")

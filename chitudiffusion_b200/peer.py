@@ -61,7 +61,6 @@ class PeerUlysses:
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         torch.cuda.synchronize(device)
         dist.barrier(group=group.gpu_group)  # every flag array is zero before anyone signals
-        self.epoch = 0
 
         def view(off, shape):
             n = 1
@@ -83,8 +82,7 @@ class PeerUlysses:
         return [p + off + self._row0 for p in self.ptrs]
 
     def barrier(self) -> None:
-        self.epoch += 1
-        ops.peer_barrier(self.flag_ptrs, self.rank, self.U, self.epoch, self.device)
+        ops.peer_barrier(self.flag_ptrs, self.rank, self.U, self.device)
 
     def scatter_plain(self, x: torch.Tensor, which: str = "v") -> None:
         """``x [B, s, H*D]`` (or ``[B,s,H,D]``) 16-bit: copy each head group to its owner."""

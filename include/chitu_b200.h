@@ -140,9 +140,11 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
  * chitu_b200_attn_fwd_scatter: as chitu_b200_attn_fwd, but query row r is written to
  *   out_ptrs[r / rows_per_dest] at element offset
  *   batch*dest_batch_stride + (r % rows_per_dest)*dest_row_stride + dest_head_offset + head*128 + d.
- * chitu_b200_peer_barrier: every rank enqueues it with the same, growing epoch; flag_ptrs[i] is
- *   rank i's array of `world` int32 flags (zero-initialised) mapped into this process.  The wait is
- *   bounded (about a second); on timeout *status is set to 5 and the kernel returns.
+ * chitu_b200_peer_barrier: every rank enqueues it the same number of times; flag_ptrs[i] is rank i's
+ *   array of `world + 1` int32 (zero-initialised: one flag per peer, then the local epoch counter)
+ *   mapped into this process.  The epoch is kept on the device, so the call can be replayed from a
+ *   CUDA graph.  The wait is bounded (about a second); on timeout *status is set to 5 and the kernel
+ *   returns.
  */
 int chitu_b200_qk_norm_rope_scatter(const void* x, int in_dtype, int64_t x_row_stride, const void* weight,
                                     int w_dtype, float eps, int norm_mode, int rope_mode, const float* rope_table,
@@ -154,7 +156,7 @@ int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, voi
                                 int64_t dest_head_offset, float* lse, int B, int Sq, int Sk, int H, int D,
                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                                 float softmax_scale, int dtype, int* status, void* stream);
-int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int epoch, int* status, void* stream);
+int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream);
 
 #ifdef __cplusplus
 }
