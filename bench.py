@@ -148,16 +148,15 @@ def joint_ids(w):
 
 
 def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
-    """Seeded q/k/v projection outputs [1, s_local, H*D] bf16 (the same global tensors on every rank)."""
+    """Seeded q/k/v projection outputs of this rank's token shard, [1, s_local, H*D] bf16."""
     S, C = seq_len(w), w["H"] * w["D"]
-    pos = local_positions(w, rank, world)
+    s_local = S // world
     sets = []
     for i in range(n_sets):
-        gen = torch.Generator().manual_seed(seed * 1000 + i)
+        gen = torch.Generator().manual_seed((seed * 1000 + i) * 64 + rank)
         trip = []
         for _ in range(3):
-            full = torch.randn(1, S, C, generator=gen, dtype=torch.float32).to(torch.bfloat16)
-            t = full[:, pos].contiguous()
+            t = torch.randn(1, s_local, C, generator=gen, dtype=torch.float32).to(torch.bfloat16)
             if pinned:
                 t = t.pin_memory()
             elif device is not None:
@@ -173,7 +172,7 @@ def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
 class Pipeline:
     """Per-rank block function: pre-attention pass + (context-parallel) attention."""
 
-    def __init__(self, w, rank, world, device, exchange="peer"):
+    def __init__(self, w, rank, world, device, exchange="peer", init_groups=True):
         from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
         from chitudiffusion_b200.context_parallel import B200ContextParallel
 
@@ -183,7 +182,8 @@ class Pipeline:
         self.attn = self.backend
         if world > 1:
             up = max(u for u in (8, 4, 2, 1) if u <= world and self.H % u == 0 and world % u == 0)
-            comm.initialize_diffusion_parallel_groups(1, world, up)
+            if init_groups:
+                comm.initialize_diffusion_parallel_groups(1, world, up)
             self.attn = B200ContextParallel(self.backend, up, cp_backend="ucp")
             self.parallelism = f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else "")
             self.peer = None
@@ -249,6 +249,42 @@ class Pipeline:
         return out
 
 
+def measure_extra(name, layers, rank, world, device, exchange, sync, dist):
+    """Device-resident throughput of a few layers of a second workload (no host leg): the
+    compute-bound Wan2.1-14B 720p shape, whose scaling the latency-bound default cannot show."""
+    w = dict(WORKLOADS[name], blocks=layers)
+    pipe = Pipeline(w, rank, world, device, exchange=exchange, init_groups=False)
+    s_local, C = seq_len(w) // world, w["H"] * w["D"]
+    gen = torch.Generator(device=device).manual_seed(77 + rank)
+    sets = [tuple(torch.randn(1, s_local, C, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+                  for _ in range(3))]
+    pipe.step(sets)
+    fn = lambda: pipe.step(sets)  # noqa: E731
+    if world > 1 and pipe.peer is not None:
+        sync()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            pipe.step(sets)
+        fn = graph.replay
+    sync()
+    steps = 2
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fn()
+    t1.record()
+    sync()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_layer = float(ms.item()) / (steps * layers)
+    tf = flops_per_block(w) / (ms_layer * 1e-3) / 1e12
+    return {"workload": name, "seq_len": seq_len(w), "heads": w["H"], "layers_timed": layers, "steps": steps,
+            "ms_per_layer": round(ms_layer, 3), "value": round(tf, 1), "unit": "TFLOP/s",
+            "per_gpu_tflops": round(tf / world, 1), "parallelism": pipe.parallelism,
+            "input": "one device-generated q/k/v set (2.3 GB, larger than L2)"}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -268,7 +304,7 @@ def run_ours(args):
         raise ValueError("sequence not divisible by the number of GPUs")
     pipe = Pipeline(w, rank, world, device, exchange=args.exchange)
     dev_sets = make_inputs(w, rank, world, seed=1, n_sets=INPUT_SETS, device=device)
-    host_sets = make_inputs(w, rank, world, seed=1, n_sets=2, device=None, pinned=True)
+    host_sets = make_inputs(w, rank, world, seed=1, n_sets=0 if args.profile else 2, device=None, pinned=True)
     e2e_dev = [tuple(torch.empty_like(t, device=device) for t in trip) for trip in host_sets]
     s_local = dev_sets[0][0].shape[1]
     out_host = torch.empty((1, s_local, w["H"], w["D"]), dtype=torch.bfloat16).pin_memory()
@@ -316,9 +352,10 @@ def run_ours(args):
         step_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(step_graph):
             pipe.step(dev_sets)
-        e2e_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(e2e_graph):
-            e2e_out[0] = pipe.step(e2e_dev)
+        if not args.profile:
+            e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(e2e_graph):
+                e2e_out[0] = pipe.step(e2e_dev)
         sync()
     pipe.launches = 0
     pipe.step(dev_sets)
@@ -341,6 +378,10 @@ def run_ours(args):
         for _ in range(max(1, min(args.warmup, 3))):
             e2e_step()
         e2e_ms = timed_region(e2e_step, args.steps)
+
+    extra = None
+    if args.workload == DEFAULT_WORKLOAD and not args.profile and not args.no_extra:
+        extra = measure_extra("wan14b-720p-81f", 4, rank, world, device, args.exchange, sync, dist)
 
     from chitudiffusion_b200 import ops
 
@@ -389,6 +430,8 @@ def run_ours(args):
         "gpu_launches": launches,
         "roofline": roof,
     }
+    if extra is not None:
+        line["also"] = [extra]
     if world == 1 and not args.profile:
         line["cpu_baseline"] = cpu_baseline(w, repeats=3)
     if args.profile:
@@ -479,6 +522,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: Ulysses exchange by peer stores fused into the kernels, or by NCCL all-to-all")
+    ap.add_argument("--no-extra", action="store_true", help="skip the second (Wan2.1-14B 720p) workload")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch kernel by kernel instead of replaying a graph")
     ap.add_argument("--profile", action="store_true",
                     help="short run for ncu: device-resident leg only (no host-buffer leg, no CPU baseline)")
