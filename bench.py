@@ -50,7 +50,7 @@ INPUT_SETS = 4  # distinct q/k/v projection sets cycled over the blocks: 4 x 85 
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # DRAM bytes per attention launch of the default workload, from the ncu capture summarised in
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured for a workload.
-NCU_TRAFFIC_BYTES = {"flux1-dev-1024-joint-attn": None}
+NCU_TRAFFIC_BYTES = {"flux1-dev-1024-joint-attn": 93.8e6}
 
 
 def seq_len(w):
