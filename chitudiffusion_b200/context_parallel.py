@@ -21,6 +21,7 @@ What differs is the schedule, not the result:
 
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -75,6 +76,10 @@ class B200ContextParallel:
         self._merger_factory = merger_factory or _KernelMerger
         self._comm_stream: Optional[torch.cuda.Stream] = None
         self._graph_cache: dict = {}
+        # pure-Ulysses exchange over peer-mapped memory instead of NCCL all-to-all (CUDA, one node,
+        # at most 8 ranks); "nccl" keeps the collective form
+        self.ulysses_exchange = os.environ.get("CHITU_B200_ULYSSES_EXCHANGE", "peer").strip().lower()
+        self._peer_cache: dict = {}
 
     # ------------------------------------------------------------------ knobs
     @staticmethod
@@ -179,7 +184,36 @@ class B200ContextParallel:
                 g.p2p_wait()
         return nk, nv, done
 
+    def peer_exchange(self, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device):
+        """Cached peer-store exchange for one problem shape (collective on first use: every rank must call it)."""
+        from .peer import PeerUlysses
+
+        key = (B, s, H, D, dtype, str(device))
+        px = self._peer_cache.get(key)
+        if px is None:
+            u, _ = self._split()
+            px = PeerUlysses(self._up_group_lookup(u), B, s, H, D, dtype, device)
+            self._peer_cache[key] = px
+        return px
+
+    def _use_peer(self, q, k, u: int, r: int, kw: dict) -> bool:
+        return (
+            self.ulysses_exchange == "peer" and r == 1 and 1 < u <= 8 and q.is_cuda
+            and getattr(self.attn, "impl", "") == "b200" and q.shape == k.shape and q.shape[2] % u == 0
+            and q.dtype in (torch.bfloat16, torch.float16) and not kw["causal"] and not kw["dropout_p"]
+            and tuple(kw["window_size"]) == (-1, -1)
+        )
+
     def _cp_forward(self, q, k, v, u: int, r: int, kw: dict) -> torch.Tensor:
+        if self._use_peer(q, k, u, r, kw):
+            B, s, H, D = q.shape
+            px = self.peer_exchange(B, s, H, D, q.dtype, q.device)
+            px.scatter_plain(q, "q")
+            px.scatter_plain(k, "k")
+            px.scatter_plain(v, "v")
+            # the exchange buffer is reused by the next call: hand back a copy, as the reference
+            # hands back a fresh tensor
+            return px.attention(kw["softmax_scale"]).clone()
         up_group = self._up_group_lookup(u) if u > 1 else None
         if up_group is not None:
             q = up_group.all_to_all(q, 2, 1)

@@ -41,14 +41,19 @@ def main():
     ql, kl, vl = (t[:, sl].contiguous().to(dev) for t in (q, k, v))
     backend = B200AttnBackend("b200")
     results = {}
-    layouts = [("ulysses", world, "ucp"), ("ring", 1, "ucp"), ("agcp", world, "agcp")]
+    layouts = [("ulysses_peer", world, "ucp"), ("ulysses_nccl", world, "ucp"), ("ring", 1, "ucp"),
+               ("agcp", world, "agcp")]
     if world >= 4:
         layouts.append(("usp", world // 2, "ucp"))
     for name, up, cpb in layouts:
         comm.destroy_diffusion_parallel_groups()
         comm.initialize_diffusion_parallel_groups(1, world, up)
         wrapper = B200ContextParallel(backend, up, cp_backend=cpb)
+        if name.endswith("_nccl"):
+            wrapper.ulysses_exchange = "nccl"
         out = wrapper(ql, kl, vl)[0]
+        if name == "ulysses_peer":  # second call reuses the exchange buffers
+            out = wrapper(ql, kl, vl)[0]
         results[name] = rel_err(out, full[:, sl])
 
     # peer-store exchange: norm + rotary pre-pass scattered to the owners, attention scattered back
