@@ -27,6 +27,8 @@ EXPORTS = (
     "chitu_b200_qk_norm_rope_scatter",
     "chitu_b200_attn_fwd_scatter",
     "chitu_b200_peer_barrier",
+    "chitu_b200_attn_splitkv_workspace_bytes",
+    "chitu_b200_attn_fwd_splitkv",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -87,7 +89,15 @@ def load() -> ctypes.CDLL:
     lib.chitu_b200_attn_fwd_scatter.argtypes = [
         _vp, _vp, _vp, _vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp,
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, _vp,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp,
+    ]
+    lib.chitu_b200_attn_splitkv_workspace_bytes.restype = ctypes.c_int64
+    lib.chitu_b200_attn_splitkv_workspace_bytes.argtypes = [ctypes.c_int] * 5
+    lib.chitu_b200_attn_fwd_splitkv.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_splitkv.argtypes = [
+        _vp, _vp, _vp, _vp, _vp,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp,
     ]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]

@@ -55,6 +55,13 @@ struct AttnParams {
   int n_dest;
   int rows_per_dest;
   long long dest_batch_bytes, dest_row_bytes, dest_head_bytes;
+  // Split over keys (under-filled grids): blockIdx.z = batch * n_splits + split; split s takes
+  // key tiles [s * tiles_per_split, (s+1) * tiles_per_split).  With n_splits > 1 each CTA writes a
+  // normalised fp32 partial result and its log-sum-exp to scratch memory for the combine kernel:
+  //   part_o [n_splits][B][Sq][H][128] fp32,  part_lse [n_splits][B][H][Sq] fp32 (natural log)
+  int n_splits, tiles_per_split;
+  float* part_o;
+  float* part_lse;
 #ifdef CHITU_ATTN_TIMING
   long long* dbg;   // per-phase clock totals of CTA 0 (development builds only)
 #endif
@@ -121,8 +128,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * (kQTiles * kTileM);
   const int head = blockIdx.y;
-  const int batch = blockIdx.z;
-  const int n_kv = (p.Sk + kTileN - 1) / kTileN;
+  const int batch = blockIdx.z / p.n_splits;
+  const int split = blockIdx.z - batch * p.n_splits;
+  const int n_kv_total = (p.Sk + kTileN - 1) / kTileN;
+  const int kv0 = split * p.tiles_per_split;                      // first key tile of this CTA
+  const int n_kv = min(p.tiles_per_split, n_kv_total - kv0);      // >= 1 (the host sizes the splits)
   const int n_qt = (q0 + kTileM < p.Sq) ? 2 : 1;
 
   if (threadIdx.x == 0) {
@@ -175,7 +185,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (round > 0) mbar_wait(bar_kv_empty + 8 * slot, (round - 1) & 1, abort_flag, p.status, kDevTimeoutLoad);
       if (lane == 0) {
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
-        const int row = (i >> 1) * kTileN;
+        const int row = (kv0 + (i >> 1)) * kTileN;
         const uint32_t dst = kv_smem + slot * kTileBytes;
         const uint32_t bar = bar_kv_full + 8 * slot;
         mbar_arrive_expect_tx(bar, kTileBytes);
@@ -295,7 +305,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t t_s = tmem_base + lane_base + t * kTileN;
       const uint32_t t_o = tmem_base + lane_base + 2 * kTileN + t * kHeadDim;
       const float sl2 = p.scale_log2;
-      const int tail_valid = p.Sk - (n_kv - 1) * kTileN;  // 1..128 valid keys in the last tile
+      const int tail_valid = p.Sk - (n_kv_total - 1) * kTileN;  // 1..128 valid keys in the last tile of K
       float m_used = -INFINITY;
       float l_sum = 0.f;
 
@@ -315,7 +325,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // Row of 128 scores into registers, 32 columns per load; the load of chunk
         // c+1 is in flight while the running maximum of chunk c is taken.
         uint32_t s[4][32];
-        const bool last_tile = (j == n_kv - 1 && tail_valid < kTileN);
+        const bool last_tile = (kv0 + j == n_kv_total - 1 && tail_valid < kTileN);
         float mx0 = -INFINITY, mx1 = -INFINITY;
         tmem_ld32(t_s, s[0]);
 #pragma unroll
@@ -422,6 +432,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_ptrs[dest]) + batch * p.dest_batch_bytes +
                                        local_row * p.dest_row_bytes + p.dest_head_bytes + head * (kHeadDim * 2));
       }
+      if (p.n_splits > 1) {
+        // partial result of this key range: normalised fp32 rows + log-sum-exp for the combine kernel
+        float4* pdst = reinterpret_cast<float4*>(
+            p.part_o + (((static_cast<size_t>(split) * p.B + batch) * p.Sq + row) * p.H + head) * kHeadDim);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_o + c * 32, o);
+          tmem_wait_ld();
+          if (row < p.Sq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              pdst[c * 8 + (i >> 2)] = make_float4(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l,
+                                                   __uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+          }
+        }
+        if (row < p.Sq)
+          p.part_lse[((static_cast<size_t>(split) * p.B + batch) * p.H + head) * p.Sq + row] =
+              (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
+      } else {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -439,7 +469,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-      if (p.lse != nullptr && row < p.Sq) {
+      }
+      if (p.n_splits == 1 && p.lse != nullptr && row < p.Sq) {
         p.lse[(static_cast<size_t>(batch) * p.H + head) * p.Sq + row] =
             (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
       }

@@ -112,9 +112,22 @@ struct OutScatter {
   int64_t batch_stride = 0, row_stride = 0, head_offset = 0;  // elements
 };
 
+struct KeySplit {
+  int n_splits = 1;
+  void* workspace = nullptr;
+  int64_t workspace_bytes = 0;
+};
+
+int64_t splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits) {
+  if (n_splits <= 1) return 0;
+  const int64_t rows = static_cast<int64_t>(B) * Sq * H;
+  return static_cast<int64_t>(n_splits) * rows * (static_cast<int64_t>(D) + 1) * 4;  // fp32 rows + one LSE each
+}
+
 int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const OutScatter& sc, float* lse, int B,
                   int Sq, int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
-                  const int64_t* v_strides, float softmax_scale, int dtype, int* status, void* stream) {
+                  const int64_t* v_strides, float softmax_scale, int dtype, int* status, void* stream,
+                  const KeySplit& ks = KeySplit{}) {
   if (!q || !k || !v || (!out && sc.n_dest == 0) || !q_strides || !k_strides || !v_strides)
     return fail(CHITU_E_INVALID, "attn_fwd: null pointer argument");
   if (sc.n_dest != 0) {
@@ -136,6 +149,21 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   if (sc.n_dest == 0 && (reinterpret_cast<uintptr_t>(out) & 15))
     return fail(CHITU_E_INVALID, "attn_fwd: out must be 16-byte aligned");
   if (H > 65535 || B > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: H and B must be below 65536");
+
+  const int n_kv_tiles = (Sk + chitu::kTileN - 1) / chitu::kTileN;
+  int n_splits = ks.n_splits;
+  if (n_splits < 1 || n_splits > 64) return fail(CHITU_E_INVALID, "attn_fwd: n_splits must be in 1..64");
+  if (n_splits > n_kv_tiles) n_splits = n_kv_tiles;
+  int tiles_per_split = (n_kv_tiles + n_splits - 1) / n_splits;
+  n_splits = (n_kv_tiles + tiles_per_split - 1) / tiles_per_split;  // no empty split
+  if (n_splits > 1) {
+    if (!ks.workspace || (reinterpret_cast<uintptr_t>(ks.workspace) & 15))
+      return fail(CHITU_E_INVALID, "attn_fwd: split over keys needs a 16-byte aligned workspace");
+    if (ks.workspace_bytes < splitkv_workspace_bytes(B, Sq, H, D, n_splits))
+      return fail(CHITU_E_INVALID, "attn_fwd: workspace too small (%lld bytes needed)",
+                  (long long)splitkv_workspace_bytes(B, Sq, H, D, n_splits));
+    if (static_cast<int64_t>(B) * n_splits > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: B * n_splits too large");
+  }
 
   CUtensorMap tq, tk, tv;
   int rc;
@@ -159,6 +187,10 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   p.dest_row_bytes = sc.row_stride * 2;
   p.dest_head_bytes = sc.head_offset * 2;
   for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < sc.n_dest ? sc.ptrs[i] : nullptr;
+  p.n_splits = n_splits;
+  p.tiles_per_split = tiles_per_split;
+  p.part_o = static_cast<float*>(ks.workspace);
+  p.part_lse = p.part_o ? p.part_o + static_cast<size_t>(n_splits) * B * Sq * H * D : nullptr;
 #ifdef CHITU_ATTN_TIMING
   p.dbg = g_dbg;
 #endif
@@ -174,7 +206,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   });
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
 
-  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B);
+  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B * n_splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p.is_fp16)
     chitu::attn_fwd_kernel<true><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
@@ -182,6 +214,29 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     chitu::attn_fwd_kernel<false><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attn_fwd: launch");
+  if (n_splits > 1) {
+    chitu::SplitCombineParams c;
+    c.part_o = p.part_o;
+    c.part_lse = p.part_lse;
+    c.out = out;
+    c.lse = lse;
+    c.n = n_splits;
+    c.B = B;
+    c.S = Sq;
+    c.H = H;
+    c.D = D;
+    c.out_dtype = dtype;
+    c.n_dest = sc.n_dest;
+    c.rows_per_dest = sc.rows_per_dest;
+    c.dest_batch_bytes = p.dest_batch_bytes;
+    c.dest_row_bytes = p.dest_row_bytes;
+    c.dest_head_bytes = p.dest_head_bytes;
+    for (int i = 0; i < 8; ++i) c.out_ptrs[i] = p.out_ptrs[i];
+    const long long rows = static_cast<long long>(B) * Sq * H;
+    chitu::splitkv_combine_kernel<<<grid_for(rows, 8, 148 * 16), 256, 0, st>>>(c);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd: combine launch");
+  }
   return CHITU_OK;
 }
 
@@ -196,11 +251,32 @@ int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, 
                        softmax_scale, dtype, status, stream);
 }
 
+int64_t chitu_b200_attn_splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits) {
+  return splitkv_workspace_bytes(B, Sq, H, D, n_splits);
+}
+
+int chitu_b200_attn_fwd_splitkv(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq,
+                                int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
+                                const int64_t* v_strides, float softmax_scale, int dtype, int n_splits,
+                                void* workspace, int64_t workspace_bytes, int* status, void* stream) {
+  KeySplit ks;
+  ks.n_splits = n_splits;
+  ks.workspace = workspace;
+  ks.workspace_bytes = workspace_bytes;
+  return attn_fwd_impl(q, k, v, out, OutScatter{}, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides,
+                       softmax_scale, dtype, status, stream, ks);
+}
+
 int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
                                 int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
                                 int64_t dest_head_offset, float* lse, int B, int Sq, int Sk, int H, int D,
                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
-                                float softmax_scale, int dtype, int* status, void* stream) {
+                                float softmax_scale, int dtype, int n_splits, void* workspace,
+                                int64_t workspace_bytes, int* status, void* stream) {
+  KeySplit ks;
+  ks.n_splits = n_splits;
+  ks.workspace = workspace;
+  ks.workspace_bytes = workspace_bytes;
   OutScatter sc;
   sc.ptrs = out_ptrs;
   sc.n_dest = n_dest;
@@ -210,7 +286,7 @@ int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, voi
   sc.head_offset = dest_head_offset;
   if (n_dest <= 0) return fail(CHITU_E_INVALID, "attn_fwd_scatter: n_dest must be positive");
   return attn_fwd_impl(q, k, v, nullptr, sc, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides, softmax_scale,
-                       dtype, status, stream);
+                       dtype, status, stream, ks);
 }
 
 int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out, const float* block_lse, int B, int S,

@@ -57,6 +57,28 @@ def check_status(device: Optional[torch.device] = None) -> None:
         raise _lib.ChituB200Error(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
 
 
+_workspaces = {}
+NUM_SMS = 148
+
+
+def auto_key_splits(B: int, Sq: int, Sk: int, H: int) -> int:
+    """How many key ranges to run as separate CTAs so that a small grid still covers the SMs."""
+    ctas = -(-Sq // 256) * H * B
+    if ctas * 10 >= NUM_SMS * 7:  # already at least 0.7 of a wave
+        return 1
+    return max(1, min(-(-Sk // 128), NUM_SMS // ctas, 16))
+
+
+def splitkv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-device scratch for key-split partials, grown on demand and reused by later calls on the same stream."""
+    key = torch.device(device).index
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
 def attn_fwd(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -64,6 +86,7 @@ def attn_fwd(
     softmax_scale: Optional[float] = None,
     return_lse: bool = False,
     out: Optional[torch.Tensor] = None,
+    n_splits: Optional[int] = None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """``softmax(scale * q k^T) v`` for ``[B,S,H,128]`` bf16/fp16 tensors of any (16-byte aligned) strides.
 
@@ -92,12 +115,25 @@ def attn_fwd(
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if return_lse else None
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     lib = _lib.load()
+    if n_splits is None:
+        n_splits = auto_key_splits(B, Sq, Sk, H)
     with torch.cuda.device(q.device):
-        rc = lib.chitu_b200_attn_fwd(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
-            B, Sq, Sk, H, D, _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()),
-            scale, _DTYPES[q.dtype], status_word(q.device).data_ptr(), _stream_ptr(q.device),
-        )
+        if n_splits > 1:
+            need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
+            ws = splitkv_workspace(q.device, need)
+            rc = lib.chitu_b200_attn_fwd_splitkv(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                lse.data_ptr() if lse is not None else None, B, Sq, Sk, H, D, _lib.i64_array(q.stride()),
+                _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale, _DTYPES[q.dtype], int(n_splits),
+                ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream_ptr(q.device),
+            )
+        else:
+            rc = lib.chitu_b200_attn_fwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                lse.data_ptr() if lse is not None else None, B, Sq, Sk, H, D, _lib.i64_array(q.stride()),
+                _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale, _DTYPES[q.dtype],
+                status_word(q.device).data_ptr(), _stream_ptr(q.device),
+            )
     _lib.check(rc, "attn_fwd")
     return out, lse
 
@@ -237,6 +273,7 @@ def attn_fwd_scatter(
     dest_row_stride: int,
     dest_head_offset: int,
     softmax_scale: Optional[float] = None,
+    n_splits: Optional[int] = None,
 ) -> None:
     """Attention whose query row ``r`` is stored to ``out_ptrs[r // rows_per_dest]``; see ``chitu_b200_attn_fwd_scatter``."""
     _require_cuda(q, k, v)
@@ -246,12 +283,20 @@ def attn_fwd_scatter(
         raise NotImplementedError("attention kernel takes bf16 or fp16 q/k/v of one dtype")
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     lib = _lib.load()
+    if n_splits is None:
+        n_splits = auto_key_splits(B, Sq, Sk, H)
+    ws_ptr, ws_bytes = None, 0
+    if n_splits > 1:
+        need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
+        ws = splitkv_workspace(q.device, need)
+        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         rc = lib.chitu_b200_attn_fwd_scatter(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr_array(out_ptrs), len(out_ptrs), int(rows_per_dest),
             int(dest_batch_stride), int(dest_row_stride), int(dest_head_offset), None, B, Sq, Sk, H, D,
             _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale,
-            _DTYPES[q.dtype], status_word(q.device).data_ptr(), _stream_ptr(q.device),
+            _DTYPES[q.dtype], int(n_splits), ws_ptr, ws_bytes, status_word(q.device).data_ptr(),
+            _stream_ptr(q.device),
         )
     _lib.check(rc, "attn_fwd_scatter")
 

@@ -64,6 +64,22 @@ int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, 
                         float softmax_scale, int dtype, int* status, void* stream);
 
 /*
+ * The same attention with the keys split into n_splits ranges that run as separate CTAs (for grids
+ * that would leave most of the 148 SMs idle: few query rows or few heads per GPU); a second kernel
+ * merges the partial results.  Same reference call sites as chitu_b200_attn_fwd.  The split count is
+ * clamped to the number of 128-key tiles; with one split no workspace is touched.
+ *
+ *   workspace        device scratch of at least chitu_b200_attn_splitkv_workspace_bytes(...) bytes,
+ *                    16-byte aligned: fp32 partial rows [n_splits][B][Sq][H][D] then their
+ *                    log-sum-exps [n_splits][B][H][Sq].  Contents need no initialisation.
+ */
+int64_t chitu_b200_attn_splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits);
+int chitu_b200_attn_fwd_splitkv(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq,
+                                int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
+                                const int64_t* v_strides, float softmax_scale, int dtype, int n_splits,
+                                void* workspace, int64_t workspace_bytes, int* status, void* stream);
+
+/*
  * Fold one partial attention result into the running (out, lse) pair:
  *   out <- out - sigmoid(lse_b - lse) * (out - out_b),  lse <- lse - logsigmoid(lse - lse_b)
  * or, when `first` is non-zero, initialise them from the block.
@@ -139,7 +155,8 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
  *   With norm_mode 2 and rope_mode 0 it is the plain scatter used for v.
  * chitu_b200_attn_fwd_scatter: as chitu_b200_attn_fwd, but query row r is written to
  *   out_ptrs[r / rows_per_dest] at element offset
- *   batch*dest_batch_stride + (r % rows_per_dest)*dest_row_stride + dest_head_offset + head*128 + d.
+ *   batch*dest_batch_stride + (r % rows_per_dest)*dest_row_stride + dest_head_offset + head*128 + d;
+ *   n_splits / workspace as in chitu_b200_attn_fwd_splitkv (the merge kernel then does the scattered store).
  * chitu_b200_peer_barrier: every rank enqueues it the same number of times; flag_ptrs[i] is rank i's
  *   array of `world + 1` int32 (zero-initialised: one flag per peer, then the local epoch counter)
  *   mapped into this process.  The epoch is kept on the device, so the call can be replayed from a
@@ -155,7 +172,8 @@ int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, voi
                                 int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
                                 int64_t dest_head_offset, float* lse, int B, int Sq, int Sk, int H, int D,
                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
-                                float softmax_scale, int dtype, int* status, void* stream);
+                                float softmax_scale, int dtype, int n_splits, void* workspace,
+                                int64_t workspace_bytes, int* status, void* stream);
 int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream);
 
 #ifdef __cplusplus
