@@ -29,6 +29,7 @@ EXPORTS = (
     "chitu_b200_peer_barrier",
     "chitu_b200_attn_splitkv_workspace_bytes",
     "chitu_b200_attn_fwd_splitkv",
+    "chitu_b200_attn_fwd_splitkv_static",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -98,6 +99,12 @@ def load() -> ctypes.CDLL:
         _vp, _vp, _vp, _vp, _vp,
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp,
+    ]
+    lib.chitu_b200_attn_fwd_splitkv_static.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_splitkv_static.argtypes = [
+        _vp, _vp, _vp, _vp, _vp,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, _vp,
     ]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]

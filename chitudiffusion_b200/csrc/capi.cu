@@ -485,3 +485,74 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
 }
 
 }  // extern "C"
+
+// ----------------------------------------------------------------------------
+// Key-split attention for callers that may not allocate.
+//
+// Some hosts of this library cannot hand over a scratch buffer: an inference server that gave
+// every free byte of device memory to its own pool at start-up has nothing left to allocate from,
+// and a plugin called from inside somebody else's step function has no business calling
+// cudaMalloc there (it may fail, and it stalls every stream of the device while it runs).  For
+// them the scratch of the key-split path lives in a fixed array inside the library image.
+//
+// The array below is a DEVICE symbol.  In host code its name is only a handle: the usable device
+// address comes from cudaGetSymbolAddress, looked up once per device with that device current.
+// ----------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB, resident on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the scratch array on the CURRENT device (looked up on first use).
+int static_scratch_for_current_device(void** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_splitkv_static: cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_splitkv_static: device index %d", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_splitkv_static: cudaGetSymbolAddress");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *ptr = g_static_scratch_ptr[dev];
+  return CHITU_OK;
+}
+
+}  // namespace
+
+extern "C" int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, const void* v, void* out, float* lse,
+                                                  int B, int Sq, int Sk, int H, int D, const int64_t* q_strides,
+                                                  const int64_t* k_strides, const int64_t* v_strides,
+                                                  float softmax_scale, int dtype, int n_splits, int* status,
+                                                  void* stream) {
+  if (n_splits < 1 || n_splits > 64) return fail(CHITU_E_INVALID, "attn_fwd_splitkv_static: n_splits must be in 1..64");
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0 || D <= 0)
+    return fail(CHITU_E_INVALID, "attn_fwd_splitkv_static: B, Sq, Sk, H, D must be positive");
+  // the same clamping the general path applies, so the size check below is the real requirement
+  const int tiles = (Sk + chitu::kTileN - 1) / chitu::kTileN;
+  int n = n_splits < tiles ? n_splits : tiles;
+  const int per = (tiles + n - 1) / n;
+  n = (tiles + per - 1) / per;
+  const int64_t need = splitkv_workspace_bytes(B, Sq, H, D, n);
+  if (need > static_cast<int64_t>(kStaticScratchBytes))
+    return fail(CHITU_E_INVALID,
+                "attn_fwd_splitkv_static: %d key ranges of [%d x %d x %d x %d] need %lld bytes of scratch, the built-in "
+                "array holds %lld; use fewer ranges or chitu_b200_attn_fwd_splitkv with your own workspace",
+                n, B, Sq, H, D, (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != CHITU_OK) return rc;
+  KeySplit ks;
+  ks.n_splits = n_splits;
+  ks.workspace = scratch;
+  ks.workspace_bytes = static_cast<int64_t>(kStaticScratchBytes);
+  return attn_fwd_impl(q, k, v, out, OutScatter{}, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides,
+                       softmax_scale, dtype, status, stream, ks);
+}
+

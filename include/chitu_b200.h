@@ -80,6 +80,32 @@ int chitu_b200_attn_fwd_splitkv(const void* q, const void* k, const void* v, voi
                                 void* workspace, int64_t workspace_bytes, int* status, void* stream);
 
 /*
+ * chitu_b200_attn_fwd_splitkv for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: ChituDiffusion always runs inside torch's allocator.)
+ *
+ * Meant for hosts that have no scratch buffer to give: a server that committed all free device
+ * memory to its own pool at start-up, or a plugin invoked in the middle of another runtime's step,
+ * where calling cudaMalloc is off the table (it can fail, and it stalls the whole device while it
+ * runs).  The partial results live in a 32 MiB array built into the library image, present on every
+ * GPU that loads the library for as long as the process lives.  This call, and everything it
+ * reaches, calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *   - Limit: the key-split scratch, chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n) bytes for the
+ *     effective split count n, must fit in 32 MiB; larger requests return CHITU_E_INVALID with the sizes
+ *     in chitu_b200_last_error().  Arguments and results are those of chitu_b200_attn_fwd_splitkv.
+ *   - First call on a device: looks up the array's device address (cudaGetSymbolAddress, with the
+ *     caller's current device current) and caches it.  Make that first call before starting any
+ *     stream capture on that device.
+ *   - One array per GPU, shared by every call: it keeps the previous call's partial results and nothing
+ *     in it needs clearing, because each call overwrites every row it later reads.  Two calls that run
+ *     at the same time on one GPU (different streams, or different threads) race on it; serialise them.
+ */
+int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                                       int Sq, int Sk, int H, int D, const int64_t* q_strides,
+                                       const int64_t* k_strides, const int64_t* v_strides, float softmax_scale,
+                                       int dtype, int n_splits, int* status, void* stream);
+
+/*
  * Fold one partial attention result into the running (out, lse) pair:
  *   out <- out - sigmoid(lse_b - lse) * (out - out_b),  lse <- lse - logsigmoid(lse - lse_b)
  * or, when `first` is non-zero, initialise them from the block.
