@@ -214,22 +214,16 @@ class Pipeline:
     def block(self, qp, kp, vp, timed=False):
         if self.peer is not None:
             px = self.peer
-            place = dict(out_strides=px.gather_strides, heads_per_group=px.hc)
-            if self.w["kind"] == "joint":
-                self.pre.one(qp, self.nq, out_ptrs=px.dest_ptrs("q"), **place)
-                self.pre.one(kp, self.nk, out_ptrs=px.dest_ptrs("k"), **place)
-            else:
-                self.pre.one(qp, self.nq, self.w["grid"], out_ptrs=px.dest_ptrs("q"), **place)
-                self.pre.one(kp, self.nk, self.w["grid"], out_ptrs=px.dest_ptrs("k"), **place)
-            px.scatter_plain(vp, "v")
+            grid = self.w.get("grid", (0, 0, 0))
+            px.scatter_qkv(self.pre.jobs(qp, kp, self.nq, self.nk), vp, **self.pre.batch_args(px.s, grid))
             out = px.attention()
-            self.launches += 6  # 3 scatter stores, attention, 2 barriers
+            self.launches += 4  # fused q/k/v pre-pass + scatter, attention, 2 barriers
             return out
         if self.w["kind"] == "joint":
             q, k, v = self.pre(qp, kp, vp, self.nq, self.nk)
         else:
             q, k, v = self.pre(qp, kp, vp, self.nq, self.nk, self.w["grid"])
-        self.launches += 2
+        self.launches += 1  # q and k share one pre-attention launch
         if timed and self.world == 1:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

@@ -30,6 +30,7 @@ EXPORTS = (
     "chitu_b200_attn_splitkv_workspace_bytes",
     "chitu_b200_attn_fwd_splitkv",
     "chitu_b200_attn_fwd_splitkv_static",
+    "chitu_b200_qk_norm_rope_batch",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -40,6 +41,16 @@ _vp = ctypes.c_void_p
 
 class ChituB200Error(RuntimeError):
     pass
+
+
+class NormRopeJob(ctypes.Structure):
+    """Mirror of ``chitu_b200_norm_rope_job``."""
+
+    _fields_ = [
+        ("x", ctypes.c_void_p), ("x_row_stride", ctypes.c_int64), ("weight", ctypes.c_void_p),
+        ("norm_mode", ctypes.c_int), ("rope_mode", ctypes.c_int), ("out", ctypes.c_void_p),
+        ("out_ptrs", ctypes.POINTER(ctypes.c_void_p)), ("n_out_ptrs", ctypes.c_int),
+    ]
 
 
 def load() -> ctypes.CDLL:
@@ -105,6 +116,12 @@ def load() -> ctypes.CDLL:
         _vp, _vp, _vp, _vp, _vp,
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, _vp,
+    ]
+    lib.chitu_b200_qk_norm_rope_batch.restype = ctypes.c_int
+    lib.chitu_b200_qk_norm_rope_batch.argtypes = [
+        ctypes.POINTER(NormRopeJob), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, _vp, ctypes.c_int,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int64, ctypes.c_int,
+        _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp,
     ]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]

@@ -312,104 +312,131 @@ int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out
 
 namespace {
 
-int qk_norm_rope_impl(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype, float eps,
-                      int norm_mode, int rope_mode, const float* rope_table, int table_rows, int gf, int gh, int gw,
-                      const int* axis_split, int64_t pos_offset, void* out, void* const* out_ptrs, int n_out_ptrs,
-                      int out_dtype, const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
-                      int round_mid, void* stream) {
-  if (!x || (!out && n_out_ptrs == 0) || !out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
-  if (n_out_ptrs != 0) {
-    if (n_out_ptrs < 0 || n_out_ptrs > 8 || !out_ptrs || heads_per_group <= 0 || n_out_ptrs * heads_per_group != H)
-      return fail(CHITU_E_INVALID, "qk_norm_rope: need one destination per head group (at most 8)");
-    for (int i = 0; i < n_out_ptrs; ++i)
-      if (!out_ptrs[i] || (reinterpret_cast<uintptr_t>(out_ptrs[i]) & 15))
-        return fail(CHITU_E_INVALID, "qk_norm_rope: destination %d null or not 16-byte aligned", i);
-  }
+struct NormRopeShared {
+  int in_dtype, w_dtype;
+  float eps;
+  const float* rope_table;
+  int table_rows, gf, gh, gw;
+  const int* axis_split;
+  int64_t pos_offset;
+  int out_dtype;
+  const int64_t* out_strides;
+  int heads_per_group, B, S, H, D, round_mid;
+};
+
+int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, const NormRopeShared& sh, void* stream) {
+  if (!jobs || n_jobs < 1 || n_jobs > 3) return fail(CHITU_E_INVALID, "qk_norm_rope: 1..3 jobs per launch");
+  if (!sh.out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+  const int B = sh.B, S = sh.S, H = sh.H, D = sh.D;
   if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: bad shape");
   if (D & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: head_dim must be a multiple of 8");
   const long long C = static_cast<long long>(H) * D;
   if (C > chitu::kNormMaxThreads * 8)
     return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: at most %d channels per token", chitu::kNormMaxThreads * 8);
-  if (in_dtype < 0 || in_dtype > 2 || (out_dtype != CHITU_DTYPE_BF16 && out_dtype != CHITU_DTYPE_FP16))
+  if (sh.in_dtype < 0 || sh.in_dtype > 2 || (sh.out_dtype != CHITU_DTYPE_BF16 && sh.out_dtype != CHITU_DTYPE_FP16))
     return fail(CHITU_E_INVALID, "qk_norm_rope: bad dtype");
-  if (weight && w_dtype != CHITU_DTYPE_BF16 && w_dtype != CHITU_DTYPE_FP32 && w_dtype != CHITU_DTYPE_FP16)
-    return fail(CHITU_E_INVALID, "qk_norm_rope: bad weight dtype");
-  if (norm_mode < 0 || norm_mode > 2 || rope_mode < 0 || rope_mode > 2)
-    return fail(CHITU_E_INVALID, "qk_norm_rope: bad mode");
-  if (norm_mode == 1) {
-    const int vph = D >> 3;
-    if (vph > 32 || (vph & (vph - 1))) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: per-head norm needs D in {8..256} power of two");
-  }
-  if (x_row_stride < C || (x_row_stride * elem_size(in_dtype)) % 16)
-    return fail(CHITU_E_INVALID, "qk_norm_rope: x_row_stride must cover H*D and keep rows 16-byte aligned");
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15)
-    return fail(CHITU_E_INVALID, "qk_norm_rope: x and out must be 16-byte aligned");
-  if (heads_per_group <= 0 || H % heads_per_group) return fail(CHITU_E_INVALID, "qk_norm_rope: heads_per_group must divide H");
+  if (sh.w_dtype < 0 || sh.w_dtype > 2) return fail(CHITU_E_INVALID, "qk_norm_rope: bad weight dtype");
+  if (sh.heads_per_group <= 0 || H % sh.heads_per_group)
+    return fail(CHITU_E_INVALID, "qk_norm_rope: heads_per_group must divide H");
   for (int i = 0; i < 4; ++i)
-    if (out_strides[i] & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: out_strides must be multiples of 8 elements");
-  chitu::NormRopeParams p;
-  p.n_t = p.n_h = 0;
-  if (rope_mode != 0) {
-    if (!rope_table || table_rows <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: rope table missing");
-    if (rope_mode == 1) {
-      if (!axis_split || gf <= 0 || gh <= 0 || gw <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: grid / axis_split missing");
-      if (axis_split[0] < 0 || axis_split[1] < 0 || axis_split[0] + axis_split[1] > D / 2)
-        return fail(CHITU_E_INVALID, "qk_norm_rope: axis_split out of range");
-      if (gf > table_rows || gh > table_rows || gw > table_rows)
-        return fail(CHITU_E_INVALID, "qk_norm_rope: rope table has fewer rows than the grid extent");
-      p.n_t = axis_split[0];
-      p.n_h = axis_split[1];
-    }
-  }
-  p.x = x;
-  p.in_dtype = in_dtype;
-  p.x_row_stride = x_row_stride;
-  p.weight = weight;
-  p.w_dtype = w_dtype;
-  p.eps = eps;
-  p.norm_mode = norm_mode;
-  p.rope_mode = rope_mode;
-  p.table = reinterpret_cast<const float2*>(rope_table);
-  p.table_rows = table_rows;
-  p.gf = gf;
-  p.gh = gh;
-  p.gw = gw;
-  p.pos_offset = pos_offset;
-  p.out = out;
-  p.out_dtype = out_dtype;
-  p.os_b = out_strides[0];
-  p.os_s = out_strides[1];
-  p.os_g = out_strides[2];
-  p.os_h = out_strides[3];
-  p.heads_per_group = heads_per_group;
-  p.B = B;
-  p.S = S;
-  p.H = H;
-  p.D = D;
-  p.round_mid = round_mid;
-  p.n_out_ptrs = n_out_ptrs;
-  for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < n_out_ptrs ? out_ptrs[i] : nullptr;
+    if (sh.out_strides[i] & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: out_strides must be multiples of 8 elements");
   const long long tokens = static_cast<long long>(B) * S;
   if (tokens > 2147483647LL) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: too many tokens");
+
+  chitu::NormRopeBatch batch;
+  for (int j = 0; j < n_jobs; ++j) {
+    const chitu_b200_norm_rope_job& jb = jobs[j];
+    chitu::NormRopeParams& p = batch.job[j];
+    if (!jb.x || (!jb.out && jb.n_out_ptrs == 0)) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+    if (jb.n_out_ptrs != 0) {
+      if (jb.n_out_ptrs < 0 || jb.n_out_ptrs > 8 || !jb.out_ptrs || jb.n_out_ptrs * sh.heads_per_group != H)
+        return fail(CHITU_E_INVALID, "qk_norm_rope: need one destination per head group (at most 8)");
+      for (int i = 0; i < jb.n_out_ptrs; ++i)
+        if (!jb.out_ptrs[i] || (reinterpret_cast<uintptr_t>(jb.out_ptrs[i]) & 15))
+          return fail(CHITU_E_INVALID, "qk_norm_rope: destination %d null or not 16-byte aligned", i);
+    }
+    if (jb.norm_mode < 0 || jb.norm_mode > 2 || jb.rope_mode < 0 || jb.rope_mode > 2)
+      return fail(CHITU_E_INVALID, "qk_norm_rope: bad mode");
+    if (jb.norm_mode == 1) {
+      const int vph = D >> 3;
+      if (vph > 32 || (vph & (vph - 1)))
+        return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: per-head norm needs D in {8..256} power of two");
+    }
+    if (jb.x_row_stride < C || (jb.x_row_stride * elem_size(sh.in_dtype)) % 16)
+      return fail(CHITU_E_INVALID, "qk_norm_rope: x_row_stride must cover H*D and keep rows 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(jb.x) | reinterpret_cast<uintptr_t>(jb.out)) & 15)
+      return fail(CHITU_E_INVALID, "qk_norm_rope: x and out must be 16-byte aligned");
+    p.n_t = p.n_h = 0;
+    if (jb.rope_mode != 0) {
+      if (!sh.rope_table || sh.table_rows <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: rope table missing");
+      if (jb.rope_mode == 1) {
+        if (!sh.axis_split || sh.gf <= 0 || sh.gh <= 0 || sh.gw <= 0)
+          return fail(CHITU_E_INVALID, "qk_norm_rope: grid / axis_split missing");
+        if (sh.axis_split[0] < 0 || sh.axis_split[1] < 0 || sh.axis_split[0] + sh.axis_split[1] > D / 2)
+          return fail(CHITU_E_INVALID, "qk_norm_rope: axis_split out of range");
+        if (sh.gf > sh.table_rows || sh.gh > sh.table_rows || sh.gw > sh.table_rows)
+          return fail(CHITU_E_INVALID, "qk_norm_rope: rope table has fewer rows than the grid extent");
+        p.n_t = sh.axis_split[0];
+        p.n_h = sh.axis_split[1];
+      }
+    }
+    p.x = jb.x;
+    p.in_dtype = sh.in_dtype;
+    p.x_row_stride = jb.x_row_stride;
+    p.weight = jb.weight;
+    p.w_dtype = sh.w_dtype;
+    p.eps = sh.eps;
+    p.norm_mode = jb.norm_mode;
+    p.rope_mode = jb.rope_mode;
+    p.table = reinterpret_cast<const float2*>(sh.rope_table);
+    p.table_rows = sh.table_rows;
+    p.gf = sh.gf;
+    p.gh = sh.gh;
+    p.gw = sh.gw;
+    p.pos_offset = sh.pos_offset;
+    p.out = jb.out;
+    p.out_dtype = sh.out_dtype;
+    p.os_b = sh.out_strides[0];
+    p.os_s = sh.out_strides[1];
+    p.os_g = sh.out_strides[2];
+    p.os_h = sh.out_strides[3];
+    p.heads_per_group = sh.heads_per_group;
+    p.B = B;
+    p.S = S;
+    p.H = H;
+    p.D = D;
+    p.round_mid = sh.round_mid;
+    p.n_out_ptrs = jb.n_out_ptrs;
+    for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < jb.n_out_ptrs ? jb.out_ptrs[i] : nullptr;
+  }
   // one 8-channel vector per thread, whole warps; the grid fills the 148 SMs a few CTAs deep
   const int threads = static_cast<int>(((C / 8) + 31) / 32 * 32);
   const int per_sm = threads <= 256 ? 8 : (threads <= 512 ? 4 : 2);
-  const unsigned grid = static_cast<unsigned>(tokens < 148LL * per_sm ? tokens : 148LL * per_sm);
+  const int per_job = (per_sm + n_jobs - 1) / n_jobs;
+  const unsigned gx = static_cast<unsigned>(tokens < 148LL * per_job ? tokens : 148LL * per_job);
+  const dim3 grid(gx, n_jobs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define CHITU_NR_LAUNCH(IN, NM, RM) chitu::qk_norm_rope_kernel<IN, NM, RM><<<grid, threads, 0, st>>>(p)
+  // the kernel is specialised on the modes of job 0; other jobs either share them or are plain
+  const int nm = jobs[0].norm_mode, rm = jobs[0].rope_mode;
+  for (int j = 1; j < n_jobs; ++j) {
+    const bool same = jobs[j].norm_mode == nm && jobs[j].rope_mode == rm;
+    const bool plain = jobs[j].norm_mode == 2 && jobs[j].rope_mode == 0;
+    if (!same && !plain) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: jobs of one launch share modes or are plain copies");
+  }
+#define CHITU_NR_LAUNCH(IN, NM, RM) chitu::qk_norm_rope_kernel<IN, NM, RM><<<grid, threads, 0, st>>>(batch)
 #define CHITU_NR_ROPE(IN, NM)                     \
-  switch (rope_mode) {                            \
+  switch (rm) {                                   \
     case 0: CHITU_NR_LAUNCH(IN, NM, 0); break;    \
     case 1: CHITU_NR_LAUNCH(IN, NM, 1); break;    \
     default: CHITU_NR_LAUNCH(IN, NM, 2); break;   \
   }
 #define CHITU_NR_NORM(IN)                         \
-  switch (norm_mode) {                            \
+  switch (nm) {                                   \
     case 0: CHITU_NR_ROPE(IN, 0); break;          \
     case 1: CHITU_NR_ROPE(IN, 1); break;          \
     default: CHITU_NR_ROPE(IN, 2); break;         \
   }
-  switch (in_dtype) {
+  switch (sh.in_dtype) {
     case CHITU_DTYPE_BF16: CHITU_NR_NORM(0); break;
     case CHITU_DTYPE_FP16: CHITU_NR_NORM(1); break;
     default: CHITU_NR_NORM(2); break;
@@ -420,6 +447,25 @@ int qk_norm_rope_impl(const void* x, int in_dtype, int64_t x_row_stride, const v
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "qk_norm_rope: launch");
   return CHITU_OK;
+}
+
+int qk_norm_rope_impl(const void* x, int in_dtype, int64_t x_row_stride, const void* weight, int w_dtype, float eps,
+                      int norm_mode, int rope_mode, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                      const int* axis_split, int64_t pos_offset, void* out, void* const* out_ptrs, int n_out_ptrs,
+                      int out_dtype, const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                      int round_mid, void* stream) {
+  chitu_b200_norm_rope_job job;
+  job.x = x;
+  job.x_row_stride = x_row_stride;
+  job.weight = weight;
+  job.norm_mode = norm_mode;
+  job.rope_mode = rope_mode;
+  job.out = out;
+  job.out_ptrs = out_ptrs;
+  job.n_out_ptrs = n_out_ptrs;
+  NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
+                    out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
+  return qk_norm_rope_batch_impl(&job, 1, sh, stream);
 }
 
 }  // namespace
@@ -445,6 +491,16 @@ int chitu_b200_qk_norm_rope_scatter(const void* x, int in_dtype, int64_t x_row_s
   return qk_norm_rope_impl(x, in_dtype, x_row_stride, weight, w_dtype, eps, norm_mode, rope_mode, rope_table,
                            table_rows, gf, gh, gw, axis_split, pos_offset, nullptr, out_ptrs, n_out_ptrs, out_dtype,
                            out_strides, heads_per_group, B, S, H, D, round_mid, stream);
+}
+
+int chitu_b200_qk_norm_rope_batch(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
+                                  float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                                  const int* axis_split, int64_t pos_offset, int out_dtype,
+                                  const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                                  int round_mid, void* stream) {
+  NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
+                    out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
+  return qk_norm_rope_batch_impl(jobs, n_jobs, sh, stream);
 }
 
 int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream) {

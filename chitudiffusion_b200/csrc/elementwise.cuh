@@ -209,8 +209,19 @@ __device__ __forceinline__ void ld8(const void* p, size_t i, float (&v)[8]) {
 // visits, so the norm weights live in registers; the next token's vector is loaded before the
 // current one is transformed.  Full-width statistics need one block reduction per token,
 // per-head statistics only warp shuffles.
-template <int kInDtype, int kNormMode, int kRopeMode>
-__global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const NormRopeParams p) {
+// Up to three tensors (q, k, v) of one layer share a launch: blockIdx.y picks the job.  Jobs 0 and
+// 1 use the template's norm / rotary modes; a job whose own modes are (2, 0) is a plain cast /
+// scatter (the v tensor).
+struct NormRopeBatch {
+  NormRopeParams job[3];
+};
+
+template <int kInDtype, int kNormModeT, int kRopeModeT>
+__global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const __grid_constant__ NormRopeBatch batch) {
+  const NormRopeParams& p = batch.job[blockIdx.y];
+  const bool plain = (p.norm_mode == 2 && p.rope_mode == 0);
+  const int kNormMode = plain ? 2 : kNormModeT;
+  const int kRopeMode = plain ? 0 : kRopeModeT;
   __shared__ float red[2][kNormMaxThreads / 32];
   const int C = p.H * p.D;
   const int c0 = threadIdx.x * 8;
@@ -246,6 +257,38 @@ __global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const Nor
     const long long t_next = token + gridDim.x;
     if (active && t_next < tokens) ld8<kInDtype>(p.x, static_cast<size_t>(t_next) * p.x_row_stride + c0, nxt);
 
+    // Position and rotary factors first: their (L2) loads overlap the reduction below.
+    const int b = static_cast<int>(token / p.S);
+    const int s = static_cast<int>(token - static_cast<long long>(b) * p.S);
+    float rc[4], rs[4];
+    bool rotate = false;
+    if (kRopeMode != 0 && active) {
+      const long long n = p.pos_offset + s;
+      if (kRopeMode == 2) {
+        if (n < p.table_rows) {
+          rotate = true;
+          // per-token table: the four (cos, sin) pairs of this vector are 32 contiguous bytes
+          const float4* trow = reinterpret_cast<const float4*>(p.table + n * half_d + (d0 >> 1));
+          const float4 c0v = __ldg(trow), c1v = __ldg(trow + 1);
+          rc[0] = c0v.x; rs[0] = c0v.y; rc[1] = c0v.z; rs[1] = c0v.w;
+          rc[2] = c1v.x; rs[2] = c1v.y; rc[3] = c1v.z; rs[3] = c1v.w;
+        }
+      } else if (n < static_cast<long long>(p.gf) * p.gh * p.gw) {  // padding tokens past the grid pass through
+        rotate = true;
+        const int pf = static_cast<int>(n / (static_cast<long long>(p.gh) * p.gw));
+        const int ph = static_cast<int>((n / p.gw) % p.gh);
+        const int pw = static_cast<int>(n % p.gw);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int j = (d0 >> 1) + q;
+          const long long trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
+          const float2 cs = __ldg(&p.table[trow * half_d + j]);
+          rc[q] = cs.x;
+          rs[q] = cs.y;
+        }
+      }
+    }
+
     float rstd = 1.f;
     if (kNormMode != 2) {
       float ss = 0.f;
@@ -265,8 +308,6 @@ __global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const Nor
       }
     }
     if (active) {
-      const int b = static_cast<int>(token / p.S);
-      const int s = static_cast<int>(token - static_cast<long long>(b) * p.S);
       float y[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -281,33 +322,13 @@ __global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const Nor
         }
         y[e] = t;
       }
-      if (kRopeMode != 0) {
-        const long long n = p.pos_offset + s;
-        bool rotate = true;
-        int pf = 0, ph = 0, pw = 0;
-        if (kRopeMode == 1) {
-          if (n >= static_cast<long long>(p.gf) * p.gh * p.gw) {
-            rotate = false;  // padding tokens past the grid pass through
-          } else {
-            pf = static_cast<int>(n / (static_cast<long long>(p.gh) * p.gw));
-            ph = static_cast<int>((n / p.gw) % p.gh);
-            pw = static_cast<int>(n % p.gw);
-          }
-        } else if (n >= p.table_rows) {
-          rotate = false;
-        }
-        if (rotate) {
+      if (rotate) {
 #pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            const int j = (d0 + e) >> 1;
-            long long trow = n;
-            if (kRopeMode == 1) trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
-            const float2 cs = __ldg(&p.table[trow * half_d + j]);
-            const float re = y[e] * cs.x - y[e + 1] * cs.y;
-            const float im = y[e] * cs.y + y[e + 1] * cs.x;
-            y[e] = re;
-            y[e + 1] = im;
-          }
+        for (int q = 0; q < 4; ++q) {
+          const float re = y[2 * q] * rc[q] - y[2 * q + 1] * rs[q];
+          const float im = y[2 * q] * rs[q] + y[2 * q + 1] * rc[q];
+          y[2 * q] = re;
+          y[2 * q + 1] = im;
         }
       }
       uint4 o;

@@ -247,6 +247,85 @@ def qk_norm_rope(
     return out
 
 
+def qk_norm_rope_batch(
+    jobs: Sequence[dict],
+    num_heads: int,
+    eps: float,
+    rope_table: Optional[torch.Tensor],
+    grid: Sequence[int] = (0, 0, 0),
+    axis_split: Sequence[int] = (0, 0),
+    pos_offset: int = 0,
+    out_strides: Optional[Sequence[int]] = None,
+    heads_per_group: Optional[int] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    round_mid: bool = True,
+):
+    """Up to three pre-attention jobs (q, k, v) in one launch; see ``chitu_b200_qk_norm_rope_batch``.
+
+    Each job is a dict with ``x [B,S,H*D]``, optional ``weight``, ``norm_mode``, ``rope_mode`` and
+    either ``out`` (tensor), ``out_ptrs`` (list of device addresses) or neither (a contiguous
+    ``[B,S,H,D]`` result is allocated).  All jobs share dtype, shape and placement.  Returns the list
+    of output tensors (``None`` for jobs written through ``out_ptrs``).
+    """
+    import ctypes
+
+    x0 = jobs[0]["x"]
+    B, S, C = x0.shape
+    D = C // num_heads
+    arr = (_lib.NormRopeJob * len(jobs))()
+    keep, outs = [], []
+    w_dtype = None
+    for i, jb in enumerate(jobs):
+        x = jb["x"]
+        _require_cuda(x, jb.get("weight"), jb.get("out"))
+        if x.shape != x0.shape or x.dtype != x0.dtype:
+            raise ValueError("batched pre-attention jobs must share shape and dtype")
+        if x.stride(2) != 1 or (B > 1 and x.stride(0) != S * x.stride(1)):
+            x = x.contiguous()
+        w = jb.get("weight")
+        if w is not None:
+            w = w.contiguous()
+            if w_dtype is not None and w.dtype != w_dtype:
+                raise ValueError("batched pre-attention jobs must share the weight dtype")
+            w_dtype = w.dtype
+        out, ptrs = jb.get("out"), jb.get("out_ptrs")
+        if ptrs is None and out is None:
+            if out_strides is not None:
+                raise ValueError("explicit out_strides need out or out_ptrs in every job")
+            out = torch.empty((B, S, num_heads, D), dtype=out_dtype, device=x.device)
+        keep += [x, w, out]
+        arr[i].x = x.data_ptr()
+        arr[i].x_row_stride = x.stride(1)
+        arr[i].weight = w.data_ptr() if w is not None else None
+        arr[i].norm_mode = int(jb.get("norm_mode", 2))
+        arr[i].rope_mode = int(jb.get("rope_mode", 0))
+        arr[i].out = out.data_ptr() if out is not None else None
+        if ptrs is not None:
+            pa = _lib.ptr_array(ptrs)
+            keep.append(pa)
+            arr[i].out_ptrs = ctypes.cast(pa, ctypes.POINTER(ctypes.c_void_p))
+            arr[i].n_out_ptrs = len(ptrs)
+        else:
+            arr[i].n_out_ptrs = 0
+        outs.append(out)
+    if out_strides is None:
+        out_strides, heads_per_group = (S * C, C, 0, D), num_heads
+    if rope_table is not None and (rope_table.dtype != torch.float32 or not rope_table.is_contiguous()):
+        raise ValueError("rope_table must be a contiguous fp32 [rows, D/2, 2] tensor")
+    split = (ctypes.c_int * 2)(int(axis_split[0]), int(axis_split[1]))
+    lib = _lib.load()
+    with torch.cuda.device(x0.device):
+        rc = lib.chitu_b200_qk_norm_rope_batch(
+            arr, len(jobs), _DTYPES[x0.dtype], _DTYPES[w_dtype] if w_dtype is not None else _lib.DTYPE_FP32,
+            float(eps), rope_table.data_ptr() if rope_table is not None else None,
+            int(rope_table.shape[0]) if rope_table is not None else 0, int(grid[0]), int(grid[1]), int(grid[2]),
+            split, int(pos_offset), _DTYPES[out_dtype], _lib.i64_array(out_strides), int(heads_per_group),
+            B, S, num_heads, D, 1 if round_mid else 0, _stream_ptr(x0.device),
+        )
+    _lib.check(rc, "qk_norm_rope_batch")
+    return outs
+
+
 def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     """Copy a 5-d view ``src [n0,n1,n2,n3,row]`` (last dim contiguous) into contiguous ``dst``."""
     _require_cuda(src, dst)

@@ -91,6 +91,18 @@ class PeerUlysses:
                          out_ptrs=self.dest_ptrs(which), out_strides=self.gather_strides,
                          heads_per_group=self.hc, out_dtype=self.dtype)
 
+    def scatter_qkv(self, jobs, v: torch.Tensor, **batch_args) -> None:
+        """One launch: the q and k jobs of a pre-attention object plus the plain scatter of ``v``."""
+        jobs = [dict(j) for j in jobs]
+        if v.dtype == jobs[0]["x"].dtype:
+            jobs.append(dict(x=v.reshape(self.B, self.s, self.H * self.D), norm_mode=2, rope_mode=0))
+        else:  # a launch shares one input dtype
+            self.scatter_plain(v, "v")
+        for j, which in zip(jobs, ("q", "k", "v")):
+            j["out_ptrs"] = self.dest_ptrs(which)
+        ops.qk_norm_rope_batch(jobs, out_strides=self.gather_strides, heads_per_group=self.hc, out_dtype=self.dtype,
+                               **batch_args)
+
     def attention(self, softmax_scale: Optional[float] = None) -> torch.Tensor:
         """Barrier, attention over the gathered q/k/v with the output scattered to its owners, barrier."""
         self.barrier()

@@ -108,10 +108,16 @@ class WanPreAttention:
             axis_split=self.split, pos_offset=self.cp_rank * s if self.cp_size > 1 else 0, **placement,
         )
 
+    def jobs(self, q_proj, k_proj, wq, wk):
+        return [dict(x=q_proj, weight=wq, norm_mode=0, rope_mode=1), dict(x=k_proj, weight=wk, norm_mode=0, rope_mode=1)]
+
+    def batch_args(self, s: int, grid: Sequence[int]) -> dict:
+        return dict(num_heads=self.num_heads, eps=self.eps, rope_table=self.table, grid=grid, axis_split=self.split,
+                    pos_offset=self.cp_rank * s if self.cp_size > 1 else 0)
+
     def __call__(self, q_proj, k_proj, v_proj, wq, wk, grid):
         B, S, C = q_proj.shape
-        q = self.one(q_proj, wq, grid)
-        k = self.one(k_proj, wk, grid)
+        q, k = ops.qk_norm_rope_batch(self.jobs(q_proj, k_proj, wq, wk), **self.batch_args(S, grid))
         v = v_proj.view(B, S, self.num_heads, self.head_dim)
         if v.dtype not in (torch.bfloat16, torch.float16):
             v = v.to(torch.bfloat16)
@@ -128,10 +134,16 @@ class JointPreAttention:
         return ops.qk_norm_rope(x, self.num_heads, weight, self.eps, norm_mode=1, rope_mode=2, rope_table=self.table,
                                 pos_offset=pos_offset, round_mid=False, **placement)
 
+    def jobs(self, q_proj, k_proj, wq=None, wk=None):
+        return [dict(x=q_proj, weight=wq, norm_mode=1, rope_mode=2), dict(x=k_proj, weight=wk, norm_mode=1, rope_mode=2)]
+
+    def batch_args(self, s: int = 0, grid: Sequence[int] = (0, 0, 0), pos_offset: int = 0) -> dict:
+        return dict(num_heads=self.num_heads, eps=self.eps, rope_table=self.table, pos_offset=pos_offset,
+                    round_mid=False)
+
     def __call__(self, q_proj, k_proj, v_proj, wq=None, wk=None, pos_offset: int = 0):
         B, S, C = q_proj.shape
-        q = self.one(q_proj, wq, pos_offset)
-        k = self.one(k_proj, wk, pos_offset)
+        q, k = ops.qk_norm_rope_batch(self.jobs(q_proj, k_proj, wq, wk), **self.batch_args(pos_offset=pos_offset))
         v = v_proj.view(B, S, self.num_heads, self.head_dim)
         if v.dtype not in (torch.bfloat16, torch.float16):
             v = v.to(torch.bfloat16)

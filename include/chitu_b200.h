@@ -154,6 +154,29 @@ int chitu_b200_qk_norm_rope(const void* x, int in_dtype, int64_t x_row_stride, c
                             int round_mid, void* stream);
 
 /*
+ * q, k (and v) of one layer in ONE launch: up to three jobs that share shape, dtypes, rotary table
+ * and output placement, each with its own input, weight and modes (v is usually norm_mode 2,
+ * rope_mode 0: a plain cast / scatter).  Same reference lines as chitu_b200_qk_norm_rope - it replaces
+ * the q and k chains of WanSelfAttention.forward (chitu_diffusion/models/model_wan.py:152-156,194-200)
+ * at once.  A job writes to `out`, or, when n_out_ptrs > 0, head group g goes to out_ptrs[g] as in
+ * chitu_b200_qk_norm_rope_scatter.
+ */
+typedef struct {
+  const void* x;
+  int64_t x_row_stride;
+  const void* weight; /* NULL = unit weight */
+  int norm_mode, rope_mode;
+  void* out;
+  void* const* out_ptrs;
+  int n_out_ptrs;
+} chitu_b200_norm_rope_job;
+int chitu_b200_qk_norm_rope_batch(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
+                                  float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                                  const int* axis_split, int64_t pos_offset, int out_dtype,
+                                  const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                                  int round_mid, void* stream);
+
+/*
  * Layout shuffles either side of the Ulysses all-to-all (packed single-buffer form).
  * Replace the permute + contiguous() pairs in CommGroup._all_to_all_single
  * (chitu_diffusion/core/distributed/comm_group.py:350-384).
