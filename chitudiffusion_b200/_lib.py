@@ -31,6 +31,8 @@ EXPORTS = (
     "chitu_b200_attn_fwd_splitkv",
     "chitu_b200_attn_fwd_splitkv_static",
     "chitu_b200_qk_norm_rope_batch",
+    "chitu_b200_attn_q8_workspace_bytes",
+    "chitu_b200_attn_fwd_q8",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -122,6 +124,14 @@ def load() -> ctypes.CDLL:
         ctypes.POINTER(NormRopeJob), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, _vp, ctypes.c_int,
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int64, ctypes.c_int,
         _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp,
+    ]
+    lib.chitu_b200_attn_q8_workspace_bytes.restype = ctypes.c_int64
+    lib.chitu_b200_attn_q8_workspace_bytes.argtypes = [ctypes.c_int] * 4
+    lib.chitu_b200_attn_fwd_q8.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_q8.argtypes = [
+        _vp, _vp, _vp, _vp, _vp,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp,
     ]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]

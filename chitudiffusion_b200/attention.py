@@ -16,7 +16,9 @@ import torch
 from . import _lib, ops
 
 BACKEND_NAME = "b200"
-_ALIASES = {"b200": "b200", "b200_attn": "b200", "chitu_b200": "b200", "tcgen05": "b200"}
+QUANT_BACKEND_NAME = "b200_q8"
+_ALIASES = {"b200": "b200", "b200_attn": "b200", "chitu_b200": "b200", "tcgen05": "b200",
+            "b200_q8": "b200_q8", "b200_sage": "b200_q8", "b200_int8": "b200_q8"}
 
 
 class B200AttnBackend:
@@ -61,5 +63,10 @@ class B200AttnBackend:
             raise NotImplementedError("b200 backend does not support dropout.")
         if tuple(window_size) != (-1, -1):
             raise NotImplementedError("b200 backend does not support sliding-window attention.")
-        out, lse = ops.attn_fwd(q, k, v, softmax_scale=softmax_scale, return_lse=return_attn_probs)
+        if self.impl == QUANT_BACKEND_NAME:
+            # per-block INT8 QK^T / E4M3 PV, the role SageAttention plays in the reference
+            # (diffusion_attn_backend.py:242-268); like there, ring CP refuses it (no LSE merge of 8-bit partials)
+            out, lse = ops.attn_fwd_q8(q, k, v, softmax_scale=softmax_scale, return_lse=return_attn_probs)
+        else:
+            out, lse = ops.attn_fwd(q, k, v, softmax_scale=softmax_scale, return_lse=return_attn_probs)
         return out, lse, None

@@ -14,6 +14,8 @@
 
 #include "attn_fwd.cuh"
 #include "elementwise.cuh"
+#include "quant.cuh"
+#include "attn_q8.cuh"
 
 namespace {
 
@@ -96,7 +98,7 @@ int chitu_b200_version(void) { return 100; }
 
 unsigned chitu_b200_caps(void) {
   return CHITU_CAP_ATTN_BF16 | CHITU_CAP_ATTN_FP16 | CHITU_CAP_NORM_ROPE | CHITU_CAP_LSE_COMBINE | CHITU_CAP_A2A_LAYOUT |
-         CHITU_CAP_PEER_EXCHANGE;
+         CHITU_CAP_PEER_EXCHANGE | CHITU_CAP_ATTN_Q8;
 }
 
 const char* chitu_b200_last_error(void) { return g_err; }
@@ -610,5 +612,144 @@ extern "C" int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, 
   ks.workspace_bytes = static_cast<int64_t>(kStaticScratchBytes);
   return attn_fwd_impl(q, k, v, out, OutScatter{}, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides,
                        softmax_scale, dtype, status, stream, ks);
+}
+
+// ----------------------------------------------------------------------------
+// 8-bit attention: quantisation pre-pass + INT8 / FP8 tensor-core kernel
+// ----------------------------------------------------------------------------
+namespace {
+
+struct Q8Layout {
+  int64_t q8, k8, v8, q_scale, k_scale, k_sum, v_amax, q_corr, total;
+};
+
+int64_t align256(int64_t n) { return (n + 255) / 256 * 256; }
+
+Q8Layout q8_layout(int B, int Sq, int Sk, int H) {
+  Q8Layout L;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    const int64_t at = off;
+    off += align256(bytes);
+    return at;
+  };
+  L.q8 = take(static_cast<int64_t>(B) * Sq * H * 128);
+  L.k8 = take(static_cast<int64_t>(B) * Sk * H * 128);
+  L.v8 = take(static_cast<int64_t>(B) * Sk * H * 128);
+  L.q_scale = take(static_cast<int64_t>(B) * H * ((Sq + 127) / 128) * 4);
+  L.k_scale = take(static_cast<int64_t>(B) * H * ((Sk + 63) / 64) * 4);
+  L.k_sum = take(static_cast<int64_t>(B) * H * 128 * 4);
+  L.v_amax = take(static_cast<int64_t>(B) * H * 128 * 4);  // directly after k_sum: one memset clears both
+  L.q_corr = take(static_cast<int64_t>(B) * H * Sq * 4);
+  L.total = off;
+  return L;
+}
+
+// Tensor map over a contiguous [B, S, H, 128] byte tensor: one 128-row x 128-byte panel per copy.
+int make_u8_map(CUtensorMap* map, const void* base, int B, int S, int H, const char* name) {
+  auto encode = get_encode_fn();
+  if (!encode) return fail(CHITU_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[3] = {128, static_cast<cuuint64_t>(H) * 128, static_cast<cuuint64_t>(S) * H * 128};
+  cuuint32_t box[4] = {128, 1, 128, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CHITU_E_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", name, (int)r);
+  return CHITU_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t chitu_b200_attn_q8_workspace_bytes(int B, int Sq, int Sk, int H) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0) return 0;
+  return q8_layout(B, Sq, Sk, H).total;
+}
+
+extern "C" int chitu_b200_attn_fwd_q8(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq,
+                                      int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
+                                      const int64_t* v_strides, float softmax_scale, int dtype, void* workspace,
+                                      int64_t workspace_bytes, int* status, void* stream) {
+  if (!q || !k || !v || !out || !q_strides || !k_strides || !v_strides || !workspace)
+    return fail(CHITU_E_INVALID, "attn_fwd_q8: null pointer argument");
+  if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0) return fail(CHITU_E_INVALID, "attn_fwd_q8: B, H, Sq, Sk must be positive");
+  if (D != 128) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: head_dim %d not supported (only 128)", D);
+  if (dtype != CHITU_DTYPE_BF16 && dtype != CHITU_DTYPE_FP16)
+    return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: dtype must be bf16 or fp16");
+  if (!(softmax_scale > 0.f)) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: softmax_scale must be positive");
+  if (H > 65535 || B > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: H and B must be below 65536");
+  for (const int64_t* st : {q_strides, k_strides, v_strides})
+    if (st[3] != 1 || (st[0] & 3) || (st[1] & 3) || (st[2] & 3))
+      return fail(CHITU_E_INVALID, "attn_fwd_q8: head_dim stride must be 1, the others multiples of 4 elements");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(CHITU_E_INVALID, "attn_fwd_q8: q, k, v, out must be 16-byte aligned");
+  const Q8Layout L = q8_layout(B, Sq, Sk, H);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < L.total)
+    return fail(CHITU_E_INVALID, "attn_fwd_q8: workspace must be 256-byte aligned and hold %lld bytes", (long long)L.total);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* q8 = ws + L.q8;
+  uint8_t* k8 = ws + L.k8;
+  uint8_t* v8 = ws + L.v8;
+  float* q_scale = reinterpret_cast<float*>(ws + L.q_scale);
+  float* k_scale = reinterpret_cast<float*>(ws + L.k_scale);
+  float* k_sum = reinterpret_cast<float*>(ws + L.k_sum);
+  unsigned* v_amax = reinterpret_cast<unsigned*>(ws + L.v_amax);
+  float* q_corr = reinterpret_cast<float*>(ws + L.q_corr);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  cudaError_t e = cudaMemsetAsync(k_sum, 0, static_cast<size_t>(L.q_corr - L.k_sum), st);  // k_sum and v_amax
+  if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_q8: memset");
+  const int chunk = 256;
+  chitu::q8_colstat_kernel<<<dim3((Sk + chunk - 1) / chunk, H, B), 128, 0, st>>>(
+      k, v, dtype, k_strides[0], k_strides[1], k_strides[2], v_strides[0], v_strides[1], v_strides[2], Sk, H, chunk,
+      k_sum, v_amax);
+  const float pre = softmax_scale * 1.4426950408889634f;
+  chitu::q8_quant_kernel<<<dim3((Sq + 127) / 128, H, B), 128, 0, st>>>(
+      q, dtype, q_strides[0], q_strides[1], q_strides[2], Sq, H, 0, pre, k_sum, v_amax, q8, q_scale, 128, q_corr, Sk);
+  chitu::q8_quant_kernel<<<dim3((Sk + 63) / 64, H, B), 128, 0, st>>>(
+      k, dtype, k_strides[0], k_strides[1], k_strides[2], Sk, H, 1, 1.f, k_sum, v_amax, k8, k_scale, 64, nullptr, Sk);
+  chitu::q8_quant_kernel<<<dim3((Sk + 127) / 128, H, B), 128, 0, st>>>(
+      v, dtype, v_strides[0], v_strides[1], v_strides[2], Sk, H, 2, 1.f, k_sum, v_amax, v8, nullptr, 128, nullptr, Sk);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_q8: quantisation launch");
+
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_u8_map(&tq, q8, B, Sq, H, "q8")) != CHITU_OK) return rc;
+  if ((rc = make_u8_map(&tk, k8, B, Sk, H, "k8")) != CHITU_OK) return rc;
+  if ((rc = make_u8_map(&tv, v8, B, Sk, H, "v8")) != CHITU_OK) return rc;
+  chitu::AttnQ8Params p;
+  p.out = out;
+  p.lse = lse;
+  p.status = status;
+  p.B = B;
+  p.H = H;
+  p.Sq = Sq;
+  p.Sk = Sk;
+  p.is_fp16 = dtype == CHITU_DTYPE_FP16;
+  p.q_scale = q_scale;
+  p.k_scale = k_scale;
+  p.v_amax = v_amax;
+  p.q_corr = q_corr;
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute(chitu::attn_q8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    chitu::kQ8SmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(chitu::attn_q8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      chitu::kQ8SmemBytes);
+  });
+  if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd_q8: cudaFuncSetAttribute");
+  dim3 grid((Sq + 255) / 256, H, B);
+  if (p.is_fp16)
+    chitu::attn_q8_kernel<true><<<grid, chitu::kQ8Threads, chitu::kQ8SmemBytes, st>>>(tq, tk, tv, p);
+  else
+    chitu::attn_q8_kernel<false><<<grid, chitu::kQ8Threads, chitu::kQ8SmemBytes, st>>>(tq, tk, tv, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_q8: launch");
+  return CHITU_OK;
 }
 

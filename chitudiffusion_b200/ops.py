@@ -138,6 +138,43 @@ def attn_fwd(
     return out, lse
 
 
+def attn_fwd_q8(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    return_lse: bool = False,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Quantised attention (INT8 QK^T, E4M3 PV); see ``chitu_b200_attn_fwd_q8``."""
+    _require_cuda(q, k, v)
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    if k.shape != v.shape or k.shape[0] != B or k.shape[2] != H or k.shape[3] != D:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError("attention kernel takes bf16 or fp16 q/k/v of one dtype")
+
+    def usable(t):
+        return t.stride(3) == 1 and all(s % 4 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+
+    q, k, v = (t if usable(t) else t.contiguous() for t in (q, k, v))
+    out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if return_lse else None
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    lib = _lib.load()
+    need = int(lib.chitu_b200_attn_q8_workspace_bytes(B, Sq, Sk, H))
+    ws = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    with torch.cuda.device(q.device):
+        rc = lib.chitu_b200_attn_fwd_q8(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+            B, Sq, Sk, H, D, _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()),
+            scale, _DTYPES[q.dtype], base, need, status_word(q.device).data_ptr(), _stream_ptr(q.device),
+        )
+    _lib.check(rc, "attn_fwd_q8")
+    return out, lse
+
+
 def lse_combine(
     acc_out: torch.Tensor,
     acc_lse: torch.Tensor,

@@ -43,6 +43,7 @@ int chitu_b200_version(void);
 #define CHITU_CAP_LSE_COMBINE 8u
 #define CHITU_CAP_A2A_LAYOUT 16u
 #define CHITU_CAP_PEER_EXCHANGE 32u
+#define CHITU_CAP_ATTN_Q8 64u
 unsigned chitu_b200_caps(void);
 const char* chitu_b200_last_error(void);
 
@@ -104,6 +105,22 @@ int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, const void*
                                        int Sq, int Sk, int H, int D, const int64_t* q_strides,
                                        const int64_t* k_strides, const int64_t* v_strides, float softmax_scale,
                                        int dtype, int n_splits, int* status, void* stream);
+
+/*
+ * Quantised attention: per-block INT8 Q K^T, E4M3 P V, fp32 accumulation, 16-bit output.
+ * Stands in for the SageAttention backend call sageattn(q, k, v, tensor_layout="NHD", ...)
+ * (chitu_diffusion/modules/attention/diffusion_attn_backend.py:242-268).  The call runs the
+ * quantisation pre-pass (K centred over the tokens; Q scaled by softmax_scale*log2 e and quantised per
+ * 128-token block, K per 64-token block, V to E4M3 per channel) and then the 8-bit kernel.
+ * Arguments as chitu_b200_attn_fwd; `workspace` (256-byte aligned, at least
+ * chitu_b200_attn_q8_workspace_bytes(B, Sq, Sk, H) bytes) receives the 8-bit copies and scales and
+ * needs no initialisation.  Unlike the reference call, softmax_scale is honoured.
+ */
+int64_t chitu_b200_attn_q8_workspace_bytes(int B, int Sq, int Sk, int H);
+int chitu_b200_attn_fwd_q8(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                           int H, int D, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                           float softmax_scale, int dtype, void* workspace, int64_t workspace_bytes, int* status,
+                           void* stream);
 
 /*
  * Fold one partial attention result into the running (out, lse) pair:

@@ -43,3 +43,4 @@ from .layouts import (  # noqa: F401
     cfg_rank_lists,
     up_rank_lists,
 )
+from .quantised import attention_q8  # noqa: F401,E402
