@@ -13,6 +13,9 @@
 // room at the small end; the common factor cancels in O / l.
 #pragma once
 
+#include <type_traits>
+
+#include "attn_fwd.cuh"
 #include "ptx.cuh"
 
 namespace chitu {
@@ -23,6 +26,10 @@ constexpr int kQ8Threads = 384;
 constexpr int kQ8SmemBytes = (2 + kQ8Stages) * kQ8TileBytes + 256 + 1024;
 constexpr float kQ8Shift = 4.0f;      // exponent offset of the stored probabilities
 constexpr float kQ8Threshold = 4.0f;  // lazy-rescale threshold (log2 units)
+#ifndef CHITU_Q8_POLY_PAIRS
+#define CHITU_Q8_POLY_PAIRS 4
+#endif
+constexpr int kQ8PolyPairs = CHITU_Q8_POLY_PAIRS;  // of every 8 score pairs, how many take the polynomial 2^x
 
 struct AttnQ8Params {
   void* out;              // [B, Sq, H, 128] contiguous, bf16 / fp16
@@ -34,7 +41,26 @@ struct AttnQ8Params {
   const float* k_scale;   // [B, H, ceil(Sk / 64)]
   const unsigned* v_amax; // [B, H, 128] bit patterns of max |v| per channel (dequantisation = amax / 448)
   const float* q_corr;    // [B, H, Sq] q' . mean(k) in the base-2 domain (undoes the K centring in the LSE)
+#ifdef CHITU_ATTN_TIMING
+  long long* dbg;
+#endif
 };
+
+// 2^x for a pair of values on the FMA pipe, quadratic form of exp2_poly2 (max relative error 1.7e-3:
+// enough for probabilities that are rounded to three mantissa bits)
+__device__ __forceinline__ float2 exp2_quad2(float2 x) {
+  const float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rd(x, make_float2(kMagic, kMagic));
+  const float2 nf = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+  const float2 f = __fadd2_rn(x, make_float2(-nf.x, -nf.y));
+  float2 r = __ffma2_rn(make_float2(0.33718944f, 0.33718944f), f, make_float2(0.6576363f, 0.6576363f));
+  r = __ffma2_rn(r, f, make_float2(1.0017247f, 1.0017247f));
+  r.x = __uint_as_float(__float_as_uint(r.x) + (__float_as_uint(t.x) << 23));
+  r.y = __uint_as_float(__float_as_uint(r.y) + (__float_as_uint(t.y) << 23));
+  return r;
+}
 
 // two floats -> two E4M3 bytes (first argument in the low byte)
 __device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
@@ -57,9 +83,9 @@ attn_q8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t bar_kv_full = bar_base + 16;                 // [kQ8Stages]
   const uint32_t bar_kv_empty = bar_kv_full + 8 * kQ8Stages;  // [kQ8Stages]
   const uint32_t bar_s_full = bar_kv_empty + 8 * kQ8Stages;   // [2]
-  const uint32_t bar_p_full = bar_s_full + 16;                // [2]
-  const uint32_t bar_o_final = bar_p_full + 16;               // [2]
-  uint8_t* tail = smem_gen + (2 + kQ8Stages) * kQ8TileBytes + (16 + 16 * kQ8Stages + 48);
+  const uint32_t bar_p_full = bar_s_full + 16;                // [2 tiles][2 halves]
+  const uint32_t bar_o_final = bar_p_full + 32;               // [2]
+  uint8_t* tail = smem_gen + (2 + kQ8Stages) * kQ8TileBytes + (16 + 16 * kQ8Stages + 64);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
 
@@ -81,7 +107,8 @@ attn_q8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1);
-      mbar_init(bar_p_full + 8 * t, 128);
+      mbar_init(bar_p_full + 16 * t, 128);
+      mbar_init(bar_p_full + 16 * t + 8, 128);
       mbar_init(bar_o_final + 8 * t, 1);
     }
     mbar_fence_init();
@@ -142,14 +169,14 @@ attn_q8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma_ss_i8(tmem_base + t * 128, a0 + 2 * k, b0 + 2 * k, kIdescQK, k > 0);
       };
-      auto issue_pv = [&](int t, int slot, bool accumulate) {
-        // 4 steps of 32 keys: A = P (four E4M3 per TMEM column), B = V rows as loaded (MN-major)
-        const uint64_t b0 = kv_desc0 + static_cast<uint64_t>((slot * kQ8TileBytes) >> 4);
+      auto issue_pv_half = [&](int t, int slot, int h, bool accumulate) {
+        // keys [64h, 64h+64) in 2 steps of 32: A = P (four E4M3 per TMEM column), B = V rows as loaded (MN-major)
+        const uint64_t b0 = kv_desc0 + static_cast<uint64_t>((slot * kQ8TileBytes + h * 8192) >> 4);
         const uint32_t acc0 = accumulate ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_ts_f8(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, b0 + static_cast<uint64_t>((k * 4096) >> 4),
-                     kIdescPV, k > 0 ? 1u : acc0);
+        for (int k = 0; k < 2; ++k)
+          umma_ts_f8(tmem_base + 256 + t * 128, tmem_base + t * 128 + h * 16 + k * 8,
+                     b0 + static_cast<uint64_t>((k * 4096) >> 4), kIdescPV, k > 0 ? 1u : acc0);
       };
       auto wait_item = [&](int i) {
         mbar_wait(bar_kv_full + 8 * (i % kQ8Stages), (i / kQ8Stages) & 1, abort_flag, p.status, kDevTimeoutMma);
@@ -179,10 +206,14 @@ attn_q8_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (more) wait_item(ik);
         wait_item(iv);
         for (int t = 0; t < n_qt; ++t) {
-          mbar_wait(bar_p_full + 8 * t, j & 1, abort_flag, p.status, kDevTimeoutMma);
+          mbar_wait(bar_p_full + 16 * t, j & 1, abort_flag, p.status, kDevTimeoutMma);
+          tc_fence_after_sync();
+          if (leader) issue_pv_half(t, iv % kQ8Stages, 0, j > 0);
+          __syncwarp();
+          mbar_wait(bar_p_full + 16 * t + 8, j & 1, abort_flag, p.status, kDevTimeoutMma);
           tc_fence_after_sync();
           if (leader) {
-            issue_pv(t, iv % kQ8Stages, j > 0);
+            issue_pv_half(t, iv % kQ8Stages, 1, true);
             if (more) {
               issue_qk(t, ik % kQ8Stages);
               umma_commit(bar_s_full + 8 * t);

@@ -679,6 +679,8 @@ extern "C" int chitu_b200_attn_fwd_q8(const void* q, const void* k, const void* 
     return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: dtype must be bf16 or fp16");
   if (!(softmax_scale > 0.f)) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: softmax_scale must be positive");
   if (H > 65535 || B > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: H and B must be below 65536");
+  if ((Sq + 127) / 128 + (Sk + 63) / 64 + (Sk + 127) / 128 > 65535)
+    return fail(CHITU_E_UNSUPPORTED, "attn_fwd_q8: sequences too long for the quantisation grid");
   for (const int64_t* st : {q_strides, k_strides, v_strides})
     if (st[3] != 1 || (st[0] & 3) || (st[1] & 3) || (st[2] & 3))
       return fail(CHITU_E_INVALID, "attn_fwd_q8: head_dim stride must be 1, the others multiples of 4 elements");
@@ -701,17 +703,34 @@ extern "C" int chitu_b200_attn_fwd_q8(const void* q, const void* k, const void* 
 
   cudaError_t e = cudaMemsetAsync(k_sum, 0, static_cast<size_t>(L.q_corr - L.k_sum), st);  // k_sum and v_amax
   if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_q8: memset");
-  const int chunk = 256;
-  chitu::q8_colstat_kernel<<<dim3((Sk + chunk - 1) / chunk, H, B), 128, 0, st>>>(
-      k, v, dtype, k_strides[0], k_strides[1], k_strides[2], v_strides[0], v_strides[1], v_strides[2], Sk, H, chunk,
-      k_sum, v_amax);
-  const float pre = softmax_scale * 1.4426950408889634f;
-  chitu::q8_quant_kernel<<<dim3((Sq + 127) / 128, H, B), 128, 0, st>>>(
-      q, dtype, q_strides[0], q_strides[1], q_strides[2], Sq, H, 0, pre, k_sum, v_amax, q8, q_scale, 128, q_corr, Sk);
-  chitu::q8_quant_kernel<<<dim3((Sk + 63) / 64, H, B), 128, 0, st>>>(
-      k, dtype, k_strides[0], k_strides[1], k_strides[2], Sk, H, 1, 1.f, k_sum, v_amax, k8, k_scale, 64, nullptr, Sk);
-  chitu::q8_quant_kernel<<<dim3((Sk + 127) / 128, H, B), 128, 0, st>>>(
-      v, dtype, v_strides[0], v_strides[1], v_strides[2], Sk, H, 2, 1.f, k_sum, v_amax, v8, nullptr, 128, nullptr, Sk);
+  chitu::q8_colstat_kernel<<<dim3(H, (Sk + 127) / 128, B), chitu::kQ8QuantThreads, 0, st>>>(
+      k, v, dtype, k_strides[0], k_strides[1], k_strides[2], v_strides[0], v_strides[1], v_strides[2], Sk, H, k_sum,
+      v_amax);
+  chitu::Q8QuantParams qp;
+  const void* xs[3] = {q, k, v};
+  const int64_t* strides[3] = {q_strides, k_strides, v_strides};
+  uint8_t* outs[3] = {q8, k8, v8};
+  const int tokens[3] = {Sq, Sk, Sk};
+  const int blocks[3] = {(Sq + 127) / 128, (Sk + 63) / 64, (Sk + 127) / 128};
+  qp.first_block[0] = 0;
+  for (int i = 0; i < 3; ++i) {
+    qp.x[i] = xs[i];
+    qp.xs_b[i] = strides[i][0];
+    qp.xs_s[i] = strides[i][1];
+    qp.xs_h[i] = strides[i][2];
+    qp.out[i] = outs[i];
+    qp.S[i] = tokens[i];
+    qp.first_block[i + 1] = qp.first_block[i] + blocks[i];
+  }
+  qp.dtype = dtype;
+  qp.H = H;
+  qp.pre_scale = softmax_scale * 1.4426950408889634f;
+  qp.k_sum = k_sum;
+  qp.v_amax = v_amax;
+  qp.q_scale = q_scale;
+  qp.k_scale = k_scale;
+  qp.q_corr = q_corr;
+  chitu::q8_quant_kernel<<<dim3(H, qp.first_block[3], B), chitu::kQ8QuantThreads, 0, st>>>(qp);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attn_fwd_q8: quantisation launch");
 
@@ -733,6 +752,9 @@ extern "C" int chitu_b200_attn_fwd_q8(const void* q, const void* k, const void* 
   p.k_scale = k_scale;
   p.v_amax = v_amax;
   p.q_corr = q_corr;
+#ifdef CHITU_ATTN_TIMING
+  p.dbg = g_dbg;
+#endif
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {

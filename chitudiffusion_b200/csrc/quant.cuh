@@ -4,6 +4,11 @@
 //   Q (pre-multiplied by softmax_scale * log2 e) gets one scale per 128-token block,
 //   K one scale per 64-token block, V one scale per (batch, head, channel) so that max |v| -> 448.
 // All tensors are [B, S, H, 128]; the 8-bit outputs are contiguous in that layout.
+//
+// Both kernels are HBM-bound streams.  A CTA of 256 threads covers 16 token rows at a time: 16
+// consecutive threads read one 256-byte head row as 16-byte vectors, so every warp request is two
+// full rows.  Algorithmic bytes: colstat reads K and V once (4 * S * H * 128 bytes); quant reads Q, K,
+// V once and writes one byte per element (6 + 3 = 9 bytes per (token, head, channel) triple).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -18,109 +23,218 @@ namespace chitu {
 
 constexpr int kQ8BlockQ = 128;  // tokens per Q scale
 constexpr int kQ8BlockK = 64;   // tokens per K scale
+constexpr int kQ8QuantThreads = 256;
 
-// Column statistics of K and V over a chunk of tokens, accumulated with atomics into
-// k_sum [B,H,128] (plain sums) and v_amax [B,H,128] (bit pattern of a non-negative float).
-// Both must be zero before the launch.  grid = (chunks, H, B), 128 threads = one channel each.
-__global__ void __launch_bounds__(128)
-q8_colstat_kernel(const void* __restrict__ k, const void* __restrict__ v, int dtype, long long ks_b, long long ks_s,
-                  long long ks_h, long long vs_b, long long vs_s, long long vs_h, int S, int H,
-                  int tokens_per_chunk, float* __restrict__ k_sum, unsigned* __restrict__ v_amax) {
-  const int d = threadIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int s0 = blockIdx.x * tokens_per_chunk;
-  const int s1 = min(S, s0 + tokens_per_chunk);
-  float sum = 0.f, amax = 0.f;
-  for (int s = s0; s < s1; ++s) {
-    sum += ld_as_float(k, dtype, static_cast<size_t>(b * ks_b + s * ks_s + h * ks_h + d));
-    amax = fmaxf(amax, fabsf(ld_as_float(v, dtype, static_cast<size_t>(b * vs_b + s * vs_s + h * vs_h + d))));
+// eight consecutive 16-bit values: raw load, and conversion to floats
+__device__ __forceinline__ uint4 q8_load_raw(const void* base, size_t elem) {
+  return __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem));
+}
+__device__ __forceinline__ void q8_unpack8(const uint4 raw, int dtype, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dtype == 0) {  // bf16 (dtype code 0): the value is the high half of an fp32 pattern
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = h.x;
+      f[2 * i + 1] = h.y;
+    }
   }
-  const size_t idx = (static_cast<size_t>(b) * H + h) * 128 + d;
-  atomicAdd(k_sum + idx, sum);
-  atomicMax(v_amax + idx, __float_as_uint(amax));
 }
 
-// One CTA per (token block, head, batch); thread = one token row of 128 channels.
-//   mode 0: Q  -> int8, x * pre_scale, one scale per block of kQ8BlockQ tokens; q_corr[b,h,s] = q' . mean(k)
-//   mode 1: K  -> int8, x - k_sum / S, one scale per block of kQ8BlockK tokens
-//   mode 2: V  -> e4m3, x / (v_amax / 448) per channel (no block scale)
-// scales [B, H, n_blocks] receive the dequantisation factor (max|x| / 127).
-__global__ void __launch_bounds__(128)
-q8_quant_kernel(const void* __restrict__ x, int dtype, long long xs_b, long long xs_s, long long xs_h, int S, int H,
-                int mode, float pre_scale, const float* __restrict__ k_sum, const unsigned* __restrict__ v_amax,
-                uint8_t* __restrict__ out, float* __restrict__ scales, int block_tokens,
-                float* __restrict__ q_corr, int k_tokens) {
-  __shared__ float red[4];
-  __shared__ float chan[128];
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int n_blocks = gridDim.x;
-  const int s = blockIdx.x * block_tokens + threadIdx.x;
-  const bool valid = threadIdx.x < block_tokens && s < S;
-  const size_t stat = (static_cast<size_t>(b) * H + h) * 128;
-  if (mode == 1 || mode == 0) chan[threadIdx.x] = k_sum[stat + threadIdx.x] / static_cast<float>(k_tokens);
-  if (mode == 2) chan[threadIdx.x] = 448.0f / fmaxf(__uint_as_float(v_amax[stat + threadIdx.x]), 1e-8f);
+// Column statistics of K and V over 128 tokens per CTA, accumulated with atomics into
+// k_sum [B,H,128] (plain sums) and v_amax [B,H,128] (bit pattern of a non-negative float).
+// Both must be zero before the launch.  grid = (H, ceil(S / 128), B): heads vary fastest, so CTAs
+// that run together read neighbouring 256-byte pieces of the same token rows.
+__global__ void __launch_bounds__(kQ8QuantThreads)
+q8_colstat_kernel(const void* __restrict__ k, const void* __restrict__ v, int dtype, long long ks_b, long long ks_s,
+                  long long ks_h, long long vs_b, long long vs_s, long long vs_h, int S, int H,
+                  float* __restrict__ k_sum, unsigned* __restrict__ v_amax) {
+  __shared__ float sh_sum[8][128];
+  __shared__ float sh_max[8][128];
+  const int h = blockIdx.x, b = blockIdx.z;
+  const int sub = threadIdx.x >> 4;        // row within a pass of 16
+  const int c0 = (threadIdx.x & 15) * 8;   // first channel of this thread
+  float sum[8], amax[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) sum[e] = amax[e] = 0.f;
+#pragma unroll 4
+  for (int pass = 0; pass < 8; ++pass) {
+    const int s = blockIdx.y * 128 + pass * 16 + sub;
+    if (s < S) {
+      float fk[8], fv[8];
+      const uint4 rk = q8_load_raw(k, static_cast<size_t>(b * ks_b + s * ks_s + h * ks_h + c0));
+      const uint4 rv = q8_load_raw(v, static_cast<size_t>(b * vs_b + s * vs_s + h * vs_h + c0));
+      q8_unpack8(rk, dtype, fk);
+      q8_unpack8(rv, dtype, fv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        sum[e] += fk[e];
+        amax[e] = fmaxf(amax[e], fabsf(fv[e]));
+      }
+    }
+  }
+  // lanes l and l + 16 of a warp hold the same channels
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    sum[e] += __shfl_xor_sync(0xffffffffu, sum[e], 16);
+    amax[e] = fmaxf(amax[e], __shfl_xor_sync(0xffffffffu, amax[e], 16));
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane < 16) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      sh_sum[warp][c0 + e] = sum[e];
+      sh_max[warp][c0 + e] = amax[e];
+    }
+  }
   __syncthreads();
+  if (threadIdx.x < 128) {
+    float s_all = 0.f, m_all = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      s_all += sh_sum[w][threadIdx.x];
+      m_all = fmaxf(m_all, sh_max[w][threadIdx.x]);
+    }
+    const size_t idx = (static_cast<size_t>(b) * H + h) * 128 + threadIdx.x;
+    atomicAdd(k_sum + idx, s_all);
+    atomicMax(v_amax + idx, __float_as_uint(m_all));
+  }
+}
 
-  float vals[128];
+struct Q8QuantParams {
+  const void* x[3];          // q, k, v
+  long long xs_b[3], xs_s[3], xs_h[3];
+  uint8_t* out[3];           // 8-bit copies, [B, S, H, 128] contiguous
+  int S[3];                  // tokens of q, k, v
+  int first_block[4];        // block index ranges along grid.y: q | k | v
+  int dtype, H;
+  float pre_scale;           // softmax_scale * log2 e, applied to q
+  const float* k_sum;        // [B, H, 128] column sums of k
+  const unsigned* v_amax;    // [B, H, 128] column max |v| (float bit patterns)
+  float* q_scale;            // [B, H, ceil(Sq / 128)]
+  float* k_scale;            // [B, H, ceil(Sk / 64)]
+  float* q_corr;             // [B, H, Sq]: q' . mean(k), what the centring removed from every score of the row
+};
+
+// One CTA per (head, token block, batch) of q (128 tokens), k (64 tokens) or v (128 tokens); heads vary
+// fastest across the grid for the same locality as in q8_colstat_kernel:
+//   q -> int8 of x * pre_scale, one scale per block, plus q_corr
+//   k -> int8 of x - mean_k, one scale per block
+//   v -> e4m3 of x * 448 / amax per channel
+// The scale arrays receive the dequantisation factor max|x| / 127.
+__global__ void __launch_bounds__(kQ8QuantThreads, 4)
+q8_quant_kernel(const __grid_constant__ Q8QuantParams p) {
+  __shared__ float red[8];
+  const int which = (blockIdx.y >= p.first_block[2]) ? 2 : (blockIdx.y >= p.first_block[1]) ? 1 : 0;
+  const int blk = blockIdx.y - p.first_block[which];
+  const int block_tokens = (which == 1) ? kQ8BlockK : kQ8BlockQ;
+  const int n_pass = block_tokens / 16;
+  const int h = blockIdx.x, b = blockIdx.z;
+  const int S = p.S[which];
+  const int sub = threadIdx.x >> 4;
+  const int c0 = (threadIdx.x & 15) * 8;
+  const size_t stat = (static_cast<size_t>(b) * p.H + h) * 128 + c0;
+
+  float chan[8];  // q, k: mean of k per channel; v: 448 / amax per channel
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    if (which == 2)
+      chan[e] = 448.0f / fmaxf(__uint_as_float(p.v_amax[stat + e]), 1e-8f);
+    else
+      chan[e] = p.k_sum[stat + e] / static_cast<float>(p.S[1]);
+  }
+
+  // all loads of the block first (up to eight 16-byte requests in flight per thread), then the math
+  uint4 raw[8];
+#pragma unroll
+  for (int pass = 0; pass < 8; ++pass) {
+    const int s = blk * block_tokens + pass * 16 + sub;
+    raw[pass] = make_uint4(0u, 0u, 0u, 0u);
+    if (pass < n_pass && s < S)
+      raw[pass] = q8_load_raw(p.x[which],
+                              static_cast<size_t>(b * p.xs_b[which] + s * p.xs_s[which] + h * p.xs_h[which] + c0));
+  }
+  // first sweep over the registers: block maximum (and q_corr); second sweep: quantise.  The transformed
+  // values are recomputed rather than kept, which halves the register count and doubles the CTAs per SM.
+  auto transformed = [&](int pass, float (&f)[8]) {
+    q8_unpack8(raw[pass], p.dtype, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (which == 0) f[e] *= p.pre_scale;
+      else if (which == 1) f[e] -= chan[e];
+      else f[e] *= chan[e];
+    }
+  };
   float amax = 0.f;
-  if (valid) {
-    const size_t base = static_cast<size_t>(b * xs_b + s * xs_s + h * xs_h);
+  if (which != 2) {
 #pragma unroll
-    for (int d = 0; d < 128; d += 4) {
-      const float4 f = ld4(x, dtype, base + d);
-      vals[d] = f.x; vals[d + 1] = f.y; vals[d + 2] = f.z; vals[d + 3] = f.w;
+    for (int pass = 0; pass < 8; ++pass) {
+      const int s = blk * block_tokens + pass * 16 + sub;
+      const bool valid = pass < n_pass && s < S;
+      float f[8];
+      transformed(pass, f);  // rows that were not loaded hold zeros: harmless for the maximum
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (which == 0) dot = fmaf(f[e], chan[e], dot);
+        if (valid) amax = fmaxf(amax, fabsf(f[e]));
+      }
+      if (which == 0 && pass < n_pass) {  // whole-warp shuffles: the two rows of a warp may differ in validity
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (valid && (threadIdx.x & 15) == 0) p.q_corr[(static_cast<size_t>(b) * p.H + h) * S + s] = dot;
+      }
     }
-#pragma unroll
-    for (int d = 0; d < 128; ++d) {
-      if (mode == 0) vals[d] *= pre_scale;
-      if (mode == 1) vals[d] -= chan[d];
-      if (mode == 2) vals[d] *= chan[d];
-      amax = fmaxf(amax, fabsf(vals[d]));
-    }
-  } else {
-#pragma unroll
-    for (int d = 0; d < 128; ++d) vals[d] = 0.f;
   }
-  if (mode == 0 && valid && q_corr != nullptr) {
-    // q' . mean(k): what the centring of K removed from every score of this row (base-2 domain)
-    float dot = 0.f;
-#pragma unroll
-    for (int d = 0; d < 128; ++d) dot = fmaf(vals[d], chan[d], dot);
-    q_corr[(static_cast<size_t>(b) * H + h) * S + s] = dot;
-  }
+
   float inv = 1.f;
-  if (mode != 2) {
+  if (which != 2) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
-    const float bmax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    float bmax = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) bmax = fmaxf(bmax, red[w]);
     const float scale = fmaxf(bmax, 1e-8f) / 127.0f;
     inv = 1.0f / scale;
-    if (threadIdx.x == 0) scales[(static_cast<size_t>(b) * H + h) * n_blocks + blockIdx.x] = scale;
-  }
-  if (!valid) return;
-  uint4* dst = reinterpret_cast<uint4*>(out + ((static_cast<size_t>(b) * S + s) * H + h) * 128);
-#pragma unroll
-  for (int d = 0; d < 128; d += 16) {
-    uint32_t w[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float f = vals[d + q * 4 + e];
-        uint32_t byte;
-        if (mode == 2) {
-          byte = static_cast<uint32_t>(__nv_cvt_float_to_fp8(f, __NV_SATFINITE, __NV_E4M3));
-        } else {
-          const int r = max(-127, min(127, __float2int_rn(f * inv)));
-          byte = static_cast<uint32_t>(r) & 0xffu;
-        }
-        word |= byte << (8 * e);
-      }
-      w[q] = word;
+    if (threadIdx.x == 0) {
+      const int n_blocks = (S + block_tokens - 1) / block_tokens;
+      float* scales = (which == 0) ? p.q_scale : p.k_scale;
+      scales[(static_cast<size_t>(b) * p.H + h) * n_blocks + blk] = scale;
     }
-    dst[d >> 4] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+
+#pragma unroll
+  for (int pass = 0; pass < 8; ++pass) {
+    const int s = blk * block_tokens + pass * 16 + sub;
+    if (pass < n_pass && s < S) {
+      float f[8];
+      transformed(pass, f);
+      uint32_t w[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint32_t word = 0;
+        if (which == 2) {
+          uint16_t lo, hi;  // two E4M3 bytes per conversion (first source operand -> high byte)
+          asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f[q * 4 + 1]), "f"(f[q * 4]));
+          asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f[q * 4 + 3]), "f"(f[q * 4 + 2]));
+          word = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int r = max(-127, min(127, __float2int_rn(f[q * 4 + e] * inv)));
+            word |= (static_cast<uint32_t>(r) & 0xffu) << (8 * e);
+          }
+        }
+        w[q] = word;
+      }
+      *reinterpret_cast<uint2*>(p.out[which] + ((static_cast<size_t>(b) * S + s) * p.H + h) * 128 + c0) =
+          make_uint2(w[0], w[1]);
+    }
   }
 }
 
