@@ -145,7 +145,52 @@ class B200ContextParallel:
             v_full = self.group.all_gather_sequence(v)
             out = self.attn(q, k_full, v_full, return_attn_probs=False, **kw)[0]
             return out, None, None
+        if self.use_ring_cudagraph and self.cp_size > 1 and q.is_cuda and self._capturable(q, k, u, r, kw):
+            return self._cp_forward_graphed(q, k, v, u, r, kw), None, None
         return self._cp_forward(q, k, v, u, r, kw), None, None
+
+    # ------------------------------------------------------------------ whole-call CUDA graph
+    def _capturable(self, q, k, u: int, r: int, kw: dict) -> bool:
+        """Only exchanges made of this library's own kernels over peer memory are captured.
+
+        A captured NCCL send/recv ring (what the reference captures) did not complete on B200 with
+        torch 2.11 / NCCL 2.28 in this build's 2-GPU test, so layouts that still go through NCCL run
+        eagerly even when ``ring_cudagraph`` is set.
+        """
+        return self._use_peer(q, k, u, r, kw)
+
+    def _cp_forward_graphed(self, q, k, v, u: int, r: int, kw: dict) -> torch.Tensor:
+        """Capture the whole exchange + attention + exchange-back once per problem and replay it.
+
+        Mirror of ``_cp_forward_graphed`` (diffusion_attn_backend.py:1154-1203): the graph is keyed by
+        shapes, dtype, ``causal`` and ``softmax_scale``; inputs are copied into static buffers, the
+        static result is cloned out so that the next replay may overwrite it.  Everything inside is
+        capturable: the kernels take their workspace from torch's allocator, device waits are bounded
+        and report through the status word, and the peer barrier keeps its epoch on the device.
+        """
+        key = (tuple(q.shape), tuple(k.shape), tuple(v.shape), q.dtype, bool(kw["causal"]), kw["softmax_scale"])
+        entry = self._graph_cache.get(key)
+        if entry is None:
+            sq, sk, sv = q.clone(), k.clone(), v.clone()
+            cur = torch.cuda.current_stream(q.device)
+            warm = torch.cuda.Stream(device=q.device)
+            warm.wait_stream(cur)
+            with torch.cuda.stream(warm):  # sets up communicators, peer buffers and the side stream
+                for _ in range(3):
+                    self._cp_forward(sq, sk, sv, u, r, kw)
+            cur.wait_stream(warm)
+            torch.cuda.synchronize(q.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_out = self._cp_forward(sq, sk, sv, u, r, kw)
+            torch.cuda.synchronize(q.device)
+            entry = dict(graph=graph, q=sq, k=sk, v=sv, out=static_out)
+            self._graph_cache[key] = entry
+        entry["q"].copy_(q)
+        entry["k"].copy_(k)
+        entry["v"].copy_(v)
+        entry["graph"].replay()
+        return entry["out"].clone()
 
     # ------------------------------------------------------------------ Ulysses x ring
     def _ring_peers(self, u: int) -> Tuple[int, int]:

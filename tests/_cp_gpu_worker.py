@@ -5,6 +5,7 @@ the NCCL context-parallel layouts (Ulysses, ring, Ulysses x ring, all-gather-KV)
 ``B200ContextParallel`` with the b200 kernel, and the peer-store Ulysses exchange (``PeerUlysses``).
 """
 
+import faulthandler
 import os
 import sys
 
@@ -28,6 +29,8 @@ def rel_err(a, ref):
 
 
 def main():
+    # a rank that stops making progress dumps its stack and exits instead of waiting for the caller's timeout
+    faulthandler.dump_traceback_later(240, exit=True)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
@@ -55,6 +58,21 @@ def main():
         if name == "ulysses_peer":  # second call reuses the exchange buffers
             out = wrapper(ql, kl, vl)[0]
         results[name] = rel_err(out, full[:, sl])
+        print(f"rank {rank}: {name} done", flush=True)
+
+    # whole-call CUDA graph (ring_cudagraph=True): capture once, replay on new inputs
+    q2, k2, v2 = ((torch.randn(1, S, H, D, generator=gen)).to(torch.bfloat16) for _ in range(3))
+    full2 = oracle.sdpa_fp32(q2, k2, v2)
+    ql2, kl2, vl2 = (t[:, sl].contiguous().to(dev) for t in (q2, k2, v2))
+    for name, up in (("graph_ulysses", world),):
+        comm.destroy_diffusion_parallel_groups()
+        comm.initialize_diffusion_parallel_groups(1, world, up)
+        wrapper = B200ContextParallel(backend, up, ring_cudagraph=True)
+        first = wrapper(ql, kl, vl)[0]
+        second = wrapper(ql2, kl2, vl2)[0]  # replay of the captured graph
+        assert len(wrapper._graph_cache) == 1
+        results[name] = max(rel_err(first, full[:, sl]), rel_err(second, full2[:, sl]))
+        print(f"rank {rank}: {name} done", flush=True)
 
     # peer-store exchange: norm + rotary pre-pass scattered to the owners, attention scattered back
     comm.destroy_diffusion_parallel_groups()
