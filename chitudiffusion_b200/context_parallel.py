@@ -141,11 +141,17 @@ class B200ContextParallel:
         kw = dict(dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal, window_size=window_size,
                   deterministic=deterministic)
         if self.uses_agcp():
+            if self._peer_ok(q, k, kw):
+                ring = self.peer_ring(q, "agkv")
+                ring.scatter_plain(k, "k")
+                ring.scatter_plain(v, "v")
+                return ring.attention(kw["softmax_scale"], q=q), None, None
             k_full = self.group.all_gather_sequence(k)
             v_full = self.group.all_gather_sequence(v)
             out = self.attn(q, k_full, v_full, return_attn_probs=False, **kw)[0]
             return out, None, None
-        if self.use_ring_cudagraph and self.cp_size > 1 and q.is_cuda and self._capturable(q, k, u, r, kw):
+        if (self.use_ring_cudagraph and self.cp_size > 1 and q.is_cuda and not self.uses_agcp()
+                and self._capturable(q, k, u, r, kw)):
             return self._cp_forward_graphed(q, k, v, u, r, kw), None, None
         return self._cp_forward(q, k, v, u, r, kw), None, None
 
@@ -153,11 +159,11 @@ class B200ContextParallel:
     def _capturable(self, q, k, u: int, r: int, kw: dict) -> bool:
         """Only exchanges made of this library's own kernels over peer memory are captured.
 
-        A captured NCCL send/recv ring (what the reference captures) did not complete on B200 with
-        torch 2.11 / NCCL 2.28 in this build's 2-GPU test, so layouts that still go through NCCL run
-        eagerly even when ``ring_cudagraph`` is set.
+        A captured NCCL send/recv ring (what the reference captures) did not complete in a 2-GPU run
+        on B200 with torch 2.11 / NCCL 2.28, so layouts that still go through NCCL run eagerly even
+        when ``ring_cudagraph`` is set.
         """
-        return self._use_peer(q, k, u, r, kw)
+        return self._use_peer(q, k, u, r, kw) or self._use_peer_ring(q, k, u, r, kw)
 
     def _cp_forward_graphed(self, q, k, v, u: int, r: int, kw: dict) -> torch.Tensor:
         """Capture the whole exchange + attention + exchange-back once per problem and replay it.
@@ -241,13 +247,34 @@ class B200ContextParallel:
             self._peer_cache[key] = px
         return px
 
-    def _use_peer(self, q, k, u: int, r: int, kw: dict) -> bool:
+    def peer_ring(self, q: torch.Tensor, mode: str):
+        """Cached peer-memory ring / all-gather-KV exchange for one problem shape (collective on first use)."""
+        from .peer import PeerRing
+
+        B, s, H, D = q.shape
+        key = (mode, B, s, H, D, q.dtype, str(q.device))
+        ring = self._peer_cache.get(key)
+        if ring is None:
+            u, _ = self._split()
+            ring = PeerRing(self.group, u, B, s, H, D, q.dtype, q.device, mode=mode,
+                            merger_factory=self._merger_factory)
+            self._peer_cache[key] = ring
+        return ring
+
+    def _peer_ok(self, q, k, kw: dict) -> bool:
+        """The exchange may run over peer-mapped memory with this library's kernels (one node, <= 8 GPUs)."""
         return (
-            self.ulysses_exchange == "peer" and r == 1 and 1 < u <= 8 and q.is_cuda
-            and getattr(self.attn, "impl", "") == "b200" and q.shape == k.shape and q.shape[2] % u == 0
+            self.ulysses_exchange == "peer" and 1 < self.cp_size <= 8 and q.is_cuda
+            and getattr(self.attn, "impl", "") == "b200" and q.shape == k.shape
             and q.dtype in (torch.bfloat16, torch.float16) and not kw["causal"] and not kw["dropout_p"]
             and tuple(kw["window_size"]) == (-1, -1)
         )
+
+    def _use_peer(self, q, k, u: int, r: int, kw: dict) -> bool:
+        return r == 1 and u > 1 and q.shape[2] % u == 0 and self._peer_ok(q, k, kw)
+
+    def _use_peer_ring(self, q, k, u: int, r: int, kw: dict) -> bool:
+        return r > 1 and self.cp_size == u * r and q.shape[2] % u == 0 and self._peer_ok(q, k, kw)
 
     def _cp_forward(self, q, k, v, u: int, r: int, kw: dict) -> torch.Tensor:
         if self._use_peer(q, k, u, r, kw):
@@ -259,6 +286,14 @@ class B200ContextParallel:
             # the exchange buffer is reused by the next call: hand back a copy, as the reference
             # hands back a fresh tensor
             return px.attention(kw["softmax_scale"]).clone()
+        if self._use_peer_ring(q, k, u, r, kw):
+            ring = self.peer_ring(q, "ring")
+            if u > 1:
+                ring.scatter_plain(q, "q")
+            ring.scatter_plain(k, "k")
+            ring.scatter_plain(v, "v")
+            out = ring.attention(kw["softmax_scale"], q=None if u > 1 else q)
+            return out.clone() if u > 1 else out
         up_group = self._up_group_lookup(u) if u > 1 else None
         if up_group is not None:
             q = up_group.all_to_all(q, 2, 1)

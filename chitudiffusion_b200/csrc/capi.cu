@@ -542,6 +542,52 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
   return CHITU_OK;
 }
 
+int chitu_b200_scatter_rows(const void* src, void* const* dst_ptrs, int n_dest, int64_t B, int64_t rows,
+                            int64_t row_bytes, int64_t dst_batch_stride_bytes, int64_t dst_row_stride_bytes,
+                            void* stream) {
+  if (!src || !dst_ptrs) return fail(CHITU_E_INVALID, "scatter_rows: null pointer");
+  if (n_dest < 1 || n_dest > 8) return fail(CHITU_E_INVALID, "scatter_rows: n_dest must be 1..8");
+  if (B <= 0 || rows <= 0 || row_bytes <= 0 || (row_bytes & 15) || (dst_batch_stride_bytes & 15) ||
+      (dst_row_stride_bytes & 15))
+    return fail(CHITU_E_INVALID, "scatter_rows: extents must be positive, byte counts multiples of 16");
+  chitu::ScatterRowsParams p;
+  for (int i = 0; i < 8; ++i) p.dst[i] = nullptr;
+  for (int i = 0; i < n_dest; ++i) {
+    if (!dst_ptrs[i] || (reinterpret_cast<uintptr_t>(dst_ptrs[i]) & 15))
+      return fail(CHITU_E_INVALID, "scatter_rows: destinations must be non-null and 16-byte aligned");
+    p.dst[i] = static_cast<uint8_t*>(dst_ptrs[i]);
+  }
+  if (reinterpret_cast<uintptr_t>(src) & 15) return fail(CHITU_E_INVALID, "scatter_rows: src must be 16-byte aligned");
+  p.n_dest = n_dest;
+  p.B = B;
+  p.rows = rows;
+  p.row_vecs = row_bytes / 16;
+  p.dst_batch_bytes = dst_batch_stride_bytes;
+  p.dst_row_bytes = dst_row_stride_bytes;
+  const long long total = B * n_dest * rows * p.row_vecs;
+  const int grid = grid_for(total, 256 * 4, 148 * 8);
+  chitu::scatter_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src), p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "scatter_rows: launch");
+  return CHITU_OK;
+}
+
+int chitu_b200_peer_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                            int64_t width_bytes, int64_t rows, void* stream) {
+  if (!dst || !src) return fail(CHITU_E_INVALID, "peer_copy_2d: null pointer");
+  if (width_bytes <= 0 || rows <= 0 || dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes)
+    return fail(CHITU_E_INVALID, "peer_copy_2d: width and rows must be positive, pitches at least the width");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (rows == 1 || (dst_pitch_bytes == width_bytes && src_pitch_bytes == width_bytes))
+    e = cudaMemcpyAsync(dst, src, static_cast<size_t>(width_bytes * rows), cudaMemcpyDeviceToDevice, st);
+  else
+    e = cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch_bytes), src, static_cast<size_t>(src_pitch_bytes),
+                          static_cast<size_t>(width_bytes), static_cast<size_t>(rows), cudaMemcpyDeviceToDevice, st);
+  if (e != cudaSuccess) return cuda_fail(e, "peer_copy_2d");
+  return CHITU_OK;
+}
+
 }  // extern "C"
 
 // ----------------------------------------------------------------------------

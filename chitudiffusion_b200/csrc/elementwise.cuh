@@ -363,6 +363,32 @@ strided_copy_kernel(const uint8_t* __restrict__ src, uint4* __restrict__ dst, lo
 }
 
 // ----------------------------------------------------------------------------
+// Row scatter of 16-byte vectors: src is contiguous [B, n_dest * rows, row_vecs]; row
+// (b, i * rows + j) goes to dst[i] + b * dst_batch + j * dst_row (+ the offset already folded into
+// dst[i]).  The destinations may be peer-mapped buffers of other GPUs (plain stores).
+// ----------------------------------------------------------------------------
+struct ScatterRowsParams {
+  uint8_t* dst[8];
+  int n_dest;
+  long long B, rows, row_vecs;
+  long long dst_batch_bytes, dst_row_bytes;
+};
+
+__global__ void __launch_bounds__(256)
+scatter_rows_kernel(const uint4* __restrict__ src, const ScatterRowsParams p) {
+  const long long total = p.B * p.n_dest * p.rows * p.row_vecs;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    long long r = i / p.row_vecs;
+    const long long vec = i - r * p.row_vecs;
+    const long long j = r % p.rows; r /= p.rows;
+    const long long d = r % p.n_dest;
+    const long long b = r / p.n_dest;
+    reinterpret_cast<uint4*>(p.dst[d] + b * p.dst_batch_bytes + j * p.dst_row_bytes)[vec] = src[i];
+  }
+}
+
+// ----------------------------------------------------------------------------
 // Barrier among the GPUs of one exchange group over peer-mapped flag arrays.
 // Thread i tells peer i "rank `rank` has reached `epoch`" (release store, system scope) and
 // then waits until peer i has said the same to us.  The wait is bounded; on timeout the

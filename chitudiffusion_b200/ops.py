@@ -379,6 +379,31 @@ def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     return dst
 
 
+def peer_copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width: int, rows: int,
+                 device: torch.device) -> None:
+    """``rows`` pieces of ``width`` bytes between device buffers (either may be peer-mapped), on the copy engines."""
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        rc = lib.chitu_b200_peer_copy_2d(int(dst_ptr), int(dst_pitch), int(src_ptr), int(src_pitch), int(width),
+                                         int(rows), _stream_ptr(device))
+    _lib.check(rc, "peer_copy_2d")
+
+
+def scatter_rows(src: torch.Tensor, dst_ptrs: Sequence[int], rows: int, dst_batch_stride_bytes: int,
+                 dst_row_stride_bytes: int) -> None:
+    """``src [B, n_dest*rows, ...]`` contiguous: row ``(b, i*rows + j)`` goes to ``dst_ptrs[i] + b*batch + j*row`` bytes."""
+    _require_cuda(src)
+    if not src.is_contiguous() or src.dim() < 3 or src.shape[1] != rows * len(dst_ptrs):
+        raise ValueError("scatter_rows: src must be contiguous [B, n_dest*rows, ...]")
+    row_bytes = src[0, 0].numel() * src.element_size()
+    lib = _lib.load()
+    with torch.cuda.device(src.device):
+        rc = lib.chitu_b200_scatter_rows(src.data_ptr(), _lib.ptr_array(dst_ptrs), len(dst_ptrs), int(src.shape[0]),
+                                         int(rows), int(row_bytes), int(dst_batch_stride_bytes),
+                                         int(dst_row_stride_bytes), _stream_ptr(src.device))
+    _lib.check(rc, "scatter_rows")
+
+
 def attn_fwd_scatter(
     q: torch.Tensor,
     k: torch.Tensor,

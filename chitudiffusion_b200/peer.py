@@ -113,3 +113,130 @@ class PeerUlysses:
         )
         self.barrier()
         return self.out
+
+
+class PeerRing:
+    """Ring / Ulysses x ring / all-gather-KV exchange over peer-mapped memory for one problem shape.
+
+    Every rank publishes its (post-Ulysses) K/V block in a buffer mapped into all ranks of the CP
+    group.  Where the reference rotates K/V with send/recv pairs
+    (chitu_diffusion/modules/attention/diffusion_attn_backend.py:783-835: send to ``(r-U) % P``,
+    receive from ``(r+U) % P``), ring step ``t`` here PULLS the block of rank ``(r + t*U) % P`` - the
+    block that rotation delivers at step ``t`` - into local memory with the copy engines on a side
+    stream while the attention kernel works on block ``t-1``; partial results merge with the
+    log-sum-exp combine kernel.  ``mode="agkv"`` pulls every block into one ``[B, P*s, H, D]`` buffer
+    and runs a single attention call (the AGCP branch, :581-597).  No NCCL call is on the data path,
+    so the whole call can be captured in a CUDA graph.
+    """
+
+    def __init__(self, group: CommGroup, ulysses: int, B: int, s: int, H: int, D: int, dtype: torch.dtype,
+                 device: torch.device, mode: str = "ring", merger_factory=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        P = group.group_size
+        U = 1 if mode == "agkv" else ulysses
+        if P > 8:
+            raise NotImplementedError("peer exchange supports at most 8 GPUs")
+        if P % U or H % U:
+            raise ValueError(f"CP size {P} and head count {H} must be divisible by the Ulysses degree {U}")
+        self.group, self.P, self.U, self.R, self.rank = group, P, U, P // U, group.rank_in_group
+        self.mode, self.B, self.s, self.H, self.D, self.hc = mode, B, s, H, D, H // U
+        self.dtype, self.device, self.merger_factory = dtype, device, merger_factory
+        es = torch.empty((), dtype=dtype).element_size()
+        self.es = es
+        self.block_bytes = B * U * s * self.hc * D * es  # one of q / k / v of a ring block
+        out_es = 4 if self.R > 1 else es                 # merged ring results are fp32, like the reference's
+        self.off_q, self.off_k = 0, _align(self.block_bytes)
+        self.off_v = self.off_k + _align(self.block_bytes)
+        self.off_out = self.off_v + _align(self.block_bytes)
+        self.off_flags = self.off_out + _align(B * s * H * D * out_es)
+        self.buf = symm_mem.empty(self.off_flags + 256, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.gpu_group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group.gpu_group)
+
+        def view(off, shape, dt):
+            n = 1
+            for d in shape:
+                n *= d
+            return self.buf[off : off + n * torch.empty((), dtype=dt).element_size()].view(dt).view(shape)
+
+        block = (B, U * s, self.hc, D)
+        self.q, self.k, self.v = (view(o, block, dtype) for o in (self.off_q, self.off_k, self.off_v))
+        self.out = view(self.off_out, (B, s, H, D), torch.float32 if self.R > 1 else dtype)
+        self.flag_ptrs = [p + self.off_flags for p in self.ptrs]
+        self.members = [(self.rank // U) * U + i for i in range(U)]  # this rank's Ulysses group, CP-group indices
+        self.gather_strides = (U * s * self.hc * D, self.hc * D, 0, D)
+        self._row0 = (self.rank % U) * s * self.hc * D * es
+        self.side = torch.cuda.Stream(device=device)
+        if mode == "agkv":
+            self.k_full = torch.empty((B, P * s, H, D), dtype=dtype, device=device)
+            self.v_full = torch.empty_like(self.k_full)
+        elif self.R > 1:
+            self.k_fetch = [torch.empty(block, dtype=dtype, device=device) for _ in range(2)]
+            self.v_fetch = [torch.empty(block, dtype=dtype, device=device) for _ in range(2)]
+
+    def dest_ptrs(self, which: str):
+        """Per-destination base addresses (the members of this rank's Ulysses group) for its rows of q / k / v."""
+        off = {"q": self.off_q, "k": self.off_k, "v": self.off_v}[which]
+        return [self.ptrs[m] + off + self._row0 for m in self.members]
+
+    def barrier(self) -> None:
+        ops.peer_barrier(self.flag_ptrs, self.rank, self.P, self.device)
+
+    def scatter_plain(self, x: torch.Tensor, which: str) -> None:
+        flat = x.reshape(self.B, self.s, self.H * self.D)
+        ops.qk_norm_rope(flat, self.H, None, 0.0, norm_mode=2, rope_mode=0, rope_table=None,
+                         out_ptrs=self.dest_ptrs(which), out_strides=self.gather_strides,
+                         heads_per_group=self.hc, out_dtype=self.dtype)
+
+    def _pull(self, owner: int, off: int, dst: torch.Tensor) -> None:
+        ops.peer_copy_2d(dst.data_ptr(), self.block_bytes, self.ptrs[owner] + off, self.block_bytes,
+                         self.block_bytes, 1, self.device)
+
+    def attention(self, softmax_scale: Optional[float] = None, q: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Barrier, pulls + attention (+ merge, + hand-back to the sequence owners), barrier.
+
+        ``q`` is the local query tensor when the Ulysses degree is 1 (queries are then not exchanged).
+        """
+        if q is None:
+            q = self.q
+        self.barrier()  # every block is published
+        cur = torch.cuda.current_stream(self.device)
+        if self.mode == "agkv":
+            row = self.s * self.H * self.D * self.es
+            for owner in range(self.P):
+                for off, full in ((self.off_k, self.k_full), (self.off_v, self.v_full)):
+                    ops.peer_copy_2d(full.data_ptr() + owner * row, self.P * row, self.ptrs[owner] + off, row, row,
+                                     self.B, self.device)
+            result = ops.attn_fwd(q, self.k_full, self.v_full, softmax_scale=softmax_scale)[0]
+            self.barrier()  # nobody still reads this rank's published block
+            return result
+        merger = self.merger_factory()
+        k_t, v_t = self.k, self.v
+        for t in range(self.R):
+            nxt = None
+            if t + 1 < self.R:
+                owner = (self.rank + (t + 1) * self.U) % self.P
+                kb, vb = self.k_fetch[(t + 1) & 1], self.v_fetch[(t + 1) & 1]
+                self.side.wait_stream(cur)  # the attention call that last read these two buffers is enqueued
+                with torch.cuda.stream(self.side):
+                    self._pull(owner, self.off_k, kb)
+                    self._pull(owner, self.off_v, vb)
+                nxt = (kb, vb)
+            block_out, block_lse = ops.attn_fwd(q, k_t, v_t, softmax_scale=softmax_scale, return_lse=True)
+            merger.add(block_out, block_lse)
+            if nxt is not None:
+                cur.wait_stream(self.side)
+                k_t, v_t = nxt
+        merged = merger.result()  # fp32 [B, U*s, H/U, D]
+        if self.U == 1:
+            self.barrier()
+            return merged
+        col0 = (self.rank % self.U) * self.hc * self.D * 4
+        ops.scatter_rows(merged, [self.ptrs[m] + self.off_out + col0 for m in self.members], self.s,
+                         self.s * self.H * self.D * 4, self.H * self.D * 4)
+        self.barrier()  # all head groups of this rank's rows have arrived; nobody still reads its block
+        return self.out

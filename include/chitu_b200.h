@@ -209,6 +209,28 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
                             int64_t row_bytes, const int64_t* src_strides_bytes, void* stream);
 
 /*
+ * Ring and all-gather-KV exchange over peer-mapped memory: every rank publishes its K/V block in a
+ * buffer mapped into its peers, and a reader pulls the block it needs for the next ring step into
+ * local memory with the copy engines while the attention kernel works on the current block.  Replaces
+ * the send/recv rotation of DiffusionAttention_with_CP._cp_forward
+ * (chitu_diffusion/modules/attention/diffusion_attn_backend.py:783-835, built on
+ * CommGroup.p2p_isend/p2p_irecv/p2p_commit/p2p_wait, chitu_diffusion/core/distributed/comm_group.py:305-327)
+ * and the all_gather + cat of the AGCP branch (diffusion_attn_backend.py:581-597,739-742).
+ *
+ * chitu_b200_peer_copy_2d: `rows` pieces of width_bytes from src (pitch src_pitch_bytes) to dst (pitch
+ *   dst_pitch_bytes); either side may be peer-mapped.  A device-to-device cudaMemcpy(2D)Async on
+ *   `stream`: no SM is used.
+ * chitu_b200_scatter_rows: src is contiguous [B, n_dest*rows, row_bytes]; row (b, i*rows + j) is stored
+ *   to dst_ptrs[i] + b*dst_batch_stride_bytes + j*dst_row_stride_bytes.  Used to hand the merged fp32
+ *   result of a Ulysses x ring call back to the sequence owners (the all-to-all at :825-828).
+ */
+int chitu_b200_peer_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                            int64_t width_bytes, int64_t rows, void* stream);
+int chitu_b200_scatter_rows(const void* src, void* const* dst_ptrs, int n_dest, int64_t B, int64_t rows,
+                            int64_t row_bytes, int64_t dst_batch_stride_bytes, int64_t dst_row_stride_bytes,
+                            void* stream);
+
+/*
  * Ulysses exchange fused into the kernels either side of it, over peer-mapped memory of the GPUs
  * of one node (NVLink).  Together they replace the three all-to-all calls before and the one after
  * the attention kernel in DiffusionAttention_with_CP._cp_forward

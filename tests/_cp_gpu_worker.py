@@ -44,10 +44,10 @@ def main():
     ql, kl, vl = (t[:, sl].contiguous().to(dev) for t in (q, k, v))
     backend = B200AttnBackend("b200")
     results = {}
-    layouts = [("ulysses_peer", world, "ucp"), ("ulysses_nccl", world, "ucp"), ("ring", 1, "ucp"),
-               ("agcp", world, "agcp")]
+    layouts = [("ulysses_peer", world, "ucp"), ("ulysses_nccl", world, "ucp"), ("ring_peer", 1, "ucp"),
+               ("ring_nccl", 1, "ucp"), ("agcp_peer", world, "agcp"), ("agcp_nccl", world, "agcp")]
     if world >= 4:
-        layouts.append(("usp", world // 2, "ucp"))
+        layouts += [("usp_peer", world // 2, "ucp"), ("usp_nccl", world // 2, "ucp")]
     for name, up, cpb in layouts:
         comm.destroy_diffusion_parallel_groups()
         comm.initialize_diffusion_parallel_groups(1, world, up)
@@ -55,7 +55,8 @@ def main():
         if name.endswith("_nccl"):
             wrapper.ulysses_exchange = "nccl"
         out = wrapper(ql, kl, vl)[0]
-        if name == "ulysses_peer":  # second call reuses the exchange buffers
+        if name.endswith("_peer"):  # second call reuses the exchange buffers
+            assert wrapper._peer_cache, name
             out = wrapper(ql, kl, vl)[0]
         results[name] = rel_err(out, full[:, sl])
         print(f"rank {rank}: {name} done", flush=True)
@@ -64,7 +65,8 @@ def main():
     q2, k2, v2 = ((torch.randn(1, S, H, D, generator=gen)).to(torch.bfloat16) for _ in range(3))
     full2 = oracle.sdpa_fp32(q2, k2, v2)
     ql2, kl2, vl2 = (t[:, sl].contiguous().to(dev) for t in (q2, k2, v2))
-    for name, up in (("graph_ulysses", world),):
+    graphed = [("graph_ulysses", world), ("graph_ring", 1)] + ([("graph_usp", world // 2)] if world >= 4 else [])
+    for name, up in graphed:
         comm.destroy_diffusion_parallel_groups()
         comm.initialize_diffusion_parallel_groups(1, world, up)
         wrapper = B200ContextParallel(backend, up, ring_cudagraph=True)
