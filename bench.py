@@ -172,7 +172,7 @@ def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
 class Pipeline:
     """Per-rank block function: pre-attention pass + (context-parallel) attention."""
 
-    def __init__(self, w, rank, world, device, exchange="peer", init_groups=True):
+    def __init__(self, w, rank, world, device, exchange="peer", init_groups=True, layout="auto"):
         from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
         from chitudiffusion_b200.context_parallel import B200ContextParallel
 
@@ -182,23 +182,36 @@ class Pipeline:
         self.attn = self.backend
         if world > 1:
             up = max(u for u in (8, 4, 2, 1) if u <= world and self.H % u == 0 and world % u == 0)
+            if layout in ("ring", "agkv"):
+                up = 1
+            elif layout == "usp":
+                up = max(u for u in (4, 2, 1) if u < world and self.H % u == 0 and world % u == 0)
             if init_groups:
                 comm.initialize_diffusion_parallel_groups(1, world, up)
-            self.attn = B200ContextParallel(self.backend, up, cp_backend="ucp")
-            self.parallelism = f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else "")
+            elif layout != "auto":  # a second pipeline in the same process with another layout
+                comm.destroy_diffusion_parallel_groups()
+                comm.initialize_diffusion_parallel_groups(1, world, up)
+            self.attn = B200ContextParallel(self.backend, up, cp_backend="agcp" if layout == "agkv" else "ucp")
+            self.attn.ulysses_exchange = exchange
+            self.parallelism = ("agkv" if layout == "agkv" else
+                                f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else ""))
             self.peer = None
-            if exchange == "peer" and up == world:
+            self.graphable = exchange == "peer"  # no NCCL call on the data path
+            if exchange == "peer" and up == world and layout != "agkv":
                 # pure Ulysses: exchange fused into the pre-attention stores and the attention epilogue
                 from chitudiffusion_b200.peer import PeerUlysses
 
                 self.peer = PeerUlysses(comm.get_up_group(up), 1, seq_len(w) // world, self.H, self.D,
                                         torch.bfloat16, device)
                 self.parallelism += "-peer-stores"
+            elif exchange == "peer":
+                self.parallelism += "-peer-pulls"
             else:
                 self.parallelism += "-nccl"
         else:
             self.parallelism = "single"
             self.peer = None
+            self.graphable = False
         if w["kind"] == "joint":
             table = pre_attention.axis_rope_table(joint_ids(w), w["axes"])[local_positions(w, rank, world)]
             self.pre = pre_attention.JointPreAttention(self.H, self.D, table.contiguous().to(device))
@@ -243,18 +256,18 @@ class Pipeline:
         return out
 
 
-def measure_extra(name, layers, rank, world, device, exchange, sync, dist):
+def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layout="auto"):
     """Device-resident throughput of a few layers of a second workload (no host leg): the
     compute-bound Wan2.1-14B 720p shape, whose scaling the latency-bound default cannot show."""
     w = dict(WORKLOADS[name], blocks=layers)
-    pipe = Pipeline(w, rank, world, device, exchange=exchange, init_groups=False)
+    pipe = Pipeline(w, rank, world, device, exchange=exchange, init_groups=False, layout=layout)
     s_local, C = seq_len(w) // world, w["H"] * w["D"]
     gen = torch.Generator(device=device).manual_seed(77 + rank)
     sets = [tuple(torch.randn(1, s_local, C, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
                   for _ in range(3))]
     pipe.step(sets)
     fn = lambda: pipe.step(sets)  # noqa: E731
-    if world > 1 and pipe.peer is not None:
+    if world > 1 and pipe.graphable:
         sync()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
@@ -296,7 +309,7 @@ def run_ours(args):
     w = WORKLOADS[args.workload]
     if seq_len(w) % world or (w["kind"] == "joint" and (w["s_txt"] % world or w["s_img"] % world)):
         raise ValueError("sequence not divisible by the number of GPUs")
-    pipe = Pipeline(w, rank, world, device, exchange=args.exchange)
+    pipe = Pipeline(w, rank, world, device, exchange=args.exchange, layout=args.layout)
     dev_sets = make_inputs(w, rank, world, seed=1, n_sets=INPUT_SETS, device=device)
     host_sets = make_inputs(w, rank, world, seed=1, n_sets=0 if args.profile else 2, device=None, pinned=True)
     e2e_dev = [tuple(torch.empty_like(t, device=device) for t in trip) for trip in host_sets]
@@ -338,7 +351,7 @@ def run_ours(args):
         pipe.step(dev_sets)
     # On several GPUs a step is a few hundred short launches: capture it once in a CUDA graph and
     # replay it (every kernel of the peer-store path, the barrier included, is replayable).
-    use_graph = world > 1 and pipe.peer is not None and not args.no_graph
+    use_graph = world > 1 and pipe.graphable and not args.no_graph
     step_graph = e2e_graph = None
     e2e_out = [None]
     if use_graph:
@@ -376,6 +389,11 @@ def run_ours(args):
     extra = None
     if args.workload == DEFAULT_WORKLOAD and not args.profile and not args.no_extra:
         extra = measure_extra("wan14b-720p-81f", 4, rank, world, device, args.exchange, sync, dist)
+        if world > 1 and args.extra_layouts:
+            extra["layouts"] = []
+            for lay in [x.strip() for x in args.extra_layouts.split(",") if x.strip()]:
+                r = measure_extra("wan14b-720p-81f", 2, rank, world, device, args.exchange, sync, dist, layout=lay)
+                extra["layouts"].append({k: r[k] for k in ("parallelism", "ms_per_layer", "value", "per_gpu_tflops")})
 
     from chitudiffusion_b200 import ops
 
@@ -516,6 +534,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: Ulysses exchange by peer stores fused into the kernels, or by NCCL all-to-all")
+    ap.add_argument("--layout", default="auto", choices=["auto", "ulysses", "ring", "agkv", "usp"],
+                    help="N > 1: context-parallel layout (auto = the widest Ulysses degree the head count allows)")
+    ap.add_argument("--extra-layouts", default="",
+                    help="N > 1: comma-separated layouts (ring, agkv, usp) to time on the second workload as well")
     ap.add_argument("--no-extra", action="store_true", help="skip the second (Wan2.1-14B 720p) workload")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch kernel by kernel instead of replaying a graph")
     ap.add_argument("--profile", action="store_true",
