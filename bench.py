@@ -172,13 +172,15 @@ def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
 class Pipeline:
     """Per-rank block function: pre-attention pass + (context-parallel) attention."""
 
-    def __init__(self, w, rank, world, device, exchange="peer", init_groups=True, layout="auto"):
+    def __init__(self, w, rank, world, device, exchange="peer", init_groups=True, layout="auto", attn="b200"):
         from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
         from chitudiffusion_b200.context_parallel import B200ContextParallel
 
         self.w, self.rank, self.world, self.device = w, rank, world, device
         self.H, self.D = w["H"], w["D"]
-        self.backend = B200AttnBackend("b200")
+        self.backend = B200AttnBackend(attn)
+        if attn != "b200" and world > 1:
+            raise SystemExit("--attn b200_q8 is measured on one GPU")
         self.attn = self.backend
         if world > 1:
             up = max(u for u in (8, 4, 2, 1) if u <= world and self.H % u == 0 and world % u == 0)
@@ -245,7 +247,7 @@ class Pipeline:
             self.attn_events.append((e0, e1))
         else:
             out = self.attn(q, k, v)[0]
-        self.launches += 1
+        self.launches += 1 if self.backend.impl == "b200" else 3  # 8-bit: two pre-pass kernels + attention
         return out
 
     def step(self, sets, timed=False):
@@ -309,7 +311,7 @@ def run_ours(args):
     w = WORKLOADS[args.workload]
     if seq_len(w) % world or (w["kind"] == "joint" and (w["s_txt"] % world or w["s_img"] % world)):
         raise ValueError("sequence not divisible by the number of GPUs")
-    pipe = Pipeline(w, rank, world, device, exchange=args.exchange, layout=args.layout)
+    pipe = Pipeline(w, rank, world, device, exchange=args.exchange, layout=args.layout, attn=args.attn)
     dev_sets = make_inputs(w, rank, world, seed=1, n_sets=INPUT_SETS, device=device)
     host_sets = make_inputs(w, rank, world, seed=1, n_sets=0 if args.profile else 2, device=None, pinned=True)
     e2e_dev = [tuple(torch.empty_like(t, device=device) for t in trip) for trip in host_sets]
@@ -416,7 +418,8 @@ def run_ours(args):
         achieved = flops_per_block(w) / (avg_ms * 1e-3) / 1e12
         peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
         roof = {
-            "bound": "tensor", "kernel": "attn_fwd_kernel", "achieved": round(achieved, 2), "peak": peak,
+            "bound": "tensor", "kernel": "attn_fwd_kernel" if args.attn == "b200" else "q8 pre-pass + attn_q8_kernel",
+            "achieved": round(achieved, 2), "peak": peak,
             "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
             "peak_source": f"{peak_kind} bf16_tflops_sustained (kernel timed inside a long back-to-back loop)",
             "frac_of_burst": round(achieved / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), 4),
@@ -427,7 +430,8 @@ def run_ours(args):
     line = {
         "metric": "attention_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.attn == "b200" else "i8/e4m3 (bf16 in/out)",
+        "data": "synthetic",
         "config": {
             "workload": args.workload, "seq_len": seq_len(w), "heads": w["H"], "head_dim": w["D"],
             "attention_calls_per_step": w["blocks"], "parallelism": pipe.parallelism, "batch": 1,
@@ -534,6 +538,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: Ulysses exchange by peer stores fused into the kernels, or by NCCL all-to-all")
+    ap.add_argument("--attn", default="b200", choices=["b200", "b200_q8"],
+                    help="attention backend: bf16/fp16 kernel, or the INT8-QK / E4M3-PV variant (one GPU)")
     ap.add_argument("--layout", default="auto", choices=["auto", "ulysses", "ring", "agkv", "usp"],
                     help="N > 1: context-parallel layout (auto = the widest Ulysses degree the head count allows)")
     ap.add_argument("--extra-layouts", default="",
