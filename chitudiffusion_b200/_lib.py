@@ -31,6 +31,8 @@ EXPORTS = (
     "chitu_b200_attn_fwd_splitkv",
     "chitu_b200_attn_fwd_splitkv_static",
     "chitu_b200_qk_norm_rope_batch",
+    "chitu_b200_layernorm_modulate",
+    "chitu_b200_gate_residual",
     "chitu_b200_peer_copy_2d",
     "chitu_b200_scatter_rows",
     "chitu_b200_attn_q8_workspace_bytes",
@@ -127,6 +129,13 @@ def load() -> ctypes.CDLL:
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int64, ctypes.c_int,
         _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp,
     ]
+    lib.chitu_b200_layernorm_modulate.restype = ctypes.c_int
+    lib.chitu_b200_layernorm_modulate.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                                  _vp, ctypes.c_int64, _vp, ctypes.c_int64, ctypes.c_int,
+                                                  ctypes.c_float, _vp]
+    lib.chitu_b200_gate_residual.restype = ctypes.c_int
+    lib.chitu_b200_gate_residual.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                             _vp, ctypes.c_int64, _vp]
     lib.chitu_b200_peer_copy_2d.restype = ctypes.c_int
     lib.chitu_b200_peer_copy_2d.argtypes = [_vp, ctypes.c_int64, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp]
     lib.chitu_b200_scatter_rows.restype = ctypes.c_int

@@ -14,6 +14,7 @@
 
 #include "attn_fwd.cuh"
 #include "elementwise.cuh"
+#include "dit_elementwise.cuh"
 #include "quant.cuh"
 #include "attn_q8.cuh"
 
@@ -539,6 +540,66 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
       src_strides_bytes[1], src_strides_bytes[2], src_strides_bytes[3], total);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "strided_copy: launch");
+  return CHITU_OK;
+}
+
+int chitu_b200_layernorm_modulate(const float* x, void* out, int out_dtype, int64_t rows, int64_t rows_per_batch, int C,
+                                  const float* mul, int64_t mul_batch_stride, const float* add,
+                                  int64_t add_batch_stride, int add_one, float eps, void* stream) {
+  if (!x || !out) return fail(CHITU_E_INVALID, "layernorm_modulate: null pointer");
+  if (rows <= 0 || rows_per_batch <= 0 || C <= 0 || (C & 3) || C > chitu::kLnThreads * chitu::kLnMaxVec * 4)
+    return fail(CHITU_E_UNSUPPORTED, "layernorm_modulate: C must be a multiple of 4 up to %d",
+                chitu::kLnThreads * chitu::kLnMaxVec * 4);
+  if (out_dtype != CHITU_DTYPE_BF16 && out_dtype != CHITU_DTYPE_FP16)
+    return fail(CHITU_E_UNSUPPORTED, "layernorm_modulate: out_dtype must be bf16 or fp16");
+  if ((mul_batch_stride & 3) || (add_batch_stride & 3) ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(mul) | reinterpret_cast<uintptr_t>(add)) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 7))
+    return fail(CHITU_E_INVALID, "layernorm_modulate: x, mul, add must be 16-byte aligned, out 8-byte aligned");
+  chitu::LayerNormParams p;
+  p.x = x;
+  p.out = out;
+  p.mul = mul;
+  p.add = add;
+  p.mul_batch_stride = mul_batch_stride;
+  p.add_batch_stride = add_batch_stride;
+  p.rows = rows;
+  p.rows_per_batch = rows_per_batch;
+  p.C = C;
+  p.add_one = add_one;
+  p.out_fp16 = out_dtype == CHITU_DTYPE_FP16;
+  p.eps = eps;
+  const int grid = static_cast<int>(std::min<int64_t>(rows, 148 * 8));
+  chitu::layernorm_affine_kernel<<<grid, chitu::kLnThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "layernorm_modulate: launch");
+  return CHITU_OK;
+}
+
+int chitu_b200_gate_residual(float* x, const void* y, int y_dtype, int64_t rows, int64_t rows_per_batch, int C,
+                             const float* gate, int64_t gate_batch_stride, void* stream) {
+  if (!x || !y) return fail(CHITU_E_INVALID, "gate_residual: null pointer");
+  if (rows <= 0 || rows_per_batch <= 0 || C <= 0 || (C & 3))
+    return fail(CHITU_E_INVALID, "gate_residual: rows must be positive and C a multiple of 4");
+  if (y_dtype != CHITU_DTYPE_BF16 && y_dtype != CHITU_DTYPE_FP16)
+    return fail(CHITU_E_UNSUPPORTED, "gate_residual: y must be bf16 or fp16");
+  if ((gate_batch_stride & 3) || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate)) & 15) ||
+      (reinterpret_cast<uintptr_t>(y) & 7))
+    return fail(CHITU_E_INVALID, "gate_residual: x and gate must be 16-byte aligned, y 8-byte aligned");
+  chitu::GateResidualParams p;
+  p.x = x;
+  p.y = y;
+  p.gate = gate;
+  p.gate_batch_stride = gate_batch_stride;
+  p.rows = rows;
+  p.rows_per_batch = rows_per_batch;
+  p.C = C;
+  p.y_fp16 = y_dtype == CHITU_DTYPE_FP16;
+  const long long total = rows * (C >> 2);
+  const int grid = grid_for(total, 256 * 4, 148 * 8);
+  chitu::gate_residual_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "gate_residual: launch");
   return CHITU_OK;
 }
 

@@ -1,0 +1,145 @@
+// Elementwise tails of a DiT block either side of the attention path (HBM-bound streams):
+//
+//   layernorm_affine_kernel   out = LayerNorm(x) * mul + add   -> 16 bit
+//       the modulated input of the self-attention and of the FFN, LayerNorm(x) * (1 + scale) + shift,
+//       and the affine LayerNorm in front of the cross-attention: one pass over the fp32 residual
+//       stream instead of the reference's LayerNorm + float() + multiply + add kernels
+//   gate_residual_kernel      x += y * gate                    (fp32 residual stream, 16-bit branch output)
+//
+// Algorithmic bytes per element: LayerNorm 4 read + 2 written; gated residual 4 + 2 read, 4 written.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace chitu {
+
+constexpr int kLnThreads = 256;
+constexpr int kLnMaxVec = 8;  // float4 per thread: rows of up to 8192 channels
+
+struct LayerNormParams {
+  const float* x;        // [rows, C] fp32 residual stream
+  void* out;             // [rows, C] bf16 / fp16
+  const float* mul;      // [B or 1, C] fp32, or nullptr (= 1)
+  const float* add;      // [B or 1, C] fp32, or nullptr (= 0)
+  long long mul_batch_stride, add_batch_stride;  // elements between batches (0: one vector for all)
+  long long rows, rows_per_batch;
+  int C;
+  int add_one;           // multiply by (1 + mul) instead of mul
+  int out_fp16;
+  float eps;
+};
+
+__device__ __forceinline__ float ln_block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5;
+  __syncthreads();  // red[] may still be read from the previous reduction
+  if ((threadIdx.x & 31) == 0) red[warp] = v;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < kLnThreads / 32; ++w) s += red[w];
+  return s;
+}
+
+// One CTA per row at a time (grid-stride over rows); the row lives in registers between the two
+// reductions (mean, then the centred sum of squares).
+__global__ void __launch_bounds__(kLnThreads)
+layernorm_affine_kernel(const LayerNormParams p) {
+  __shared__ float red[kLnThreads / 32];
+  const int n_vec = p.C >> 2;
+  for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.C);
+    float4 v[kLnMaxVec];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxVec; ++i) {
+      const int idx = threadIdx.x + i * kLnThreads;
+      if (idx < n_vec) {
+        v[i] = __ldcs(src + idx);  // streamed once
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
+    }
+    const float mean = ln_block_sum(sum, red) / static_cast<float>(p.C);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxVec; ++i) {
+      const int idx = threadIdx.x + i * kLnThreads;
+      if (idx < n_vec) {
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+      }
+    }
+    const float rstd = rsqrtf(ln_block_sum(sq, red) / static_cast<float>(p.C) + p.eps);
+    const long long b = row / p.rows_per_batch;
+    const float4* mul = p.mul ? reinterpret_cast<const float4*>(p.mul + b * p.mul_batch_stride) : nullptr;
+    const float4* add = p.add ? reinterpret_cast<const float4*>(p.add + b * p.add_batch_stride) : nullptr;
+    uint2* dst = reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + row * p.C);
+    const float one = p.add_one ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnMaxVec; ++i) {
+      const int idx = threadIdx.x + i * kLnThreads;
+      if (idx < n_vec) {
+        float4 m = mul ? __ldg(mul + idx) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 a = add ? __ldg(add + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mul) { m.x += one; m.y += one; m.z += one; m.w += one; }
+        const float r0 = fmaf(v[i].x * rstd, m.x, a.x), r1 = fmaf(v[i].y * rstd, m.y, a.y);
+        const float r2 = fmaf(v[i].z * rstd, m.z, a.z), r3 = fmaf(v[i].w * rstd, m.w, a.w);
+        uint2 o;
+        if (p.out_fp16) {
+          const __half2 lo = __floats2half2_rn(r0, r1), hi = __floats2half2_rn(r2, r3);
+          o.x = *reinterpret_cast<const uint32_t*>(&lo);
+          o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        } else {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+          o.x = *reinterpret_cast<const uint32_t*>(&lo);
+          o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+        dst[idx] = o;
+      }
+    }
+  }
+}
+
+struct GateResidualParams {
+  float* x;              // [rows, C] fp32, updated in place
+  const void* y;         // [rows, C] bf16 / fp16 branch output
+  const float* gate;     // [B or 1, C] fp32, or nullptr (= 1)
+  long long gate_batch_stride;
+  long long rows, rows_per_batch;
+  int C;
+  int y_fp16;
+};
+
+__global__ void __launch_bounds__(256)
+gate_residual_kernel(const GateResidualParams p) {
+  const int n_vec = p.C >> 2;
+  const long long total = p.rows * n_vec;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long row = i / n_vec;
+    const int idx = static_cast<int>(i - row * n_vec);
+    float4 xv = reinterpret_cast<float4*>(p.x)[i];
+    const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p.y) + i);
+    float2 y0, y1;
+    if (p.y_fp16) {
+      y0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      y1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    } else {
+      y0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      y1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    }
+    float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (p.gate) g = __ldg(reinterpret_cast<const float4*>(p.gate + (row / p.rows_per_batch) * p.gate_batch_stride) + idx);
+    xv.x = fmaf(y0.x, g.x, xv.x);
+    xv.y = fmaf(y0.y, g.y, xv.y);
+    xv.z = fmaf(y1.x, g.z, xv.z);
+    xv.w = fmaf(y1.y, g.w, xv.w);
+    reinterpret_cast<float4*>(p.x)[i] = xv;
+  }
+}
+
+}  // namespace chitu

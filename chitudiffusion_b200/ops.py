@@ -379,6 +379,54 @@ def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     return dst
 
 
+def layernorm_modulate(x: torch.Tensor, mul: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None,
+                       add_one: bool = False, eps: float = 1e-6, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``LayerNorm(x) * m + a`` for fp32 ``x [B, L, C]``; ``mul`` / ``add`` are ``[C]``, ``[1, C]``-like or ``[B, C]``-like
+    fp32 (``m = 1 + mul`` with ``add_one``); see ``chitu_b200_layernorm_modulate``."""
+    _require_cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("layernorm_modulate: x must be a contiguous fp32 [B, L, C] tensor")
+    B, L, C = x.shape
+
+    def vec(t):
+        if t is None:
+            return None, 0
+        t = t.reshape(-1, C)
+        if t.dtype != torch.float32 or t.shape[0] not in (1, B) or t.stride(1) != 1:
+            raise ValueError("layernorm_modulate: mul / add must be fp32 with C channels for 1 or B batches")
+        return t, (t.stride(0) if t.shape[0] == B and B > 1 else 0)
+
+    (m, ms), (a, as_) = vec(mul), vec(add)
+    out = torch.empty((B, L, C), dtype=out_dtype, device=x.device)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.chitu_b200_layernorm_modulate(
+            x.data_ptr(), out.data_ptr(), _DTYPES[out_dtype], B * L, L, C, m.data_ptr() if m is not None else None, ms,
+            a.data_ptr() if a is not None else None, as_, int(add_one), float(eps), _stream_ptr(x.device))
+    _lib.check(rc, "layernorm_modulate")
+    return out
+
+
+def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In place ``x += y * gate`` (``x`` fp32 ``[B, L, C]``, ``y`` 16-bit, ``gate`` fp32 per batch and channel or None)."""
+    _require_cuda(x, y)
+    if x.dtype != torch.float32 or x.dim() != 3 or not x.is_contiguous() or y.shape != x.shape or not y.is_contiguous():
+        raise ValueError("gate_residual: x must be contiguous fp32 [B, L, C] and y contiguous of the same shape")
+    B, L, C = x.shape
+    g, gs = None, 0
+    if gate is not None:
+        g = gate.reshape(-1, C)
+        if g.dtype != torch.float32 or g.shape[0] not in (1, B) or g.stride(1) != 1:
+            raise ValueError("gate_residual: gate must be fp32 with C channels for 1 or B batches")
+        gs = g.stride(0) if g.shape[0] == B and B > 1 else 0
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.chitu_b200_gate_residual(x.data_ptr(), y.data_ptr(), _DTYPES[y.dtype], B * L, L, C,
+                                          g.data_ptr() if g is not None else None, gs, _stream_ptr(x.device))
+    _lib.check(rc, "gate_residual")
+    return x
+
+
 def peer_copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width: int, rows: int,
                  device: torch.device) -> None:
     """``rows`` pieces of ``width`` bytes between device buffers (either may be peer-mapped), on the copy engines."""

@@ -44,3 +44,4 @@ from .layouts import (  # noqa: F401
     up_rank_lists,
 )
 from .quantised import attention_q8  # noqa: F401,E402
+from .dit_block import layer_norm_fp32, wan_block  # noqa: F401,E402

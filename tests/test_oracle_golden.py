@@ -95,3 +95,20 @@ def test_pad_split(golden):
     assert len(parts) == len(c["parts"])
     for a, b in zip(parts, c["parts"]):
         assert torch.equal(a, b)
+
+
+def test_wan_block_matches_reference_block():
+    """The restated DiT block against the output of the reference's WanAttentionBlock (fixture made by
+    tests/golden/make_golden_block.py)."""
+    import os
+
+    g = torch.load(os.path.join(os.path.dirname(__file__), "golden", "wan_block_golden.pt"), weights_only=False)
+    params = {k: v.float() for k, v in g["params"].items()}
+    out = oracle.wan_block(g["x"].float(), g["e"].float(), params, g["grid"][0].tolist(), g["context"].float(),
+                           g["heads"], self_attn_bf16=True)
+    assert out.dtype == torch.float32 and out.shape == g["out"].shape
+    assert (out - g["out"]).abs().max().item() <= 2e-5
+    # the all-fp32 form differs from it only by the bf16 rounding of the self-attention operands
+    out32 = oracle.wan_block(g["x"].float(), g["e"].float(), params, g["grid"][0].tolist(), g["context"].float(),
+                             g["heads"])
+    assert (out32 - g["out"]).abs().max().item() <= 2e-2
