@@ -41,8 +41,8 @@ WORKLOADS = {
     # BASELINE config 1: one Wan2.1-1.3B self-attention layer at 480p x 17 frames
     "wan1.3b-480p-17f-layer": dict(kind="wan", grid=(5, 30, 52), H=12, D=128, blocks=1),
     # BASELINE config 3 / 4: Wan2.1 1.3B 480p x 81 frames, Wan2.1 14B 720p x 81 frames
-    "wan1.3b-480p-81f": dict(kind="wan", grid=(21, 30, 52), H=12, D=128, blocks=30),
-    "wan14b-720p-81f": dict(kind="wan", grid=(21, 45, 80), H=40, D=128, blocks=40),
+    "wan1.3b-480p-81f": dict(kind="wan", grid=(21, 30, 52), H=12, D=128, blocks=30, ffn=8960, text=512),
+    "wan14b-720p-81f": dict(kind="wan", grid=(21, 45, 80), H=40, D=128, blocks=40, ffn=13824, text=512),
 }
 DEFAULT_WORKLOAD = "flux1-dev-1024-joint-attn"
 INPUT_SETS = 4  # distinct q/k/v projection sets cycled over the blocks: 4 x 85 MB > the 126 MB L2
@@ -294,6 +294,71 @@ def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layou
             "input": "one device-generated q/k/v set (2.3 GB, larger than L2)"}
 
 
+def dit_flops_per_layer(w):
+    """Multiply-add FLOPs of one Wan block: self-attention, text cross-attention and the nine GEMMs."""
+    S, C, T, F = seq_len(w), w["H"] * w["D"], w["text"], w["ffn"]
+    gemm = 2.0 * S * (4 * C * C + 2 * C * C + 2 * C * F) + 2.0 * T * 2 * C * C
+    return flops_per_block(w) + 4.0 * S * T * C + gemm
+
+
+def measure_dit(name, rank, world, device, exchange, sync, dist, layers=None, forwards=2):
+    """Latency of one random-init DiT forward (all layers: modulated LayerNorm, QKV GEMM, norm + rotary,
+    context-parallel self-attention, text cross-attention, FFN) with the sequence sharded over the ranks."""
+    from chitudiffusion_b200 import B200AttnBackend, comm
+    from chitudiffusion_b200.context_parallel import B200ContextParallel
+    from chitudiffusion_b200.dit import WanDiTStack
+
+    w = WORKLOADS[name]
+    n_layers = layers or w["blocks"]
+    H, C = w["H"], w["H"] * w["D"]
+    backend = B200AttnBackend("b200")
+    attn, parallelism = backend, "single"
+    if world > 1:
+        up = max(u for u in (8, 4, 2, 1) if u <= world and H % u == 0 and world % u == 0)
+        comm.destroy_diffusion_parallel_groups()
+        comm.initialize_diffusion_parallel_groups(1, world, up)
+        attn = B200ContextParallel(backend, up, cp_backend="ucp")
+        attn.ulysses_exchange = exchange
+        parallelism = f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else "") + f"-{exchange}"
+    stack = WanDiTStack(n_layers, C, w["ffn"], H, device, seed=3, cp_size=world, cp_rank=rank)
+    s_local = seq_len(w) // world
+    gen = torch.Generator(device=device).manual_seed(5 + rank)
+    x0 = torch.randn(1, s_local, C, generator=gen, device=device)
+    e = 0.1 * torch.randn(1, 6, C, generator=gen, device=device)
+    ctx = torch.randn(1, w["text"], C, generator=gen, device=device).to(torch.bfloat16)
+    x = x0.clone()
+    run = lambda: stack(x, e, w["grid"], ctx, attn, backend)  # noqa: E731
+    run()
+    fn = run
+    graphed = world > 1 and exchange == "peer"
+    if graphed:
+        sync()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run()
+        fn = graph.replay
+    x.copy_(x0)
+    sync()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(forwards):
+        fn()
+    t1.record()
+    sync()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    fwd_ms = float(ms.item()) / forwards
+    finite = bool(torch.isfinite(x).all().item())
+    flops = dit_flops_per_layer(w) * n_layers
+    return {"workload": name + "-dit-forward", "layers": n_layers, "seq_len": seq_len(w), "hidden": C, "ffn": w["ffn"],
+            "text_tokens": w["text"], "forward_ms": round(fwd_ms, 2), "step_ms_cond_plus_uncond": round(2 * fwd_ms, 2),
+            "forwards_timed": forwards, "tflops": round(flops / (fwd_ms * 1e-3) / 1e12, 1),
+            "attention_share_of_flops": round(flops_per_block(w) / dit_flops_per_layer(w), 3),
+            "parallelism": parallelism, "cuda_graph": graphed, "finite": finite,
+            "weights": "random-init N(0, 0.02^2) bf16, fp32 residual stream; GEMMs are library calls"}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -397,6 +462,11 @@ def run_ours(args):
                 r = measure_extra("wan14b-720p-81f", 2, rank, world, device, args.exchange, sync, dist, layout=lay)
                 extra["layouts"].append({k: r[k] for k in ("parallelism", "ms_per_layer", "value", "per_gpu_tflops")})
 
+    dit = None
+    if args.dit and not args.profile:
+        dit = [measure_dit(n.strip(), rank, world, device, args.exchange, sync, dist)
+               for n in args.dit.split(",") if n.strip()]
+
     from chitudiffusion_b200 import ops
 
     ops.check_status(device)
@@ -448,6 +518,8 @@ def run_ours(args):
     }
     if extra is not None:
         line["also"] = [extra]
+    if dit:
+        line["dit_step"] = dit
     if world == 1 and not args.profile:
         line["cpu_baseline"] = cpu_baseline(w, repeats=3)
     if args.profile:
@@ -544,6 +616,8 @@ def main():
                     help="N > 1: context-parallel layout (auto = the widest Ulysses degree the head count allows)")
     ap.add_argument("--extra-layouts", default="",
                     help="N > 1: comma-separated layouts (ring, agkv, usp) to time on the second workload as well")
+    ap.add_argument("--dit", default="wan1.3b-480p-81f",
+                    help="comma-separated Wan workloads whose full DiT forward latency is reported too ('' = none)")
     ap.add_argument("--no-extra", action="store_true", help="skip the second (Wan2.1-14B 720p) workload")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch kernel by kernel instead of replaying a graph")
     ap.add_argument("--profile", action="store_true",
