@@ -332,6 +332,9 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
   if (!sh.out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
   const int B = sh.B, S = sh.S, H = sh.H, D = sh.D;
   if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(CHITU_E_INVALID, "qk_norm_rope: bad shape");
+  if (static_cast<long long>(B) * S + 4096LL * 8 >= (1LL << 31) || sh.pos_offset < 0 ||
+      sh.pos_offset + S >= (1LL << 31))
+    return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: token count and positions must stay below 2^31");
   if (D & 7) return fail(CHITU_E_INVALID, "qk_norm_rope: head_dim must be a multiple of 8");
   const long long C = static_cast<long long>(H) * D;
   if (C > chitu::kNormMaxThreads * 8)
@@ -414,9 +417,12 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
   }
   // one 8-channel vector per thread, whole warps; the grid fills the 148 SMs a few CTAs deep
   const int threads = static_cast<int>(((C / 8) + 31) / 32 * 32);
-  const int per_sm = threads <= 256 ? 8 : (threads <= 512 ? 4 : 2);
+  // CTAs that can be resident per SM: 80 registers per thread up to 512 threads, 64 above
+  const int per_sm = std::max(1, std::min(2048 / threads, 65536 / (threads * (threads <= 512 ? 80 : 64))));
   const int per_job = (per_sm + n_jobs - 1) / n_jobs;
-  const unsigned gx = static_cast<unsigned>(tokens < 148LL * per_job ? tokens : 148LL * per_job);
+  const long long tok_per_iter = sh.in_dtype == CHITU_DTYPE_FP32 ? 2 : 4;  // NormRopeTokens
+  const long long iters = (tokens + tok_per_iter - 1) / tok_per_iter;
+  const unsigned gx = static_cast<unsigned>(iters < 148LL * per_job ? iters : 148LL * per_job);
   const dim3 grid(gx, n_jobs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // the kernel is specialised on the modes of job 0; other jobs either share them or are plain
@@ -426,7 +432,11 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
     const bool plain = jobs[j].norm_mode == 2 && jobs[j].rope_mode == 0;
     if (!same && !plain) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: jobs of one launch share modes or are plain copies");
   }
-#define CHITU_NR_LAUNCH(IN, NM, RM) chitu::qk_norm_rope_kernel<IN, NM, RM><<<grid, threads, 0, st>>>(batch)
+#define CHITU_NR_LAUNCH(IN, NM, RM)                                                    \
+  if (threads <= 512)                                                                  \
+    chitu::qk_norm_rope_kernel<IN, NM, RM><<<grid, threads, 0, st>>>(batch);           \
+  else                                                                                 \
+    chitu::qk_norm_rope_wide_kernel<IN, NM, RM><<<grid, threads, 0, st>>>(batch)
 #define CHITU_NR_ROPE(IN, NM)                     \
   switch (rm) {                                   \
     case 0: CHITU_NR_LAUNCH(IN, NM, 0); break;    \

@@ -196,19 +196,56 @@ struct NormRopeParams {
 
 constexpr int kNormMaxThreads = 1024;  // one 8-channel vector per thread: up to 8192 channels per token
 
-// 8 consecutive input elements of a token row as floats (16-byte loads)
+// 8 consecutive input elements of a token row, as loaded (one 16-byte request for 16-bit inputs,
+// two for fp32) and converted to floats
 template <int kInDtype>
-__device__ __forceinline__ void ld8(const void* p, size_t i, float (&v)[8]) {
-  const float4 a = ld4(p, kInDtype, i);
-  const float4 c = ld4(p, kInDtype, i + 4);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+struct RawVec8 {
+  uint4 a;
+};
+template <>
+struct RawVec8<kFP32> {
+  uint4 a, b;
+};
+template <int kInDtype>
+__device__ __forceinline__ RawVec8<kInDtype> ld_raw8(const void* p, size_t i) {
+  RawVec8<kInDtype> r;
+  if constexpr (kInDtype == kFP32) {
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(p) + i);
+    r.a = __ldcs(src);
+    r.b = __ldcs(src + 1);
+  } else {
+    r.a = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + i));
+  }
+  return r;
+}
+template <int kInDtype>
+__device__ __forceinline__ void unpack8(const RawVec8<kInDtype>& r, float (&v)[8]) {
+  if constexpr (kInDtype == kFP32) {
+    v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z);
+    v[3] = __uint_as_float(r.a.w); v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y);
+    v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
+  } else {
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (kInDtype == kBF16) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+      }
+    }
+  }
 }
 
 // Persistent kernel: thread i of the CTA owns channels [8i, 8i+8) of every token the CTA
-// visits, so the norm weights live in registers; the next token's vector is loaded before the
-// current one is transformed.  Full-width statistics need one block reduction per token,
-// per-head statistics only warp shuffles.
+// visits, so the norm weights live in registers.  A CTA works on kTok consecutive tokens per
+// iteration and has the raw vectors of the next kTok tokens in flight meanwhile (up to 128 bytes of
+// loads per thread: the pass is latency-bound, and bytes in flight are what buys bandwidth).
+// Full-width statistics need one block reduction per iteration, per-head statistics only warp
+// shuffles.
 // Up to three tensors (q, k, v) of one layer share a launch: blockIdx.y picks the job.  Jobs 0 and
 // 1 use the template's norm / rotary modes; a job whose own modes are (2, 0) is a plain cast /
 // scatter (the v tensor).
@@ -216,13 +253,20 @@ struct NormRopeBatch {
   NormRopeParams job[3];
 };
 
-template <int kInDtype, int kNormModeT, int kRopeModeT>
-__global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const __grid_constant__ NormRopeBatch batch) {
-  const NormRopeParams& p = batch.job[blockIdx.y];
-  const bool plain = (p.norm_mode == 2 && p.rope_mode == 0);
-  const int kNormMode = plain ? 2 : kNormModeT;
-  const int kRopeMode = plain ? 0 : kRopeModeT;
-  __shared__ float red[2][kNormMaxThreads / 32];
+// tokens per iteration: 4 for 16-bit inputs, 2 for fp32 (the same bytes in flight)
+template <int kInDtype>
+struct NormRopeTokens {
+  static constexpr int value = kInDtype == kFP32 ? 2 : 4;
+};
+
+// One job of a launch.  Everything that does not change inside a launch is a template argument, so
+// the token loop carries no run-time mode tests: kNormMode / kRopeMode as documented at
+// NormRopeParams, kRound 0 (no intermediate rounding), 1 (round the normalised value to the input
+// type, as `type_as(x)` does) or 2 (also round after the weight multiply), kOutBf16 the store type.
+template <int kInDtype, int kNormMode, int kRopeMode, int kRound, bool kOutBf16>
+__device__ __forceinline__ void qk_norm_rope_job(const NormRopeParams& p, float (*red)[NormRopeTokens<kInDtype>::value][kNormMaxThreads / 32]) {
+  constexpr int kTok = NormRopeTokens<kInDtype>::value;
+  constexpr int kOutDtype = kOutBf16 ? kBF16 : kFP16;
   const int C = p.H * p.D;
   const int c0 = threadIdx.x * 8;
   const bool active = c0 < C;
@@ -231,116 +275,219 @@ __global__ void __launch_bounds__(kNormMaxThreads) qk_norm_rope_kernel(const __g
   const int half_d = p.D >> 1;
   const int vec_per_head = p.D >> 3;
   const int n_warps = blockDim.x >> 5;
-  const long long tokens = static_cast<long long>(p.B) * p.S;
+  const int tokens = p.B * p.S;  // the host refuses problems whose token count or positions pass 2^31
+  const float inv_n = 1.0f / static_cast<float>(kNormMode == 0 ? C : p.D);
 
   float wgt[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) wgt[e] = 1.f;
-  const bool has_w = (kNormMode != 2) && p.weight != nullptr;
-  if (has_w && active) {
+  if (kNormMode != 2 && p.weight != nullptr && active) {
     const int w0 = (kNormMode == 0) ? c0 : d0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) wgt[e] = ld_as_float(p.weight, p.w_dtype, w0 + e);
   }
-  const bool round_w = p.round_mid && p.w_dtype != kFP32 && kInDtype != kFP32;
   const int grp = h / p.heads_per_group;
   const long long out_h = (p.n_out_ptrs > 0 ? 0 : grp * p.os_g) + (h % p.heads_per_group) * p.os_h + d0;
-  uint16_t* const out_base = static_cast<uint16_t*>(p.n_out_ptrs > 0 ? p.out_ptrs[grp] : p.out);
+  uint16_t* const out_base = static_cast<uint16_t*>(p.n_out_ptrs > 0 ? p.out_ptrs[grp] : p.out) + out_h;
+  const int grid_tokens = p.gf * p.gh * p.gw;
+  const int pos0 = static_cast<int>(p.pos_offset);
 
-  long long token = blockIdx.x;
-  float v[8], nxt[8];
+  // 32-bit index arithmetic throughout: a 64-bit division costs more than the rest of a token's math
+  int base = static_cast<int>(blockIdx.x) * kTok;
+  const int step = static_cast<int>(gridDim.x) * kTok;
+  RawVec8<kInDtype> cur[kTok], nxt[kTok];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) v[e] = nxt[e] = 0.f;
-  if (active && token < tokens) ld8<kInDtype>(p.x, static_cast<size_t>(token) * p.x_row_stride + c0, v);
+  for (int i = 0; i < kTok; ++i) {
+    cur[i].a = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (kInDtype == kFP32) cur[i].b = make_uint4(0u, 0u, 0u, 0u);
+    nxt[i] = cur[i];
+    if (active && base + i < tokens)
+      cur[i] = ld_raw8<kInDtype>(p.x, static_cast<size_t>(base + i) * p.x_row_stride + c0);
+  }
   int phase = 0;
-  for (; token < tokens; token += gridDim.x, phase ^= 1) {
-    const long long t_next = token + gridDim.x;
-    if (active && t_next < tokens) ld8<kInDtype>(p.x, static_cast<size_t>(t_next) * p.x_row_stride + c0, nxt);
-
-    // Position and rotary factors first: their (L2) loads overlap the reduction below.
-    const int b = static_cast<int>(token / p.S);
-    const int s = static_cast<int>(token - static_cast<long long>(b) * p.S);
-    float rc[4], rs[4];
-    bool rotate = false;
-    if (kRopeMode != 0 && active) {
-      const long long n = p.pos_offset + s;
-      if (kRopeMode == 2) {
-        if (n < p.table_rows) {
-          rotate = true;
-          // per-token table: the four (cos, sin) pairs of this vector are 32 contiguous bytes
-          const float4* trow = reinterpret_cast<const float4*>(p.table + n * half_d + (d0 >> 1));
-          const float4 c0v = __ldg(trow), c1v = __ldg(trow + 1);
-          rc[0] = c0v.x; rs[0] = c0v.y; rc[1] = c0v.z; rs[1] = c0v.w;
-          rc[2] = c1v.x; rs[2] = c1v.y; rc[3] = c1v.z; rs[3] = c1v.w;
-        }
-      } else if (n < static_cast<long long>(p.gf) * p.gh * p.gw) {  // padding tokens past the grid pass through
-        rotate = true;
-        const int pf = static_cast<int>(n / (static_cast<long long>(p.gh) * p.gw));
-        const int ph = static_cast<int>((n / p.gw) % p.gh);
-        const int pw = static_cast<int>(n % p.gw);
+  for (; base < tokens; base += step, phase ^= 1) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int j = (d0 >> 1) + q;
-          const long long trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
-          const float2 cs = __ldg(&p.table[trow * half_d + j]);
-          rc[q] = cs.x;
-          rs[q] = cs.y;
-        }
-      }
-    }
+    for (int i = 0; i < kTok; ++i)
+      if (active && base + step + i < tokens)
+        nxt[i] = ld_raw8<kInDtype>(p.x, static_cast<size_t>(base + step + i) * p.x_row_stride + c0);
 
-    float rstd = 1.f;
-    if (kNormMode != 2) {
-      float ss = 0.f;
+    float rstd_full[kTok];
+    if constexpr (kNormMode == 0) {
+      // full-width statistics of the kTok tokens with one barrier
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
-      if (kNormMode == 0) {
+      for (int i = 0; i < kTok; ++i) {
+        float v[8];
+        unpack8<kInDtype>(cur[i], v);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if ((threadIdx.x & 31) == 0) red[phase][threadIdx.x >> 5] = ss;
-        __syncthreads();  // red[phase] is rewritten two tokens later, after the next barrier
-        float tot = 0.f;
-        for (int i = 0; i < n_warps; ++i) tot += red[phase][i];
-        rstd = rsqrtf(tot / static_cast<float>(C) + p.eps);
-      } else {
-        for (int o = vec_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        rstd = rsqrtf(ss / static_cast<float>(p.D) + p.eps);
+        if ((threadIdx.x & 31) == 0) red[phase][i][threadIdx.x >> 5] = ss;
+      }
+      __syncthreads();  // red[phase] is rewritten two iterations later, after the next barrier
+      // every warp sums the per-warp partials itself: one shared-memory read per lane, then shuffles
+#pragma unroll
+      for (int i = 0; i < kTok; ++i) {
+        const int lane = threadIdx.x & 31;
+        float tot = lane < n_warps ? red[phase][i][lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+        rstd_full[i] = rsqrtf(tot * inv_n + p.eps);
       }
     }
-    if (active) {
-      float y[8];
+
+    // batch and position of the first token of the iteration; the others follow by increments
+    int b = base / p.S;
+    int s = base - b * p.S;
+    int pf = 0, ph = 0, pw = 0;  // (frame, row, column) of the token on the three-axis grid
+    if constexpr (kRopeMode == 1) {
+      const int n = pos0 + s;
+      const int row = n / p.gw;
+      pw = n - row * p.gw;
+      pf = row / p.gh;
+      ph = row - pf * p.gh;
+    }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float t = v[e];
-        if (kNormMode != 2) {
-          t *= rstd;
-          if (p.round_mid) t = round_to(t, kInDtype);
-          if (has_w) {
-            t *= wgt[e];
-            if (round_w) t = round_to(t, p.w_dtype);
+    for (int i = 0; i < kTok; ++i) {
+      if (base + i >= tokens) break;  // uniform over the CTA
+      float v[8];
+      unpack8<kInDtype>(cur[i], v);
+      // rotary factors first: their (L1 / L2) loads overlap the statistics below
+      float rc[4], rs[4];
+      bool rotate = false;
+      if (kRopeMode != 0 && active) {
+        const int n = pos0 + s;
+        if constexpr (kRopeMode == 2) {
+          if (n < p.table_rows) {
+            rotate = true;
+            // per-token table: the four (cos, sin) pairs of this vector are 32 contiguous bytes
+            const float4* trow =
+                reinterpret_cast<const float4*>(p.table + static_cast<long long>(n) * half_d + (d0 >> 1));
+            const float4 c0v = __ldg(trow), c1v = __ldg(trow + 1);
+            rc[0] = c0v.x; rs[0] = c0v.y; rc[1] = c0v.z; rs[1] = c0v.w;
+            rc[2] = c1v.x; rs[2] = c1v.y; rc[3] = c1v.z; rs[3] = c1v.w;
+          }
+        } else if (n < grid_tokens) {  // padding tokens past the grid pass through
+          rotate = true;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int j = (d0 >> 1) + q;
+            const int trow = (j < p.n_t) ? pf : ((j < p.n_t + p.n_h) ? ph : pw);
+            const float2 cs = __ldg(&p.table[trow * half_d + j]);
+            rc[q] = cs.x;
+            rs[q] = cs.y;
           }
         }
-        y[e] = t;
       }
-      if (rotate) {
+
+      float rstd = 1.f;
+      if constexpr (kNormMode == 0) {
+        rstd = rstd_full[i];
+      } else if constexpr (kNormMode == 1) {
+        float ss = 0.f;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float re = y[2 * q] * rc[q] - y[2 * q + 1] * rs[q];
-          const float im = y[2 * q] * rs[q] + y[2 * q + 1] * rc[q];
-          y[2 * q] = re;
-          y[2 * q + 1] = im;
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+        if (vec_per_head == 16) {  // head_dim 128: the sixteen lanes of a head
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        } else {
+          for (int o = vec_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        }
+        rstd = rsqrtf(ss * inv_n + p.eps);
+      }
+      if (active) {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float t = v[e];
+          if constexpr (kNormMode != 2) {
+            t *= rstd;
+            if constexpr (kRound >= 1) t = round_to(t, kInDtype);
+            t *= wgt[e];
+            if constexpr (kRound == 2) t = round_to(t, p.w_dtype);
+          }
+          y[e] = t;
+        }
+        if (rotate) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float re = y[2 * q] * rc[q] - y[2 * q + 1] * rs[q];
+            const float im = y[2 * q] * rs[q] + y[2 * q + 1] * rc[q];
+            y[2 * q] = re;
+            y[2 * q + 1] = im;
+          }
+        }
+        uint4 o;
+        o.x = pack16(y[0], y[1], kOutDtype);
+        o.y = pack16(y[2], y[3], kOutDtype);
+        o.z = pack16(y[4], y[5], kOutDtype);
+        o.w = pack16(y[6], y[7], kOutDtype);
+        *reinterpret_cast<uint4*>(out_base + b * p.os_b + s * p.os_s) = o;
+      }
+      if (++s == p.S) {  // next batch: positions restart at the offset
+        s = 0;
+        ++b;
+        if constexpr (kRopeMode == 1) {
+          const int row = pos0 / p.gw;
+          pw = pos0 - row * p.gw;
+          pf = row / p.gh;
+          ph = row - pf * p.gh;
+        }
+      } else if constexpr (kRopeMode == 1) {
+        if (++pw == p.gw) {
+          pw = 0;
+          if (++ph == p.gh) {
+            ph = 0;
+            ++pf;
+          }
         }
       }
-      uint4 o;
-      o.x = pack16(y[0], y[1], p.out_dtype);
-      o.y = pack16(y[2], y[3], p.out_dtype);
-      o.z = pack16(y[4], y[5], p.out_dtype);
-      o.w = pack16(y[6], y[7], p.out_dtype);
-      *reinterpret_cast<uint4*>(out_base + b * p.os_b + s * p.os_s + out_h) = o;
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = nxt[e];
+    for (int i = 0; i < kTok; ++i) cur[i] = nxt[i];
   }
+}
+
+// Picks the instance of the job blockIdx.y points at: a job whose own modes are (2, 0) is a plain
+// cast / scatter whatever the launch's template modes are.
+template <int kInDtype, int kNormModeT, int kRopeModeT>
+__device__ __forceinline__ void qk_norm_rope_body(const NormRopeBatch& batch) {
+  __shared__ float red[2][NormRopeTokens<kInDtype>::value][kNormMaxThreads / 32];
+  const NormRopeParams& p = batch.job[blockIdx.y];
+  const bool out_bf16 = p.out_dtype == kBF16;
+  if (p.norm_mode == 2 && p.rope_mode == 0) {
+    if (out_bf16) qk_norm_rope_job<kInDtype, 2, 0, 0, true>(p, red);
+    else qk_norm_rope_job<kInDtype, 2, 0, 0, false>(p, red);
+    return;
+  }
+  // rounding of the weight product only where the reference's dtypes make it round (16-bit weight
+  // and input); a missing weight multiplies by one, exactly
+  const bool round_mid = p.round_mid && kNormModeT != 2;
+  const bool round_w = round_mid && p.weight != nullptr && p.w_dtype != kFP32 && kInDtype != kFP32;
+  const int round = round_w ? 2 : (round_mid ? 1 : 0);
+  if (out_bf16) {
+    if (round == 0) qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 0, true>(p, red);
+    else if (round == 1) qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 1, true>(p, red);
+    else qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 2, true>(p, red);
+  } else {
+    if (round == 0) qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 0, false>(p, red);
+    else if (round == 1) qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 1, false>(p, red);
+    else qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 2, false>(p, red);
+  }
+}
+
+// Two entry points that differ only in their register budget: rows of up to 4096 channels (at most
+// 512 threads) get 80 registers per thread - two iterations of raw vectors without spilling, two
+// CTAs of 384 threads per SM; wider rows run with the 64 registers that 1024 threads leave.
+template <int kInDtype, int kNormModeT, int kRopeModeT>
+__global__ void __maxnreg__(80) qk_norm_rope_kernel(const __grid_constant__ NormRopeBatch batch) {
+  qk_norm_rope_body<kInDtype, kNormModeT, kRopeModeT>(batch);
+}
+template <int kInDtype, int kNormModeT, int kRopeModeT>
+__global__ void __launch_bounds__(kNormMaxThreads)
+qk_norm_rope_wide_kernel(const __grid_constant__ NormRopeBatch batch) {
+  qk_norm_rope_body<kInDtype, kNormModeT, kRopeModeT>(batch);
 }
 
 // ----------------------------------------------------------------------------
