@@ -130,7 +130,7 @@ class PeerRing:
     """
 
     def __init__(self, group: CommGroup, ulysses: int, B: int, s: int, H: int, D: int, dtype: torch.dtype,
-                 device: torch.device, mode: str = "ring", merger_factory=None):
+                 device: torch.device, mode: str = "ring", merger_factory=None, direction: int = 1):
         import torch.distributed._symmetric_memory as symm_mem
 
         P = group.group_size
@@ -142,6 +142,7 @@ class PeerRing:
         self.group, self.P, self.U, self.R, self.rank = group, P, U, P // U, group.rank_in_group
         self.mode, self.B, self.s, self.H, self.D, self.hc = mode, B, s, H, D, H // U
         self.dtype, self.device, self.merger_factory = dtype, device, merger_factory
+        self.direction = 1 if direction >= 0 else -1  # -1: blocks arrive in the order of a send-to-next ring
         es = torch.empty((), dtype=dtype).element_size()
         self.es = es
         self.block_bytes = B * U * s * self.hc * D * es  # one of q / k / v of a ring block
@@ -219,7 +220,7 @@ class PeerRing:
         for t in range(self.R):
             nxt = None
             if t + 1 < self.R:
-                owner = (self.rank + (t + 1) * self.U) % self.P
+                owner = (self.rank + self.direction * (t + 1) * self.U) % self.P
                 kb, vb = self.k_fetch[(t + 1) & 1], self.v_fetch[(t + 1) & 1]
                 self.side.wait_stream(cur)  # the attention call that last read these two buffers is enqueued
                 with torch.cuda.stream(self.side):

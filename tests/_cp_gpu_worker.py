@@ -76,6 +76,30 @@ def main():
         results[name] = max(rel_err(first, full[:, sl]), rel_err(second, full2[:, sl]))
         print(f"rank {rank}: {name} done", flush=True)
 
+    # stand-alone graphed ring (send-to-next order, GQA keys / values) and the image-CP core
+    from chitudiffusion_b200.graphed_ring import B200GraphedRingAttention
+    from chitudiffusion_b200.image_cp import B200ImageContextParallel
+
+    comm.destroy_diffusion_parallel_groups()
+    comm.initialize_diffusion_parallel_groups(1, world, world)
+    kg, vg = ((torch.randn(1, S, H // 2, D, generator=gen)).to(torch.bfloat16) for _ in range(2))
+    full_gqa = oracle.sdpa_fp32(q, kg.repeat_interleave(2, dim=2), vg.repeat_interleave(2, dim=2))
+    ring = B200GraphedRingAttention(comm.get_cp_group(), use_cuda_graph=True)
+    o1 = ring(ql, kg[:, sl].contiguous().to(dev), vg[:, sl].contiguous().to(dev))
+    o2 = ring(ql, kl, vl)
+    o3 = ring(ql, kl, vl)  # replay
+    assert o1.dtype == torch.bfloat16 and len(ring._graph_cache) == 2
+    results["graphed_ring"] = max(rel_err(o1, full_gqa[:, sl]), rel_err(o2, full[:, sl]), rel_err(o3, full[:, sl]))
+    print(f"rank {rank}: graphed_ring done", flush=True)
+    txt = [(torch.randn(1, 24, H, D, generator=gen)).to(torch.bfloat16) for _ in range(3)]
+    full_it = oracle.sdpa_fp32(torch.cat([txt[0], q], 1), torch.cat([txt[1], k], 1), torch.cat([txt[2], v], 1))
+    for mode in ("ulysses", "ring", "agkv"):
+        core = B200ImageContextParallel(backend, mode=mode)
+        core.enable(comm.get_cp_group())
+        t_out, i_out = core.attention(*(t.to(dev) for t in txt), ql, kl, vl)
+        results[f"imagecp_{mode}"] = max(rel_err(t_out, full_it[:, :24]), rel_err(i_out, full_it[:, 24:][:, sl]))
+    print(f"rank {rank}: imagecp done", flush=True)
+
     # peer-store exchange: norm + rotary pre-pass scattered to the owners, attention scattered back
     comm.destroy_diffusion_parallel_groups()
     comm.initialize_diffusion_parallel_groups(1, world, world)

@@ -90,6 +90,26 @@ def main():
         err_i = (i_out[:, :valid].float() - full[:, txt_len + r * ls: txt_len + r * ls + valid]).abs().max().item()
         ok = err_t < 2e-6 and err_i < 2e-6
         print(f"rank {rank} fulltxt err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
+    elif mode.startswith("imagecp_"):
+        from chitudiffusion_b200.image_cp import B200ImageContextParallel
+
+        txt_len = 5
+        tq, tk, tv = (torch.randn(1, txt_len, H, D, generator=gen) for _ in range(3))
+        iq, ik, iv = (torch.randn(1, s * cp_size, H, D, generator=gen) for _ in range(3))
+        full = oracle.sdpa_fp32(torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1))
+        core = B200ImageContextParallel(wrapper, mode=mode.split("_", 1)[1], ulysses_size=up,
+                                        merger_factory=wrapper._merger_factory)
+        assert core.attn_backend is wrapper.attn and not core.enabled
+        core.enable(wrapper.group)
+        sl = slice(r * s, (r + 1) * s)
+        t_out, i_out = core.attention(tq, tk, tv, iq[:, sl], ik[:, sl], iv[:, sl])
+        packed = core._attention_from_packed(torch.cat([iq[:, sl], tq], 1), torch.cat([ik[:, sl], tk], 1),
+                                             torch.cat([iv[:, sl], tv], 1), s)
+        err_t = (t_out.float() - full[:, :txt_len]).abs().max().item()
+        err_i = (i_out.float() - full[:, txt_len + r * s: txt_len + (r + 1) * s]).abs().max().item()
+        ok = (err_t < 2e-6 and err_i < 2e-6 and torch.equal(packed[0], t_out) and torch.equal(packed[1], i_out)
+              and core.stats()["calls"] == 2)
+        print(f"rank {rank} {mode} err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
     elif mode == "fused":
         S = s * cp_size
         q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))

@@ -30,6 +30,9 @@ def _run(nproc, cfg_size, up, cp_backend, mode):
     (4, 1, 2, "ucp", "fulltxt"),    # Qwen layout, padded tail, Ulysses x ring
     (2, 1, 2, "agcp", "fulltxt"),
     (2, 1, 2, "ucp", "fused"),      # producer-callback API (falls back to the serial schedule on CPU)
+    (4, 1, 2, "ucp", "imagecp_unified"),   # image-CP core: Ulysses-2 x ring-2
+    (2, 1, 2, "ucp", "imagecp_ring"),
+    (2, 1, 2, "ucp", "imagecp_agkv"),
 ])
 def test_context_parallel_layouts(nproc, cfg, up, backend, mode):
     _run(nproc, cfg, up, backend, mode)
