@@ -33,6 +33,7 @@ EXPORTS = (
     "chitu_b200_qk_norm_rope_batch",
     "chitu_b200_layernorm_modulate",
     "chitu_b200_gate_residual",
+    "chitu_b200_cfg_combine",
     "chitu_b200_peer_copy_2d",
     "chitu_b200_scatter_rows",
     "chitu_b200_attn_q8_workspace_bytes",
@@ -136,6 +137,9 @@ def load() -> ctypes.CDLL:
     lib.chitu_b200_gate_residual.restype = ctypes.c_int
     lib.chitu_b200_gate_residual.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                              _vp, ctypes.c_int64, _vp]
+    lib.chitu_b200_cfg_combine.restype = ctypes.c_int
+    lib.chitu_b200_cfg_combine.argtypes = [_vp, _vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_float,
+                                           ctypes.c_int, _vp]
     lib.chitu_b200_peer_copy_2d.restype = ctypes.c_int
     lib.chitu_b200_peer_copy_2d.argtypes = [_vp, ctypes.c_int64, _vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _vp]
     lib.chitu_b200_scatter_rows.restype = ctypes.c_int

@@ -613,6 +613,27 @@ int chitu_b200_gate_residual(float* x, const void* y, int y_dtype, int64_t rows,
   return CHITU_OK;
 }
 
+int chitu_b200_cfg_combine(const void* cond, const void* uncond, void* out, int dtype, int64_t rows, int C, float scale,
+                           int rescale, void* stream) {
+  if (!cond || !uncond || !out) return fail(CHITU_E_INVALID, "cfg_combine: null pointer");
+  if (rows <= 0 || C <= 0) return fail(CHITU_E_INVALID, "cfg_combine: rows and C must be positive");
+  if (dtype < 0 || dtype > 2) return fail(CHITU_E_UNSUPPORTED, "cfg_combine: dtype must be bf16, fp16 or fp32");
+  chitu::CfgCombineParams p;
+  p.cond = cond;
+  p.uncond = uncond;
+  p.out = out;
+  p.rows = rows;
+  p.C = C;
+  p.dtype = dtype;
+  p.rescale = rescale;
+  p.scale = scale;
+  const int grid = grid_for(rows, 8, 148 * 8);
+  chitu::cfg_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "cfg_combine: launch");
+  return CHITU_OK;
+}
+
 int chitu_b200_scatter_rows(const void* src, void* const* dst_ptrs, int n_dest, int64_t B, int64_t rows,
                             int64_t row_bytes, int64_t dst_batch_stride_bytes, int64_t dst_row_stride_bytes,
                             void* stream) {

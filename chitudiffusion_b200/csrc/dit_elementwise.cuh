@@ -142,4 +142,64 @@ gate_residual_kernel(const GateResidualParams p) {
   }
 }
 
+// ----------------------------------------------------------------------------
+// Classifier-free guidance: out = uncond + scale * (cond - uncond), optionally rescaled row by row to
+// the norm of the conditional prediction (out *= ||cond|| / ||out|| over the last dim).  One warp per
+// row, three passes over registers-sized chunks are avoided by keeping the row sums in two
+// accumulators and re-reading the (L1 / L2 resident) row for the rescaled store.
+// ----------------------------------------------------------------------------
+struct CfgCombineParams {
+  const void* cond;
+  const void* uncond;
+  void* out;
+  long long rows;
+  int C;
+  int dtype;       // kBF16 / kFP16 / kFP32 of all three tensors
+  int rescale;
+  float scale;
+};
+
+__device__ __forceinline__ float cfg_ld(const void* p, int dtype, size_t i) {
+  if (dtype == 2) return static_cast<const float*>(p)[i];
+  if (dtype == 0) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ void cfg_st(void* p, int dtype, size_t i, float v) {
+  if (dtype == 2) static_cast<float*>(p)[i] = v;
+  else if (dtype == 0) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else static_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+__global__ void __launch_bounds__(256) cfg_combine_kernel(const CfgCombineParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows;
+       row += warps) {
+    const size_t base = static_cast<size_t>(row) * p.C;
+    float factor = 1.f;
+    if (p.rescale) {
+      float nc = 0.f, no = 0.f;
+      for (int c = lane; c < p.C; c += 32) {
+        const float a = cfg_ld(p.cond, p.dtype, base + c), b = cfg_ld(p.uncond, p.dtype, base + c);
+        // the reference forms `combined` in the tensors' dtype before taking its norm
+        float o = b + p.scale * (a - b);
+        if (p.dtype == 0) o = __bfloat162float(__float2bfloat16_rn(o));
+        else if (p.dtype == 1) o = __half2float(__float2half_rn(o));
+        nc = fmaf(a, a, nc);
+        no = fmaf(o, o, no);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        nc += __shfl_xor_sync(0xffffffffu, nc, o);
+        no += __shfl_xor_sync(0xffffffffu, no, o);
+      }
+      factor = sqrtf(nc) / sqrtf(no);
+    }
+    for (int c = lane; c < p.C; c += 32) {
+      const float a = cfg_ld(p.cond, p.dtype, base + c), b = cfg_ld(p.uncond, p.dtype, base + c);
+      cfg_st(p.out, p.dtype, base + c, (b + p.scale * (a - b)) * factor);
+    }
+  }
+}
+
 }  // namespace chitu

@@ -427,6 +427,22 @@ def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor]
     return x
 
 
+def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, scale: float, rescale: bool = False) -> torch.Tensor:
+    """``uncond + scale * (cond - uncond)``, with ``rescale`` multiplied row-wise by ``||cond|| / ||result||`` over the last dim."""
+    _require_cuda(cond, uncond)
+    if cond.shape != uncond.shape or cond.dtype != uncond.dtype or cond.dtype not in _DTYPES:
+        raise ValueError("cfg_combine: cond and uncond must share shape and dtype (bf16, fp16 or fp32)")
+    cond, uncond = cond.contiguous(), uncond.contiguous()
+    out = torch.empty_like(cond)
+    C = cond.shape[-1]
+    lib = _lib.load()
+    with torch.cuda.device(cond.device):
+        rc = lib.chitu_b200_cfg_combine(cond.data_ptr(), uncond.data_ptr(), out.data_ptr(), _DTYPES[cond.dtype],
+                                        cond.numel() // C, C, float(scale), int(rescale), _stream_ptr(cond.device))
+    _lib.check(rc, "cfg_combine")
+    return out
+
+
 def peer_copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width: int, rows: int,
                  device: torch.device) -> None:
     """``rows`` pieces of ``width`` bytes between device buffers (either may be peer-mapped), on the copy engines."""

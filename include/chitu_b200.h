@@ -227,6 +227,17 @@ int chitu_b200_gate_residual(float* x, const void* y, int y_dtype, int64_t rows,
                              const float* gate, int64_t gate_batch_stride, void* stream);
 
 /*
+ * Classifier-free-guidance combine of the two branch predictions after the CFG-parallel all-gather
+ * (CfgDispatcher.all_gather_cfg_noise_preds, chitu_diffusion/runtime/generator.py:134-149):
+ *   out = uncond + scale * (cond - uncond)                        (runtime/adapter/wan.py:224-228)
+ * and, with rescale != 0, the norm-preserving form of the Qwen-Image adapter
+ *   out *= ||cond|| / ||out|| over the last dim                   (runtime/adapter/qwen_image.py:678-681).
+ * cond, uncond, out are contiguous [rows, C] of one dtype (out may alias either input).
+ */
+int chitu_b200_cfg_combine(const void* cond, const void* uncond, void* out, int dtype, int64_t rows, int C, float scale,
+                           int rescale, void* stream);
+
+/*
  * Ring and all-gather-KV exchange over peer-mapped memory: every rank publishes its K/V block in a
  * buffer mapped into its peers, and a reader pulls the block it needs for the next ring step into
  * local memory with the copy engines while the attention kernel works on the current block.  Replaces

@@ -110,6 +110,31 @@ def main():
         ok = (err_t < 2e-6 and err_i < 2e-6 and torch.equal(packed[0], t_out) and torch.equal(packed[1], i_out)
               and core.stats()["calls"] == 2)
         print(f"rank {rank} {mode} err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
+    elif mode == "dispatch":
+        from chitudiffusion_b200.dispatch import CfgDispatcher, ContextParallelDispatcher, SequencePadder
+
+        disp = ContextParallelDispatcher()
+        tokens = torch.randn(2, s * cp_size - 1, 12, generator=gen)  # not divisible: padded tail
+        ref_parts = oracle.split_sequence_padding(tokens, cp_size, 1)
+        local = disp.dispatch(tokens, name="hidden_states")
+        ids = torch.arange(s * cp_size * 3).view(s * cp_size, 3)
+        ok = torch.equal(local, ref_parts[r]) and torch.equal(disp.dispatch_id_sequence(ids, "ids"),
+                                                              ids[r * s:(r + 1) * s])
+        back = disp.gather(local * 2.0, name="hidden_states")
+        ok = ok and torch.equal(back, tokens * 2.0)
+        ok = ok and torch.equal(SequencePadder.remove_sequence_padding_and_concat(ref_parts, 1, "hidden_states"), tokens)
+        if cfg_size == 2:
+            cfg = CfgDispatcher()
+            branch = cfg.group.rank_in_group
+            gen2 = torch.Generator().manual_seed(7 + r)  # both branches of one CP rank share the generator
+            preds = [torch.randn(1, 9, 16, generator=gen2) for _ in range(2)]
+            cond, uncond = cfg.all_gather_cfg_noise_preds(preds[branch])
+            ok = ok and torch.equal(cond, preds[0]) and torch.equal(uncond, preds[1])
+            guided = cfg.guided_noise_pred(preds[branch], 4.0, rescale=True)
+            comb = preds[1] + 4.0 * (preds[0] - preds[1])
+            want = comb * (torch.norm(preds[0], dim=-1, keepdim=True) / torch.norm(comb, dim=-1, keepdim=True))
+            ok = ok and torch.allclose(guided, want, atol=1e-6)
+        print(f"rank {rank} dispatch ok={ok}", flush=True)
     elif mode == "fused":
         S = s * cp_size
         q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))

@@ -33,6 +33,7 @@ def _run(nproc, cfg_size, up, cp_backend, mode):
     (4, 1, 2, "ucp", "imagecp_unified"),   # image-CP core: Ulysses-2 x ring-2
     (2, 1, 2, "ucp", "imagecp_ring"),
     (2, 1, 2, "ucp", "imagecp_agkv"),
+    (4, 2, 2, "ucp", "dispatch"),   # token dispatch / gather with a padded tail; CFG-parallel exchange + combine
 ])
 def test_context_parallel_layouts(nproc, cfg, up, backend, mode):
     _run(nproc, cfg, up, backend, mode)

@@ -112,3 +112,18 @@ def test_wan_block_against_oracle(cuda):
     out = blk(x.to(cuda), e.to(cuda), grid, ctx.to(cuda), B200AttnBackend("b200"))
     err, cos = _close(out, ref)
     assert err <= 3e-2 and cos >= 0.999, (err, cos)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rescale", [False, True])
+def test_cfg_combine(cuda, dtype, rescale):
+    from chitudiffusion_b200 import ops
+
+    gen = torch.Generator().manual_seed(3)
+    cond = torch.randn(2, 777, 64, generator=gen).to(dtype)
+    uncond = torch.randn(2, 777, 64, generator=gen).to(dtype)
+    out = ops.cfg_combine(cond.to(cuda), uncond.to(cuda), 4.0, rescale)
+    comb = uncond + 4.0 * (cond - uncond)
+    ref = comb * (torch.norm(cond, dim=-1, keepdim=True) / torch.norm(comb, dim=-1, keepdim=True)) if rescale else comb
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert out.dtype == dtype and torch.allclose(out.float().cpu(), ref.float(), atol=tol, rtol=tol)
