@@ -131,11 +131,11 @@ def load() -> ctypes.CDLL:
         _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp,
     ]
     lib.chitu_b200_layernorm_modulate.restype = ctypes.c_int
-    lib.chitu_b200_layernorm_modulate.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+    lib.chitu_b200_layernorm_modulate.argtypes = [_vp, ctypes.c_int, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                                   _vp, ctypes.c_int64, _vp, ctypes.c_int64, ctypes.c_int,
                                                   ctypes.c_float, _vp]
     lib.chitu_b200_gate_residual.restype = ctypes.c_int
-    lib.chitu_b200_gate_residual.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+    lib.chitu_b200_gate_residual.argtypes = [_vp, ctypes.c_int, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                              _vp, ctypes.c_int64, _vp]
     lib.chitu_b200_cfg_combine.restype = ctypes.c_int
     lib.chitu_b200_cfg_combine.argtypes = [_vp, _vp, _vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.c_float,

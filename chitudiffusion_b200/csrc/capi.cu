@@ -553,7 +553,7 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
   return CHITU_OK;
 }
 
-int chitu_b200_layernorm_modulate(const float* x, void* out, int out_dtype, int64_t rows, int64_t rows_per_batch, int C,
+int chitu_b200_layernorm_modulate(const void* x, int x_dtype, void* out, int out_dtype, int64_t rows, int64_t rows_per_batch, int C,
                                   const float* mul, int64_t mul_batch_stride, const float* add,
                                   int64_t add_batch_stride, int add_one, float eps, void* stream) {
   if (!x || !out) return fail(CHITU_E_INVALID, "layernorm_modulate: null pointer");
@@ -562,12 +562,14 @@ int chitu_b200_layernorm_modulate(const float* x, void* out, int out_dtype, int6
                 chitu::kLnThreads * chitu::kLnMaxVec * 4);
   if (out_dtype != CHITU_DTYPE_BF16 && out_dtype != CHITU_DTYPE_FP16)
     return fail(CHITU_E_UNSUPPORTED, "layernorm_modulate: out_dtype must be bf16 or fp16");
+  if (x_dtype < 0 || x_dtype > 2) return fail(CHITU_E_UNSUPPORTED, "layernorm_modulate: x_dtype must be bf16, fp16 or fp32");
   if ((mul_batch_stride & 3) || (add_batch_stride & 3) ||
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(mul) | reinterpret_cast<uintptr_t>(add)) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 7))
     return fail(CHITU_E_INVALID, "layernorm_modulate: x, mul, add must be 16-byte aligned, out 8-byte aligned");
   chitu::LayerNormParams p;
   p.x = x;
+  p.x_dtype = x_dtype;
   p.out = out;
   p.mul = mul;
   p.add = add;
@@ -586,18 +588,20 @@ int chitu_b200_layernorm_modulate(const float* x, void* out, int out_dtype, int6
   return CHITU_OK;
 }
 
-int chitu_b200_gate_residual(float* x, const void* y, int y_dtype, int64_t rows, int64_t rows_per_batch, int C,
+int chitu_b200_gate_residual(void* x, int x_dtype, const void* y, int y_dtype, int64_t rows, int64_t rows_per_batch, int C,
                              const float* gate, int64_t gate_batch_stride, void* stream) {
   if (!x || !y) return fail(CHITU_E_INVALID, "gate_residual: null pointer");
   if (rows <= 0 || rows_per_batch <= 0 || C <= 0 || (C & 3))
     return fail(CHITU_E_INVALID, "gate_residual: rows must be positive and C a multiple of 4");
   if (y_dtype != CHITU_DTYPE_BF16 && y_dtype != CHITU_DTYPE_FP16)
     return fail(CHITU_E_UNSUPPORTED, "gate_residual: y must be bf16 or fp16");
+  if (x_dtype < 0 || x_dtype > 2) return fail(CHITU_E_UNSUPPORTED, "gate_residual: x_dtype must be bf16, fp16 or fp32");
   if ((gate_batch_stride & 3) || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate)) & 15) ||
       (reinterpret_cast<uintptr_t>(y) & 7))
     return fail(CHITU_E_INVALID, "gate_residual: x and gate must be 16-byte aligned, y 8-byte aligned");
   chitu::GateResidualParams p;
   p.x = x;
+  p.x_dtype = x_dtype;
   p.y = y;
   p.gate = gate;
   p.gate_batch_stride = gate_batch_stride;

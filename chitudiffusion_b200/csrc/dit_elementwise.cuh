@@ -2,11 +2,12 @@
 //
 //   layernorm_affine_kernel   out = LayerNorm(x) * mul + add   -> 16 bit
 //       the modulated input of the self-attention and of the FFN, LayerNorm(x) * (1 + scale) + shift,
-//       and the affine LayerNorm in front of the cross-attention: one pass over the fp32 residual
+//       and the affine LayerNorm in front of the cross-attention: one pass over the residual
 //       stream instead of the reference's LayerNorm + float() + multiply + add kernels
-//   gate_residual_kernel      x += y * gate                    (fp32 residual stream, 16-bit branch output)
+//   gate_residual_kernel      x += y * gate                    (residual stream in place, 16-bit branch output)
 //
-// Algorithmic bytes per element: LayerNorm 4 read + 2 written; gated residual 4 + 2 read, 4 written.
+// The residual stream is fp32 (Wan) or 16-bit (Flux).  Algorithmic bytes per element with an fp32
+// stream: LayerNorm 4 read + 2 written; gated residual 4 + 2 read, 4 written.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -20,7 +21,8 @@ constexpr int kLnThreads = 256;
 constexpr int kLnMaxVec = 8;  // float4 per thread: rows of up to 8192 channels
 
 struct LayerNormParams {
-  const float* x;        // [rows, C] fp32 residual stream
+  const void* x;         // [rows, C] residual stream: fp32, or 16-bit (x_dtype 0 bf16, 1 fp16, 2 fp32)
+  int x_dtype;
   void* out;             // [rows, C] bf16 / fp16
   const float* mul;      // [B or 1, C] fp32, or nullptr (= 1)
   const float* add;      // [B or 1, C] fp32, or nullptr (= 0)
@@ -31,6 +33,38 @@ struct LayerNormParams {
   int out_fp16;
   float eps;
 };
+
+// four consecutive stream elements as floats / back (dtype 0 bf16, 1 fp16, 2 fp32)
+__device__ __forceinline__ float4 stream_ld4(const void* p, int dtype, size_t vec) {
+  if (dtype == 2) return __ldcs(reinterpret_cast<const float4*>(p) + vec);
+  const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p) + vec);
+  float2 a, b;
+  if (dtype == 0) {
+    a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  } else {
+    a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+  }
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void stream_st4(void* p, int dtype, size_t vec, float4 v) {
+  if (dtype == 2) {
+    reinterpret_cast<float4*>(p)[vec] = v;
+    return;
+  }
+  uint2 o;
+  if (dtype == 0) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  } else {
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  }
+  reinterpret_cast<uint2*>(p)[vec] = o;
+}
 
 __device__ __forceinline__ float ln_block_sum(float v, float* red) {
 #pragma unroll
@@ -52,14 +86,14 @@ layernorm_affine_kernel(const LayerNormParams p) {
   __shared__ float red[kLnThreads / 32];
   const int n_vec = p.C >> 2;
   for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    const float4* src = reinterpret_cast<const float4*>(p.x + row * p.C);
+    const size_t row_vec0 = static_cast<size_t>(row) * n_vec;
     float4 v[kLnMaxVec];
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < kLnMaxVec; ++i) {
       const int idx = threadIdx.x + i * kLnThreads;
       if (idx < n_vec) {
-        v[i] = __ldcs(src + idx);  // streamed once
+        v[i] = stream_ld4(p.x, p.x_dtype, row_vec0 + idx);  // streamed once
         sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
       }
     }
@@ -105,7 +139,8 @@ layernorm_affine_kernel(const LayerNormParams p) {
 }
 
 struct GateResidualParams {
-  float* x;              // [rows, C] fp32, updated in place
+  void* x;               // [rows, C] residual stream (x_dtype 0 bf16, 1 fp16, 2 fp32), updated in place
+  int x_dtype;
   const void* y;         // [rows, C] bf16 / fp16 branch output
   const float* gate;     // [B or 1, C] fp32, or nullptr (= 1)
   long long gate_batch_stride;
@@ -122,7 +157,7 @@ gate_residual_kernel(const GateResidualParams p) {
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     const long long row = i / n_vec;
     const int idx = static_cast<int>(i - row * n_vec);
-    float4 xv = reinterpret_cast<float4*>(p.x)[i];
+    float4 xv = stream_ld4(p.x, p.x_dtype, static_cast<size_t>(i));
     const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p.y) + i);
     float2 y0, y1;
     if (p.y_fp16) {
@@ -138,7 +173,7 @@ gate_residual_kernel(const GateResidualParams p) {
     xv.y = fmaf(y0.y, g.y, xv.y);
     xv.z = fmaf(y1.x, g.z, xv.z);
     xv.w = fmaf(y1.y, g.w, xv.w);
-    reinterpret_cast<float4*>(p.x)[i] = xv;
+    stream_st4(p.x, p.x_dtype, static_cast<size_t>(i), xv);
   }
 }
 

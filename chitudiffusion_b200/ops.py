@@ -381,11 +381,11 @@ def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
 
 def layernorm_modulate(x: torch.Tensor, mul: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None,
                        add_one: bool = False, eps: float = 1e-6, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """``LayerNorm(x) * m + a`` for fp32 ``x [B, L, C]``; ``mul`` / ``add`` are ``[C]``, ``[1, C]``-like or ``[B, C]``-like
+    """``LayerNorm(x) * m + a`` for ``x [B, L, C]`` (fp32 or 16-bit); ``mul`` / ``add`` are ``[C]``, ``[1, C]``-like or ``[B, C]``-like
     fp32 (``m = 1 + mul`` with ``add_one``); see ``chitu_b200_layernorm_modulate``."""
     _require_cuda(x)
-    if x.dtype != torch.float32 or x.dim() != 3 or not x.is_contiguous():
-        raise ValueError("layernorm_modulate: x must be a contiguous fp32 [B, L, C] tensor")
+    if x.dtype not in _DTYPES or x.dim() != 3 or not x.is_contiguous():
+        raise ValueError("layernorm_modulate: x must be a contiguous [B, L, C] tensor (fp32, bf16 or fp16)")
     B, L, C = x.shape
 
     def vec(t):
@@ -401,17 +401,18 @@ def layernorm_modulate(x: torch.Tensor, mul: Optional[torch.Tensor] = None, add:
     lib = _lib.load()
     with torch.cuda.device(x.device):
         rc = lib.chitu_b200_layernorm_modulate(
-            x.data_ptr(), out.data_ptr(), _DTYPES[out_dtype], B * L, L, C, m.data_ptr() if m is not None else None, ms,
+            x.data_ptr(), _DTYPES[x.dtype], out.data_ptr(), _DTYPES[out_dtype], B * L, L, C,
+            m.data_ptr() if m is not None else None, ms,
             a.data_ptr() if a is not None else None, as_, int(add_one), float(eps), _stream_ptr(x.device))
     _lib.check(rc, "layernorm_modulate")
     return out
 
 
 def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """In place ``x += y * gate`` (``x`` fp32 ``[B, L, C]``, ``y`` 16-bit, ``gate`` fp32 per batch and channel or None)."""
+    """In place ``x += y * gate`` (``x [B, L, C]`` fp32 or 16-bit, ``y`` 16-bit, ``gate`` fp32 per batch and channel or None)."""
     _require_cuda(x, y)
-    if x.dtype != torch.float32 or x.dim() != 3 or not x.is_contiguous() or y.shape != x.shape or not y.is_contiguous():
-        raise ValueError("gate_residual: x must be contiguous fp32 [B, L, C] and y contiguous of the same shape")
+    if x.dtype not in _DTYPES or x.dim() != 3 or not x.is_contiguous() or y.shape != x.shape or not y.is_contiguous():
+        raise ValueError("gate_residual: x must be contiguous [B, L, C] and y contiguous of the same shape")
     B, L, C = x.shape
     g, gs = None, 0
     if gate is not None:
@@ -421,7 +422,7 @@ def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor]
         gs = g.stride(0) if g.shape[0] == B and B > 1 else 0
     lib = _lib.load()
     with torch.cuda.device(x.device):
-        rc = lib.chitu_b200_gate_residual(x.data_ptr(), y.data_ptr(), _DTYPES[y.dtype], B * L, L, C,
+        rc = lib.chitu_b200_gate_residual(x.data_ptr(), _DTYPES[x.dtype], y.data_ptr(), _DTYPES[y.dtype], B * L, L, C,
                                           g.data_ptr() if g is not None else None, gs, _stream_ptr(x.device))
     _lib.check(rc, "gate_residual")
     return x

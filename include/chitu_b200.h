@@ -212,18 +212,19 @@ int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, 
  * Elementwise tails of the DiT block around the attention path (WanAttentionBlock.forward,
  * chitu_diffusion/models/model_wan.py:321-366).
  *
- * chitu_b200_layernorm_modulate: out[r, :] = LayerNorm(x[r, :]) * m + a in one pass over the fp32
- *   residual stream x [rows, C], 16-bit out; m = mul[b] (or 1 + mul[b] when add_one) and a = add[b] with
+ * chitu_b200_layernorm_modulate: out[r, :] = LayerNorm(x[r, :]) * m + a in one pass over the residual
+ *   stream x [rows, C] (x_dtype: fp32 as in the Wan block, or 16-bit as in the Flux blocks,
+ *   chitu_diffusion/models/model_flux1.py:90-236), statistics in fp32, 16-bit out; m = mul[b] (or 1 + mul[b] when add_one) and a = add[b] with
  *   b = r / rows_per_batch; a batch stride of 0 shares one vector among batches; null mul / add mean 1 / 0.
  *   With add_one it is `norm1(x).float() * (1 + e[1]) + e[0]` (:344-345, :353) including the cast the
  *   following Linear applies; without, the affine WanLayerNorm norm3 (:68-78, :303-305, :352).
- * chitu_b200_gate_residual: x[r, :] += y[r, :] * gate[b] in place (x fp32, y 16-bit; null gate = 1):
+ * chitu_b200_gate_residual: x[r, :] += y[r, :] * gate[b] in place (x of x_dtype, y 16-bit; null gate = 1):
  *   `x = x + y * e[2]` (:347-348, :354-355) and the ungated cross-attention residual (:352).
  */
-int chitu_b200_layernorm_modulate(const float* x, void* out, int out_dtype, int64_t rows, int64_t rows_per_batch, int C,
+int chitu_b200_layernorm_modulate(const void* x, int x_dtype, void* out, int out_dtype, int64_t rows, int64_t rows_per_batch, int C,
                                   const float* mul, int64_t mul_batch_stride, const float* add,
                                   int64_t add_batch_stride, int add_one, float eps, void* stream);
-int chitu_b200_gate_residual(float* x, const void* y, int y_dtype, int64_t rows, int64_t rows_per_batch, int C,
+int chitu_b200_gate_residual(void* x, int x_dtype, const void* y, int y_dtype, int64_t rows, int64_t rows_per_batch, int C,
                              const float* gate, int64_t gate_batch_stride, void* stream);
 
 /*

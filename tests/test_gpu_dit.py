@@ -127,3 +127,85 @@ def test_cfg_combine(cuda, dtype, rescale):
     ref = comb * (torch.norm(cond, dim=-1, keepdim=True) / torch.norm(comb, dim=-1, keepdim=True)) if rescale else comb
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
     assert out.dtype == dtype and torch.allclose(out.float().cpu(), ref.float(), atol=tol, rtol=tol)
+
+
+def _flux_inputs(dim, n_txt, side, heads):
+    from chitudiffusion_b200 import pre_attention
+
+    gen = torch.Generator().manual_seed(21)
+    n_img = side * side
+    img = torch.randn(2, n_img, dim, generator=gen).to(torch.bfloat16)
+    txt = torch.randn(2, n_txt, dim, generator=gen).to(torch.bfloat16)
+    temb = torch.randn(2, dim, generator=gen).to(torch.bfloat16)
+    ids = torch.zeros(n_txt + n_img, 3)
+    ids[n_txt:, 1] = torch.arange(side).repeat_interleave(side)
+    ids[n_txt:, 2] = torch.arange(side).repeat(side)
+    cos, sin = oracle.axis_rope_table(ids, (16, 56, 56))
+    table = pre_attention.axis_rope_table(ids, (16, 56, 56))
+    return img, txt, temb, cos, sin, table
+
+
+def _randomise(blk, seed):
+    """Non-trivial biases and norm weights (random_init leaves them at 0 / 1)."""
+    gen = torch.Generator().manual_seed(seed)
+    for name, t in blk.w.items():
+        if name.endswith(".bias"):
+            t.copy_((0.05 * torch.randn(t.shape, generator=gen)).to(t.dtype))
+        elif "norm_" in name:
+            t.copy_(1.0 + 0.1 * torch.randn(t.shape, generator=gen))
+
+
+def test_flux_double_block_against_oracle(cuda):
+    from chitudiffusion_b200 import B200AttnBackend
+    from chitudiffusion_b200.flux_dit import FluxDoubleBlock
+
+    dim, heads = 256, 2
+    img, txt, temb, cos, sin, table = _flux_inputs(dim, 24, 12, heads)
+    blk = FluxDoubleBlock.random_init(dim, heads, cuda, seed=9, std=0.05)
+    _randomise(blk, 4)
+    w = {k: v.float().cpu() for k, v in blk.w.items()}
+    C = dim
+    p = {}
+    for s, mod, qkv, nq, nk, out, ff in (
+            ("img", "norm1", ("attn.to_q", "attn.to_k", "attn.to_v"), "attn.norm_q", "attn.norm_k", "attn.to_out.0", "ff"),
+            ("txt", "norm1_context", ("attn.add_q_proj", "attn.add_k_proj", "attn.add_v_proj"), "attn.norm_added_q",
+             "attn.norm_added_k", "attn.to_add_out", "ff_context")):
+        p[mod + ".linear.weight"], p[mod + ".linear.bias"] = w[f"{s}.mod.weight"], w[f"{s}.mod.bias"]
+        for i, n in enumerate(qkv):
+            p[n + ".weight"], p[n + ".bias"] = w[f"{s}.qkv.weight"][i * C:(i + 1) * C], w[f"{s}.qkv.bias"][i * C:(i + 1) * C]
+        p[nq + ".weight"], p[nk + ".weight"] = w[f"{s}.norm_q"], w[f"{s}.norm_k"]
+        p[out + ".weight"], p[out + ".bias"] = w[f"{s}.out.weight"], w[f"{s}.out.bias"]
+        p[ff + ".net.0.proj.weight"], p[ff + ".net.0.proj.bias"] = w[f"{s}.ff1.weight"], w[f"{s}.ff1.bias"]
+        p[ff + ".net.2.weight"], p[ff + ".net.2.bias"] = w[f"{s}.ff2.weight"], w[f"{s}.ff2.bias"]
+    ref_txt, ref_img = oracle.flux_double_block(img.float(), txt.float(), temb.float(), p, heads, cos, sin)
+    # the from_reference_params route must rebuild the same block
+    blk2 = FluxDoubleBlock.from_reference_params(p, heads, cuda)
+    for b in (blk, blk2):
+        o_txt, o_img = b(img.to(cuda).clone(), txt.to(cuda).clone(), temb.to(cuda), table.to(cuda), B200AttnBackend("b200"))
+        for out, ref in ((o_txt, ref_txt), (o_img, ref_img)):
+            err, cos_sim = _close(out, ref)
+            assert err <= 3e-2 and cos_sim >= 0.999, (err, cos_sim)
+
+
+def test_flux_single_block_against_oracle(cuda):
+    from chitudiffusion_b200 import B200AttnBackend
+    from chitudiffusion_b200.flux_dit import FluxSingleBlock
+
+    dim, heads = 256, 2
+    img, txt, temb, cos, sin, table = _flux_inputs(dim, 24, 12, heads)
+    x = torch.cat([txt, img], 1)
+    blk = FluxSingleBlock.random_init(dim, heads, cuda, seed=10, std=0.05)
+    _randomise(blk, 5)
+    w = {k: v.float().cpu() for k, v in blk.w.items()}
+    C = dim
+    p = {"norm.linear.weight": w["mod.weight"], "norm.linear.bias": w["mod.bias"], "proj_mlp.weight": w["mlp.weight"],
+         "proj_mlp.bias": w["mlp.bias"], "attn.norm_q.weight": w["norm_q"], "attn.norm_k.weight": w["norm_k"],
+         "proj_out.weight": torch.cat([w["out_attn.weight"], w["out_mlp.weight"]], 1), "proj_out.bias": w["out.bias"]}
+    for i, n in enumerate(("attn.to_q", "attn.to_k", "attn.to_v")):
+        p[n + ".weight"], p[n + ".bias"] = w["qkv.weight"][i * C:(i + 1) * C], w["qkv.bias"][i * C:(i + 1) * C]
+    ref = oracle.flux_single_block(x.float(), temb.float(), p, heads, cos, sin)
+    blk2 = FluxSingleBlock.from_reference_params(p, heads, cuda)
+    for b in (blk, blk2):
+        out = b(x.to(cuda).clone(), temb.to(cuda), table.to(cuda), B200AttnBackend("b200"))
+        err, cos_sim = _close(out, ref)
+        assert err <= 3e-2 and cos_sim >= 0.999, (err, cos_sim)
