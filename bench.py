@@ -359,6 +359,71 @@ def measure_dit(name, rank, world, device, exchange, sync, dist, layers=None, fo
             "weights": "random-init N(0, 0.02^2) bf16, fp32 residual stream; GEMMs are library calls"}
 
 
+def measure_flux_dit(rank, world, device, exchange, sync, dist, steps=3):
+    """Latency of one random-init Flux1-dev transformer pass (19 double + 38 single blocks, 512 text + 4096 image
+    tokens, hidden 3072): one denoising step, text and image tokens sharded over the ranks."""
+    from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
+    from chitudiffusion_b200.context_parallel import B200ContextParallel
+    from chitudiffusion_b200.flux_dit import FluxDiTStack
+
+    w = WORKLOADS["flux1-dev-1024-joint-attn"]
+    H, C, n_txt, n_img = w["H"], w["H"] * w["D"], w["s_txt"], w["s_img"]
+    backend = B200AttnBackend("b200")
+    attn, parallelism = backend, "single"
+    if world > 1:
+        up = max(u for u in (8, 4, 2, 1) if u <= world and H % u == 0 and world % u == 0)
+        comm.destroy_diffusion_parallel_groups()
+        comm.initialize_diffusion_parallel_groups(1, world, up)
+        attn = B200ContextParallel(backend, up, cp_backend="ucp")
+        attn.ulysses_exchange = exchange
+        parallelism = f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else "") + f"-{exchange}"
+    stack = FluxDiTStack(19, 38, C, H, device, seed=4)
+    full = pre_attention.axis_rope_table(joint_ids(w), w["axes"])
+    t_loc, i_loc = n_txt // world, n_img // world
+    table = torch.cat([full[rank * t_loc:(rank + 1) * t_loc],
+                       full[n_txt + rank * i_loc:n_txt + (rank + 1) * i_loc]]).contiguous().to(device)
+    gen = torch.Generator(device=device).manual_seed(9 + rank)
+    img0 = torch.randn(1, i_loc, C, generator=gen, device=device).to(torch.bfloat16)
+    txt0 = torch.randn(1, t_loc, C, generator=gen, device=device).to(torch.bfloat16)
+    temb = torch.randn(1, C, generator=gen, device=device).to(torch.bfloat16)
+    img, txt = img0.clone(), txt0.clone()
+    holder = {}
+
+    def run():
+        holder["out"] = stack(img, txt, temb, table, attn)
+
+    run()
+    fn = run
+    graphed = world > 1 and exchange == "peer"
+    if graphed:
+        sync()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run()
+        fn = graph.replay
+    img.copy_(img0)
+    txt.copy_(txt0)
+    sync()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fn()
+    t1.record()
+    sync()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    step_ms = float(ms.item()) / steps
+    S = n_txt + n_img
+    # per token and block: qkv 3C^2 + out C^2 + MLP 8C^2 (double, per stream) / qkv 3C^2 + mlp 4C^2 + out 5C^2 (single)
+    flops = 57 * (flops_per_block(w) + 2.0 * S * 12 * C * C)
+    return {"workload": "flux1-dev-1024-dit-step", "double_blocks": 19, "single_blocks": 38, "seq_len": S, "hidden": C,
+            "step_ms": round(step_ms, 2), "steps_timed": steps, "tflops": round(flops / (step_ms * 1e-3) / 1e12, 1),
+            "attention_share_of_flops": round(57 * flops_per_block(w) / flops, 3), "parallelism": parallelism,
+            "cuda_graph": graphed, "finite": bool(torch.isfinite(holder["out"].float()).all().item()),
+            "weights": "random-init N(0, 0.02^2) bf16, bf16 residual streams; GEMMs are library calls"}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -464,8 +529,12 @@ def run_ours(args):
 
     dit = None
     if args.dit and not args.profile:
-        dit = [measure_dit(n.strip(), rank, world, device, args.exchange, sync, dist)
-               for n in args.dit.split(",") if n.strip()]
+        dit = []
+        for n in [x.strip() for x in args.dit.split(",") if x.strip()]:
+            if n.startswith("flux"):
+                dit.append(measure_flux_dit(rank, world, device, args.exchange, sync, dist))
+            else:
+                dit.append(measure_dit(n, rank, world, device, args.exchange, sync, dist))
 
     from chitudiffusion_b200 import ops
 
@@ -616,8 +685,9 @@ def main():
                     help="N > 1: context-parallel layout (auto = the widest Ulysses degree the head count allows)")
     ap.add_argument("--extra-layouts", default="",
                     help="N > 1: comma-separated layouts (ring, agkv, usp) to time on the second workload as well")
-    ap.add_argument("--dit", default="wan1.3b-480p-81f",
-                    help="comma-separated Wan workloads whose full DiT forward latency is reported too ('' = none)")
+    ap.add_argument("--dit", default="flux1-dev-1024,wan1.3b-480p-81f",
+                    help="comma-separated workloads (flux1-dev-1024 or a Wan workload) whose full DiT pass latency "
+                         "is reported too ('' = none)")
     ap.add_argument("--no-extra", action="store_true", help="skip the second (Wan2.1-14B 720p) workload")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch kernel by kernel instead of replaying a graph")
     ap.add_argument("--profile", action="store_true",
