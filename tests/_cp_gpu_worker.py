@@ -88,7 +88,7 @@ def main():
     o1 = ring(ql, kg[:, sl].contiguous().to(dev), vg[:, sl].contiguous().to(dev))
     o2 = ring(ql, kl, vl)
     o3 = ring(ql, kl, vl)  # replay
-    assert o1.dtype == torch.bfloat16 and len(ring._graph_cache) == 2
+    assert o1.dtype == torch.bfloat16 and len(ring._graph_cache) == 1  # GQA keys are broadcast before the graph key is formed
     results["graphed_ring"] = max(rel_err(o1, full_gqa[:, sl]), rel_err(o2, full[:, sl]), rel_err(o3, full[:, sl]))
     print(f"rank {rank}: graphed_ring done", flush=True)
     txt = [(torch.randn(1, 24, H, D, generator=gen)).to(torch.bfloat16) for _ in range(3)]
