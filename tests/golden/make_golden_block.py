@@ -1,6 +1,6 @@
 """Generate tests/golden/wan_block_golden.pt by EXECUTING the reference's ``WanAttentionBlock``.
 
-Run in a container that has the reference tree (default /root/reference, or CHITU_REFERENCE_ROOT):
+Run where the reference tree is mounted (CHITU_REFERENCE_ROOT points at it):
 
     python tests/golden/make_golden_block.py
 
