@@ -330,7 +330,7 @@ def measure_dit(name, rank, world, device, exchange, sync, dist, layers=None, fo
     run = lambda: stack(x, e, w["grid"], ctx, attn, backend)  # noqa: E731
     run()
     fn = run
-    graphed = world > 1 and exchange == "peer"
+    graphed = world == 1 or exchange == "peer"  # one GPU, or no NCCL call on the data path: the whole pass replays from a graph
     if graphed:
         sync()
         graph = torch.cuda.CUDAGraph()
@@ -394,7 +394,7 @@ def measure_flux_dit(rank, world, device, exchange, sync, dist, steps=3):
 
     run()
     fn = run
-    graphed = world > 1 and exchange == "peer"
+    graphed = world == 1 or exchange == "peer"  # one GPU, or no NCCL call on the data path: the whole pass replays from a graph
     if graphed:
         sync()
         graph = torch.cuda.CUDAGraph()
