@@ -581,8 +581,22 @@ int chitu_b200_layernorm_modulate(const void* x, int x_dtype, void* out, int out
   p.add_one = add_one;
   p.out_fp16 = out_dtype == CHITU_DTYPE_FP16;
   p.eps = eps;
-  const int grid = static_cast<int>(std::min<int64_t>(rows, 148 * 8));
-  chitu::layernorm_affine_kernel<<<grid, chitu::kLnThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int per_vec = x_dtype == CHITU_DTYPE_FP32 ? 4 : 8;
+  if (C % (32 * per_vec) == 0 && C / per_vec / 32 <= chitu::kLnWarpMaxVec &&
+      !(reinterpret_cast<uintptr_t>(out) & 15)) {
+    // rows of at most 8 KiB: one warp per row, eight rows per CTA
+    const int grid = static_cast<int>(std::min<int64_t>((rows + 7) / 8, 148 * 8));
+    if (x_dtype == CHITU_DTYPE_BF16)
+      chitu::layernorm_affine_warp_kernel<0><<<grid, 256, 0, st>>>(p);
+    else if (x_dtype == CHITU_DTYPE_FP16)
+      chitu::layernorm_affine_warp_kernel<1><<<grid, 256, 0, st>>>(p);
+    else
+      chitu::layernorm_affine_warp_kernel<2><<<grid, 256, 0, st>>>(p);
+  } else {
+    const int grid = static_cast<int>(std::min<int64_t>(rows, 148 * 8));
+    chitu::layernorm_affine_kernel<<<grid, chitu::kLnThreads, 0, st>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "layernorm_modulate: launch");
   return CHITU_OK;

@@ -138,6 +138,113 @@ layernorm_affine_kernel(const LayerNormParams p) {
   }
 }
 
+// Warp-per-row form for rows of at most 8 KiB (Flux: 3072 bf16 channels, Wan-1.3B: 1536 fp32): the row
+// sits in registers as raw 16-byte vectors (up to 16 per lane, all loads in flight at once), the two
+// reductions are warp shuffles, and nothing waits at a block barrier.  Lane l owns vectors l, l + 32, ...
+constexpr int kLnWarpMaxVec = 16;
+
+template <int kXDtype>
+__device__ __forceinline__ void ln_unpack(const uint4 raw, float (&f)[8]) {
+  // 16 bytes of the stream: 8 values when 16-bit, 4 when fp32 (f[4..7] unused)
+  if constexpr (kXDtype == 2) {
+    f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y);
+    f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+    f[4] = f[5] = f[6] = f[7] = 0.f;
+  } else {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (kXDtype == 0) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const float2 h = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = h.x;
+        f[2 * i + 1] = h.y;
+      }
+    }
+  }
+}
+
+template <int kXDtype>
+__global__ void __launch_bounds__(256) layernorm_affine_warp_kernel(const LayerNormParams p) {
+  constexpr int kPer = kXDtype == 2 ? 4 : 8;  // channels per 16-byte vector
+  const int lane = threadIdx.x & 31;
+  const int n_vec = p.C / kPer;               // vectors per row (a multiple of 32: checked by the host)
+  const int per_lane = n_vec >> 5;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const float inv_c = 1.0f / static_cast<float>(p.C);
+  const float one = p.add_one ? 1.f : 0.f;
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < p.rows;
+       row += warps) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.x) + static_cast<size_t>(row) * n_vec;
+    uint4 raw[kLnWarpMaxVec];
+#pragma unroll
+    for (int i = 0; i < kLnWarpMaxVec; ++i)
+      if (i < per_lane) raw[i] = __ldcs(src + lane + i * 32);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnWarpMaxVec; ++i)
+      if (i < per_lane) {
+        float f[8];
+        ln_unpack<kXDtype>(raw[i], f);
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) sum += f[e];
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum * inv_c;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLnWarpMaxVec; ++i)
+      if (i < per_lane) {
+        float f[8];
+        ln_unpack<kXDtype>(raw[i], f);
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) sq = fmaf(f[e] - mean, f[e] - mean, sq);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq * inv_c + p.eps);
+    const long long b = row / p.rows_per_batch;
+    const float* mul = p.mul ? p.mul + b * p.mul_batch_stride : nullptr;
+    const float* add = p.add ? p.add + b * p.add_batch_stride : nullptr;
+    uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<size_t>(row) * p.C;
+#pragma unroll
+    for (int i = 0; i < kLnWarpMaxVec; ++i)
+      if (i < per_lane) {
+        const int c0 = (lane + i * 32) * kPer;
+        float f[8], r[8];
+        ln_unpack<kXDtype>(raw[i], f);
+#pragma unroll
+        for (int q = 0; q < kPer; q += 4) {
+          float4 m = mul ? __ldg(reinterpret_cast<const float4*>(mul + c0 + q)) : make_float4(1.f, 1.f, 1.f, 1.f);
+          const float4 a = add ? __ldg(reinterpret_cast<const float4*>(add + c0 + q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          if (mul) { m.x += one; m.y += one; m.z += one; m.w += one; }
+          r[q] = fmaf((f[q] - mean) * rstd, m.x, a.x);
+          r[q + 1] = fmaf((f[q + 1] - mean) * rstd, m.y, a.y);
+          r[q + 2] = fmaf((f[q + 2] - mean) * rstd, m.z, a.z);
+          r[q + 3] = fmaf((f[q + 3] - mean) * rstd, m.w, a.w);
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < kPer / 2; ++q) {
+          if (p.out_fp16) {
+            const __half2 h = __floats2half2_rn(r[2 * q], r[2 * q + 1]);
+            o[q] = *reinterpret_cast<const uint32_t*>(&h);
+          } else {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * q], r[2 * q + 1]);
+            o[q] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        }
+        if constexpr (kPer == 8)
+          *reinterpret_cast<uint4*>(dst + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+        else
+          *reinterpret_cast<uint2*>(dst + c0) = make_uint2(o[0], o[1]);
+      }
+  }
+}
+
 struct GateResidualParams {
   void* x;               // [rows, C] residual stream (x_dtype 0 bf16, 1 fp16, 2 fp32), updated in place
   int x_dtype;
