@@ -11,9 +11,12 @@ Rank 0 prints one JSON line.
 
 `value`   device-resident throughput: algorithmic attention FLOPs (4*S^2*D*H per block) of all
           ranks / max-over-ranks device time, inputs already in HBM.
-`e2e`     the same step driven from pinned HOST buffers through the public backend API: two
-          input sets copied host->device and the last block's output copied device->host inside
-          the timed region.
+`e2e`     the same step driven from pinned HOST buffers through the public backend API: every step
+          copies its two input sets host->device and its last block's output device->host inside
+          the timed region; uploads of the next step and the read-back of the previous one run on
+          side streams while the current step computes (two device input buffers).
+`dit_step` latency of whole random-init DiT passes around the same attention path (Flux1-dev step,
+          Wan forward): library GEMMs + this package's kernels, replayed from a CUDA graph.
 With --impl reference the CPU restatement of the reference's torch-SDPA path (oracle/) is timed on
 the host cores instead, one block per step.
 """
