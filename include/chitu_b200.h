@@ -153,9 +153,11 @@ int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out
  *   norm_mode    0 = statistics over all H*D channels of a token, 1 = per head over D, 2 = no norm
  *   rope_mode    0 = none,
  *                1 = three-axis grid: token n (global index pos_offset + local index) sits at
- *                    (n / (gh*gw), (n / gw) % gh, n % gw); pair j uses axis 0 for j < D/2 - 2*(D/6... see
- *                    axis_split), rope_table is [max_pos, D/2] float2 (cos, sin) indexed by that axis' position;
- *                    tokens with n >= gf*gh*gw pass through unrotated,
+ *                    (frame, row, column) = (n / (gh*gw), (n / gw) % gh, n % gw); pair j takes its angle from
+ *                    the frame position for j < n_t, from the row position for n_t <= j < n_t + n_h, from the
+ *                    column position otherwise (n_t, n_h: axis_split); rope_table is [max_pos, D/2] float2
+ *                    (cos, sin), row = position along the pair's axis; tokens with n >= gf*gh*gw pass through
+ *                    unrotated; token count and positions must stay below 2^31,
  *                2 = per-token table: rope_table is [S_table, D/2] float2 indexed by pos_offset + local index.
  *   axis_split   {n_t, n_h} pairs for rope_mode 1 (n_w = D/2 - n_t - n_h)
  *   out          16-bit; element (b, s, h, d) is written at
