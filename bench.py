@@ -297,6 +297,54 @@ def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layou
             "input": "one device-generated q/k/v set (2.3 GB, larger than L2)"}
 
 
+def measure_nvlink(rank, world, device, sync, dist, reps=5):
+    """Bytes per second over NVLink of the two exchange primitives at the Wan2.1-14B 720p shard size:
+    the scattering store kernel of the Ulysses exchange (each rank stores (N-1)/N of its q shard into
+    its peers) and the copy-engine pull of the ring / all-gather-KV exchange (one K block from the
+    next rank).  Per GPU and direction; the measured peer-copy reference on this pool is 770 GB/s."""
+    from chitudiffusion_b200 import comm
+    from chitudiffusion_b200.context_parallel import _KernelMerger
+    from chitudiffusion_b200.peer import PeerRing, PeerUlysses
+
+    w = WORKLOADS["wan14b-720p-81f"]
+    H, D = w["H"], w["D"]
+    up = max(u for u in (8, 4, 2, 1) if u <= world and H % u == 0 and world % u == 0)
+    if up != world:
+        return None
+    s_local = seq_len(w) // world
+    comm.destroy_diffusion_parallel_groups()
+    comm.initialize_diffusion_parallel_groups(1, world, up)
+    px = PeerUlysses(comm.get_up_group(up), 1, s_local, H, D, torch.bfloat16, device)
+    x = torch.randn(1, s_local, H * D, device=device).to(torch.bfloat16)
+
+    def timed(fn):
+        fn()
+        px.barrier()
+        sync()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            fn()
+        t1.record()
+        sync()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / reps
+
+    scatter_ms = timed(lambda: px.scatter_plain(x, "q"))
+    sent = x.numel() * 2 * (world - 1) / world
+    ring = PeerRing(comm.get_cp_group(), 1, 1, s_local, H, D, torch.bfloat16, device, mode="ring",
+                    merger_factory=_KernelMerger)
+    dst = torch.empty((1, s_local, H, D), dtype=torch.bfloat16, device=device)
+    owner = (rank + 1) % world
+    pull_ms = timed(lambda: ring._pull(owner, ring.off_k, dst))
+    out = {"shard": f"[1, {s_local}, {H * D}] bf16", "peer_store_scatter_GBps": round(sent / scatter_ms / 1e6, 1),
+           "peer_store_bytes": int(sent), "copy_engine_pull_GBps": round(ring.block_bytes / pull_ms / 1e6, 1),
+           "pull_bytes": int(ring.block_bytes), "reference_peer_copy_GBps": 770.0}
+    comm.destroy_diffusion_parallel_groups()
+    return out
+
+
 def dit_flops_per_layer(w):
     """Multiply-add FLOPs of one Wan block: self-attention, text cross-attention and the nine GEMMs."""
     S, C, T, F = seq_len(w), w["H"] * w["D"], w["text"], w["ffn"]
@@ -577,6 +625,10 @@ def run_ours(args):
                 r = measure_extra("wan14b-720p-81f", 2, rank, world, device, args.exchange, sync, dist, layout=lay)
                 extra["layouts"].append({k: r[k] for k in ("parallelism", "ms_per_layer", "value", "per_gpu_tflops")})
 
+    nvlink = None
+    if world > 1 and args.exchange == "peer" and not args.profile and not args.no_extra:
+        nvlink = measure_nvlink(rank, world, device, sync, dist)
+
     dit = None
     if args.dit and not args.profile:
         dit = []
@@ -639,6 +691,8 @@ def run_ours(args):
         line["also"] = [extra]
     if dit:
         line["dit_step"] = dit
+    if nvlink:
+        line["nvlink"] = nvlink
     if world == 1 and not args.profile:
         line["cpu_baseline"] = cpu_baseline(w, repeats=3)
     if args.profile:
