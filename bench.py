@@ -291,7 +291,26 @@ def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layou
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_layer = float(ms.item()) / (steps * layers)
     tf = flops_per_block(w) / (ms_layer * 1e-3) / 1e12
+    # roofline of a context-parallel layer: the slower of this GPU's share of the FLOPs at the measured
+    # sustained tensor peak and the bytes it must send over NVLink at the measured peer-copy rate
+    peaks, _ = load_peaks()
+    peak_tf = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    compute_ms = flops_per_block(w) / world / (peak_tf * 1e12) * 1e3
+    u, r = pipe.attn._split() if world > 1 else (1, 1)
+    shard_bytes = seq_len(w) // world * w["H"] * w["D"] * 2
+    if world == 1:
+        sent = 0.0
+    elif pipe.parallelism.startswith("agkv"):
+        sent = 2.0 * shard_bytes * (world - 1)  # K and V shards of every other rank
+    else:
+        # Ulysses: q, k, v out and the result back, (u-1)/u of each; ring: K and V blocks of the other groups
+        sent = 4.0 * shard_bytes * (u - 1) / u + 2.0 * shard_bytes * (r - 1)
+    link_ms = sent / 770e9 * 1e3
+    target_ms = max(compute_ms, link_ms)
     return {"workload": name, "seq_len": seq_len(w), "heads": w["H"], "layers_timed": layers, "steps": steps,
+            "roofline": {"compute_ms": round(compute_ms, 3), "nvlink_ms": round(link_ms, 3),
+                         "exchanged_bytes_per_gpu": int(sent), "frac": round(target_ms / ms_layer, 4),
+                         "peaks": f"{peak_tf} TFLOP/s sustained bf16, 770 GB/s peer copy (both measured)"},
             "ms_per_layer": round(ms_layer, 3), "value": round(tf, 1), "unit": "TFLOP/s",
             "per_gpu_tflops": round(tf / world, 1), "parallelism": pipe.parallelism,
             "input": "one device-generated q/k/v set (2.3 GB, larger than L2)"}
