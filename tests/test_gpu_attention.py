@@ -194,3 +194,30 @@ def test_key_split_matches_oracle(backend, Sq, Sk, H, n_splits):
     auto, _ = ops.attn_fwd(q.cuda(), k.cuda(), v.cuda())  # the heuristic picks a split for this small grid
     _check(auto, ref)
     assert ops.auto_key_splits(2, Sq, Sk, H) >= 1 and ops.auto_key_splits(1, 4608, 4608, 24) == 1
+
+
+def test_attention_state_composes(backend):
+    """Key partitions folded into states in two different groupings give the full attention."""
+    from chitudiffusion_b200.state import AttentionState
+
+    gen = torch.Generator().manual_seed(31)
+    q, k, v = (_rand((1, 300, 2, 128), torch.bfloat16, gen) for _ in range(3))
+    ref, ref_lse = oracle.sdpa_fp32(q, k, v, return_lse=True)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    parts = [slice(0, 100), slice(100, 228), slice(228, 300)]
+    blocks = [backend(qc, kc[:, p], vc[:, p], return_attn_probs=True)[:2] for p in parts]
+    chain = AttentionState()
+    assert chain.is_empty()
+    for bo, bl in blocks:
+        chain.update(bo, bl)
+    left, right = AttentionState(), AttentionState()
+    left.update(*blocks[0])
+    right.update(*blocks[1])
+    right.update(*blocks[2])
+    tree = AttentionState.merge(AttentionState.merge(AttentionState(), left), right)
+    for st in (chain, tree):
+        assert st.out.dtype == torch.float32 and tuple(st.lse.shape) == (1, 300, 2, 1)
+        assert (st.out.cpu() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+        assert (st.lse.cpu().squeeze(-1).transpose(1, 2) - ref_lse).abs().max().item() <= 2e-3
+    shifted = chain.corrected(torch.ones_like(chain.out), torch.zeros_like(chain.lse))
+    assert torch.allclose(shifted.out, chain.out + 1.0) and AttentionState().corrected(chain.out, chain.lse).is_empty()
