@@ -42,7 +42,7 @@ class OracleMerger:
 
 
 def main():
-    cfg_size, up, cp_backend, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+    cfg_size, up, cp_backend, modes = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4].split(",")
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     cp_size = world // cfg_size
@@ -50,101 +50,103 @@ def main():
     group = comm.get_cp_group()
     assert group.rank_list == oracle.cp_rank_lists(world, cfg_size)[rank // cp_size if cfg_size == 2 else 0]
     assert comm.get_cfg_group().rank_list in oracle.cfg_rank_lists(world, cfg_size)
-    wrapper = B200ContextParallel(OracleBackend(), up, cp_backend=cp_backend, merger_factory=OracleMerger)
     r = group.rank_in_group
-    # each CP group (cond / uncond under CFG parallelism) works on its own seeded problem
-    gen = torch.Generator().manual_seed(100 + group.rank_list[0])
-    B, H, D = (2 if mode == "batch2" else 1), 8, 16
-    s = 6
-    ok = True
-    if mode in ("plain", "batch2"):
-        S = s * cp_size
-        q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))
-        full = oracle.sdpa_fp32(q, k, v)
-        sl = slice(r * s, (r + 1) * s)
-        out, lse, probs = wrapper(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous())
-        assert lse is None and probs is None
-        err = (out.float() - full[:, sl]).abs().max().item()
-        ok = err < 2e-6 and tuple(out.shape) == (B, s, H, D)
-        # the single-process layout simulator agrees too
-        sim = (oracle.simulate_agcp if cp_backend == "agcp" else
-               (lambda a, b, c: oracle.simulate_ucp(a, b, c, up)))(
-            [q[:, i * s:(i + 1) * s] for i in range(cp_size)], [k[:, i * s:(i + 1) * s] for i in range(cp_size)],
-            [v[:, i * s:(i + 1) * s] for i in range(cp_size)])
-        err2 = (out.float() - sim[r].float()).abs().max().item()
-        ok = ok and err2 < 2e-6
-        print(f"rank {rank} mode {mode} err {err:.2e} sim {err2:.2e}", flush=True)
-    elif mode == "fulltxt":
-        n_img = s * cp_size - 3  # not divisible: zero-padded tail that must never be attended
-        txt_len = 5
-        tq, tk, tv = (torch.randn(1, txt_len, H, D, generator=gen) for _ in range(3))
-        iq, ik, iv = (torch.randn(1, n_img, H, D, generator=gen) for _ in range(3))
-        full = oracle.sdpa_fp32(torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1))
-        shards = [oracle.split_sequence_padding(t, cp_size, 1) for t in (iq, ik, iv)]
-        t_out, i_out = wrapper.cp_attn_with_full_txt(tq, tk, tv, shards[0][r], shards[1][r], shards[2][r],
-                                                     image_seq_len=n_img)
-        ls = shards[0][r].shape[1]  # padded shard length
-        assert tuple(t_out.shape) == (1, txt_len, H, D) and tuple(i_out.shape) == (1, ls, H, D)
-        err_t = (t_out.float() - full[:, :txt_len]).abs().max().item()
-        valid = max(0, min(ls, n_img - r * ls))
-        err_i = (i_out[:, :valid].float() - full[:, txt_len + r * ls: txt_len + r * ls + valid]).abs().max().item()
-        ok = err_t < 2e-6 and err_i < 2e-6
-        print(f"rank {rank} fulltxt err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
-    elif mode.startswith("imagecp_"):
-        from chitudiffusion_b200.image_cp import B200ImageContextParallel
+    all_ok = True
+    for mode in modes:
+        wrapper = B200ContextParallel(OracleBackend(), up, cp_backend=cp_backend, merger_factory=OracleMerger)
+        # each CP group (cond / uncond under CFG parallelism) works on its own seeded problem
+        gen = torch.Generator().manual_seed(100 + group.rank_list[0])
+        B, H, D = (2 if mode == "batch2" else 1), 8, 16
+        s = 6
+        ok = True
+        if mode in ("plain", "batch2"):
+            S = s * cp_size
+            q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))
+            full = oracle.sdpa_fp32(q, k, v)
+            sl = slice(r * s, (r + 1) * s)
+            out, lse, probs = wrapper(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous())
+            assert lse is None and probs is None
+            err = (out.float() - full[:, sl]).abs().max().item()
+            ok = err < 2e-6 and tuple(out.shape) == (B, s, H, D)
+            # the single-process layout simulator agrees too
+            sim = (oracle.simulate_agcp if cp_backend == "agcp" else
+                   (lambda a, b, c: oracle.simulate_ucp(a, b, c, up)))(
+                [q[:, i * s:(i + 1) * s] for i in range(cp_size)], [k[:, i * s:(i + 1) * s] for i in range(cp_size)],
+                [v[:, i * s:(i + 1) * s] for i in range(cp_size)])
+            err2 = (out.float() - sim[r].float()).abs().max().item()
+            ok = ok and err2 < 2e-6
+            print(f"rank {rank} mode {mode} err {err:.2e} sim {err2:.2e}", flush=True)
+        elif mode == "fulltxt":
+            n_img = s * cp_size - 3  # not divisible: zero-padded tail that must never be attended
+            txt_len = 5
+            tq, tk, tv = (torch.randn(1, txt_len, H, D, generator=gen) for _ in range(3))
+            iq, ik, iv = (torch.randn(1, n_img, H, D, generator=gen) for _ in range(3))
+            full = oracle.sdpa_fp32(torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1))
+            shards = [oracle.split_sequence_padding(t, cp_size, 1) for t in (iq, ik, iv)]
+            t_out, i_out = wrapper.cp_attn_with_full_txt(tq, tk, tv, shards[0][r], shards[1][r], shards[2][r],
+                                                         image_seq_len=n_img)
+            ls = shards[0][r].shape[1]  # padded shard length
+            assert tuple(t_out.shape) == (1, txt_len, H, D) and tuple(i_out.shape) == (1, ls, H, D)
+            err_t = (t_out.float() - full[:, :txt_len]).abs().max().item()
+            valid = max(0, min(ls, n_img - r * ls))
+            err_i = (i_out[:, :valid].float() - full[:, txt_len + r * ls: txt_len + r * ls + valid]).abs().max().item()
+            ok = err_t < 2e-6 and err_i < 2e-6
+            print(f"rank {rank} fulltxt err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
+        elif mode.startswith("imagecp_"):
+            from chitudiffusion_b200.image_cp import B200ImageContextParallel
+            txt_len = 5
+            tq, tk, tv = (torch.randn(1, txt_len, H, D, generator=gen) for _ in range(3))
+            iq, ik, iv = (torch.randn(1, s * cp_size, H, D, generator=gen) for _ in range(3))
+            full = oracle.sdpa_fp32(torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1))
+            core = B200ImageContextParallel(wrapper, mode=mode.split("_", 1)[1], ulysses_size=up,
+                                            merger_factory=wrapper._merger_factory)
+            assert core.attn_backend is wrapper.attn and not core.enabled
+            core.enable(wrapper.group)
+            sl = slice(r * s, (r + 1) * s)
+            t_out, i_out = core.attention(tq, tk, tv, iq[:, sl], ik[:, sl], iv[:, sl])
+            packed = core._attention_from_packed(torch.cat([iq[:, sl], tq], 1), torch.cat([ik[:, sl], tk], 1),
+                                                 torch.cat([iv[:, sl], tv], 1), s)
+            err_t = (t_out.float() - full[:, :txt_len]).abs().max().item()
+            err_i = (i_out.float() - full[:, txt_len + r * s: txt_len + (r + 1) * s]).abs().max().item()
+            ok = (err_t < 2e-6 and err_i < 2e-6 and torch.equal(packed[0], t_out) and torch.equal(packed[1], i_out)
+                  and core.stats()["calls"] == 2)
+            print(f"rank {rank} {mode} err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
+        elif mode == "dispatch":
+            from chitudiffusion_b200.dispatch import CfgDispatcher, ContextParallelDispatcher, SequencePadder
+            disp = ContextParallelDispatcher()
+            tokens = torch.randn(2, s * cp_size - 1, 12, generator=gen)  # not divisible: padded tail
+            ref_parts = oracle.split_sequence_padding(tokens, cp_size, 1)
+            local = disp.dispatch(tokens, name="hidden_states")
+            ids = torch.arange(s * cp_size * 3).view(s * cp_size, 3)
+            ok = torch.equal(local, ref_parts[r]) and torch.equal(disp.dispatch_id_sequence(ids, "ids"),
+                                                                  ids[r * s:(r + 1) * s])
+            back = disp.gather(local * 2.0, name="hidden_states")
+            ok = ok and torch.equal(back, tokens * 2.0)
+            ok = ok and torch.equal(SequencePadder.remove_sequence_padding_and_concat(ref_parts, 1, "hidden_states"), tokens)
+            if cfg_size == 2:
+                cfg = CfgDispatcher()
+                branch = cfg.group.rank_in_group
+                gen2 = torch.Generator().manual_seed(7 + r)  # both branches of one CP rank share the generator
+                preds = [torch.randn(1, 9, 16, generator=gen2) for _ in range(2)]
+                cond, uncond = cfg.all_gather_cfg_noise_preds(preds[branch])
+                ok = ok and torch.equal(cond, preds[0]) and torch.equal(uncond, preds[1])
+                guided = cfg.guided_noise_pred(preds[branch], 4.0, rescale=True)
+                comb = preds[1] + 4.0 * (preds[0] - preds[1])
+                want = comb * (torch.norm(preds[0], dim=-1, keepdim=True) / torch.norm(comb, dim=-1, keepdim=True))
+                ok = ok and torch.allclose(guided, want, atol=1e-6)
+            print(f"rank {rank} dispatch ok={ok}", flush=True)
+        elif mode == "fused":
+            S = s * cp_size
+            q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))
+            full = oracle.sdpa_fp32(q, k, v)
+            sl = slice(r * s, (r + 1) * s)
+            out = wrapper.attention_fused(produce_q=lambda: q[:, sl].contiguous(), produce_k=lambda: k[:, sl].contiguous(),
+                                          produce_v=lambda: v[:, sl].contiguous(), num_heads=H)[0]
+            err = (out.float() - full[:, sl]).abs().max().item()
+            ok = err < 2e-6
+        all_ok = all_ok and ok
 
-        txt_len = 5
-        tq, tk, tv = (torch.randn(1, txt_len, H, D, generator=gen) for _ in range(3))
-        iq, ik, iv = (torch.randn(1, s * cp_size, H, D, generator=gen) for _ in range(3))
-        full = oracle.sdpa_fp32(torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1))
-        core = B200ImageContextParallel(wrapper, mode=mode.split("_", 1)[1], ulysses_size=up,
-                                        merger_factory=wrapper._merger_factory)
-        assert core.attn_backend is wrapper.attn and not core.enabled
-        core.enable(wrapper.group)
-        sl = slice(r * s, (r + 1) * s)
-        t_out, i_out = core.attention(tq, tk, tv, iq[:, sl], ik[:, sl], iv[:, sl])
-        packed = core._attention_from_packed(torch.cat([iq[:, sl], tq], 1), torch.cat([ik[:, sl], tk], 1),
-                                             torch.cat([iv[:, sl], tv], 1), s)
-        err_t = (t_out.float() - full[:, :txt_len]).abs().max().item()
-        err_i = (i_out.float() - full[:, txt_len + r * s: txt_len + (r + 1) * s]).abs().max().item()
-        ok = (err_t < 2e-6 and err_i < 2e-6 and torch.equal(packed[0], t_out) and torch.equal(packed[1], i_out)
-              and core.stats()["calls"] == 2)
-        print(f"rank {rank} {mode} err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
-    elif mode == "dispatch":
-        from chitudiffusion_b200.dispatch import CfgDispatcher, ContextParallelDispatcher, SequencePadder
-
-        disp = ContextParallelDispatcher()
-        tokens = torch.randn(2, s * cp_size - 1, 12, generator=gen)  # not divisible: padded tail
-        ref_parts = oracle.split_sequence_padding(tokens, cp_size, 1)
-        local = disp.dispatch(tokens, name="hidden_states")
-        ids = torch.arange(s * cp_size * 3).view(s * cp_size, 3)
-        ok = torch.equal(local, ref_parts[r]) and torch.equal(disp.dispatch_id_sequence(ids, "ids"),
-                                                              ids[r * s:(r + 1) * s])
-        back = disp.gather(local * 2.0, name="hidden_states")
-        ok = ok and torch.equal(back, tokens * 2.0)
-        ok = ok and torch.equal(SequencePadder.remove_sequence_padding_and_concat(ref_parts, 1, "hidden_states"), tokens)
-        if cfg_size == 2:
-            cfg = CfgDispatcher()
-            branch = cfg.group.rank_in_group
-            gen2 = torch.Generator().manual_seed(7 + r)  # both branches of one CP rank share the generator
-            preds = [torch.randn(1, 9, 16, generator=gen2) for _ in range(2)]
-            cond, uncond = cfg.all_gather_cfg_noise_preds(preds[branch])
-            ok = ok and torch.equal(cond, preds[0]) and torch.equal(uncond, preds[1])
-            guided = cfg.guided_noise_pred(preds[branch], 4.0, rescale=True)
-            comb = preds[1] + 4.0 * (preds[0] - preds[1])
-            want = comb * (torch.norm(preds[0], dim=-1, keepdim=True) / torch.norm(comb, dim=-1, keepdim=True))
-            ok = ok and torch.allclose(guided, want, atol=1e-6)
-        print(f"rank {rank} dispatch ok={ok}", flush=True)
-    elif mode == "fused":
-        S = s * cp_size
-        q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))
-        full = oracle.sdpa_fp32(q, k, v)
-        sl = slice(r * s, (r + 1) * s)
-        out = wrapper.attention_fused(produce_q=lambda: q[:, sl].contiguous(), produce_k=lambda: k[:, sl].contiguous(),
-                                      produce_v=lambda: v[:, sl].contiguous(), num_heads=H)[0]
-        err = (out.float() - full[:, sl]).abs().max().item()
-        ok = err < 2e-6
-    flag = torch.tensor([1 if ok else 0])
+    flag = torch.tensor([1 if all_ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()
     sys.exit(0 if flag.item() == 1 else 1)

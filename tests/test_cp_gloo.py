@@ -20,20 +20,16 @@ def _run(nproc, cfg_size, up, cp_backend, mode):
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
 
 
+# one torchrun launch per (ranks, CFG size, Ulysses limit, CP backend); the worker runs the listed modes in turn
 @pytest.mark.parametrize("nproc,cfg,up,backend,mode", [
-    (2, 1, 2, "ucp", "plain"),      # Ulysses-2
-    (2, 1, 1, "ucp", "plain"),      # ring-2
-    (2, 1, 2, "agcp", "plain"),     # all-gather-KV
-    (4, 1, 2, "ucp", "plain"),      # Ulysses-2 x ring-2
-    (4, 1, 2, "ucp", "batch2"),     # batch > 1 takes the unpack-copy path
-    (4, 2, 2, "ucp", "plain"),      # CFG-parallel 2 x Ulysses-2: two independent CP groups
-    (4, 1, 2, "ucp", "fulltxt"),    # Qwen layout, padded tail, Ulysses x ring
-    (2, 1, 2, "agcp", "fulltxt"),
-    (2, 1, 2, "ucp", "fused"),      # producer-callback API (falls back to the serial schedule on CPU)
-    (4, 1, 2, "ucp", "imagecp_unified"),   # image-CP core: Ulysses-2 x ring-2
-    (2, 1, 2, "ucp", "imagecp_ring"),
-    (2, 1, 2, "ucp", "imagecp_agkv"),
-    (4, 2, 2, "ucp", "dispatch"),   # token dispatch / gather with a padded tail; CFG-parallel exchange + combine
+    # Ulysses-2; producer-callback API (serial schedule on CPU); image-CP core in ring and all-gather-KV mode
+    (2, 1, 2, "ucp", "plain,fused,imagecp_ring,imagecp_agkv"),
+    (2, 1, 1, "ucp", "plain"),              # ring-2
+    (2, 1, 2, "agcp", "plain,fulltxt"),     # all-gather-KV, also with the replicated-text layout
+    # Ulysses-2 x ring-2; batch > 1 (unpack-copy path); Qwen layout with a padded tail; image-CP core, unified mode
+    (4, 1, 2, "ucp", "plain,batch2,fulltxt,imagecp_unified"),
+    # CFG-parallel 2 x Ulysses-2: two independent CP groups; token dispatch / gather; CFG exchange + combine
+    (4, 2, 2, "ucp", "plain,dispatch"),
 ])
 def test_context_parallel_layouts(nproc, cfg, up, backend, mode):
     _run(nproc, cfg, up, backend, mode)
