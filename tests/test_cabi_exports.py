@@ -62,3 +62,19 @@ def test_backend_construction_and_cpu_tensors_fail_loudly():
     q = torch.zeros(1, 4, 1, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         backend(q, q, q)
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C11 (no torch types, no C++ in the signatures)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "chitu_b200.h"\nint probe(void) { return (int)chitu_b200_version(); }\n')
+    include = os.path.join(os.path.dirname(__file__), "..", "include")
+    proc = subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-I", include, "-c", str(src), "-o",
+                           str(tmp_path / "use_header.o")], capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr
