@@ -27,6 +27,7 @@ EXPORTS = (
     "chitu_b200_qk_norm_rope_scatter",
     "chitu_b200_attn_fwd_scatter",
     "chitu_b200_peer_barrier",
+    "chitu_b200_set_flag_wait_cycles",
     "chitu_b200_attn_splitkv_workspace_bytes",
     "chitu_b200_attn_fwd_splitkv",
     "chitu_b200_attn_fwd_splitkv_static",
@@ -153,6 +154,8 @@ def load() -> ctypes.CDLL:
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp,
     ]
+    lib.chitu_b200_set_flag_wait_cycles.restype = ctypes.c_longlong
+    lib.chitu_b200_set_flag_wait_cycles.argtypes = [ctypes.c_longlong]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]
     _lib = lib

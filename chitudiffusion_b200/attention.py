@@ -69,4 +69,6 @@ class B200AttnBackend:
             out, lse = ops.attn_fwd_q8(q, k, v, softmax_scale=softmax_scale, return_lse=return_attn_probs)
         else:
             out, lse = ops.attn_fwd(q, k, v, softmax_scale=softmax_scale, return_lse=return_attn_probs)
+        # a bounded device wait that ran out in an earlier call surfaces here as an exception
+        ops.poll_status(q.device)
         return out, lse, None

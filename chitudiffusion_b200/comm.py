@@ -27,14 +27,22 @@ _GROUP_CACHE: Dict[Tuple[Tuple[int, ...], str], object] = {}
 
 
 def _layout_copy(src_view: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
-    """Materialise a permuted view into a contiguous buffer (16-byte vector kernel on CUDA)."""
-    if src_view.is_cuda and src_view.dim() == 5 and src_view.stride(4) == 1 and (
-        src_view.shape[4] * src_view.element_size()
-    ) % 16 == 0 and all((s * src_view.element_size()) % 16 == 0 for s in src_view.stride()[:4]) and (
-        src_view.data_ptr() % 16 == 0 and dst.data_ptr() % 16 == 0
-    ):
+    """Materialise a permuted view into a contiguous buffer.
+
+    CUDA tensors go through the library's 16-byte vector kernel and must satisfy its alignment rules
+    (rows and strides multiples of 16 bytes) - there is no silent second path on the GPU.  Host tensors
+    (the gloo ranks that test the layout logic) are copied by torch.
+    """
+    if src_view.is_cuda:
         from . import ops
 
+        es = src_view.element_size()
+        ok = (src_view.dim() == 5 and src_view.stride(4) == 1 and (src_view.shape[4] * es) % 16 == 0
+              and all((s * es) % 16 == 0 for s in src_view.stride()[:4])
+              and src_view.data_ptr() % 16 == 0 and dst.data_ptr() % 16 == 0)
+        if not ok:
+            raise ValueError("all-to-all layout copy needs 16-byte aligned rows and strides "
+                             f"(shape {tuple(src_view.shape)}, strides {tuple(src_view.stride())}, {src_view.dtype})")
         return ops.strided_copy(src_view, dst)
     dst.copy_(src_view)
     return dst
@@ -231,6 +239,11 @@ def initialize_diffusion_parallel_groups(cfg_size: int, cp_size: int, up: int = 
 def destroy_diffusion_parallel_groups() -> None:
     global _CFG_GROUP, _CP_GROUP, _UP_GROUPS
     _CFG_GROUP = _CP_GROUP = _UP_GROUPS = None
+    for group in _GROUP_CACHE.values():
+        try:
+            dist.destroy_process_group(group)
+        except Exception:  # the default group is already gone at interpreter shutdown
+            pass
     _GROUP_CACHE.clear()
 
 

@@ -130,6 +130,16 @@ class B200ContextParallel:
         deterministic: bool = False,
         return_attn_probs: bool = False,
     ):
+        result = self._call(q, k, v, cu_seqlens_q, cu_seqlens_k, dropout_p, softmax_scale, causal, window_size,
+                            deterministic)
+        if q.is_cuda:
+            from . import ops
+
+            ops.poll_status(q.device)  # a barrier or kernel wait that timed out raises here, one call later at most
+        return result
+
+    def _call(self, q, k, v, cu_seqlens_q, cu_seqlens_k, dropout_p, softmax_scale, causal, window_size,
+              deterministic):
         u, r = self._split()
         if r > 1 and getattr(self.attn, "impl", "") in {"sage", "sparge", "b200_q8"}:
             raise NotImplementedError(

@@ -123,6 +123,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* tail = smem_gen + (kQTiles + kStages) * kTileBytes + (16 + 16 * kStages + 64);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+  const uint32_t bar_drain = smem_u32(tail + 16);  // only used when a wait has run out (see the MMA warp's exit)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -149,6 +150,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_p_full + 16 * t + 8, kTileM);
       mbar_init(bar_o_final + 8 * t, 1);
     }
+    mbar_init(bar_drain, 1);
     mbar_fence_init();
   }
   if (warp == 8) {
@@ -196,7 +198,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (*abort_flag && lane == 0) {
       // A role gave up: make sure no bulk copy of ours is still landing in this
-      // CTA's shared memory before the CTA retires (bounded polls).
+      // CTA's shared memory before the CTA retires (bounded polls): the Q tiles, then the last
+      // copy into every K/V slot.
+      for (int t = 0; t < n_qt; ++t)
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar_q_full + 8 * t, 0); ++spin) {
+        }
       for (int i = max(0, n_items - kStages); i < n_items; ++i) {
         const uint32_t bar = bar_kv_full + 8 * (i % kStages);
         const uint32_t par = (i / kStages) & 1;
@@ -292,6 +298,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(bar_kv_empty + 8 * (ik % kStages));
       }
       __syncwarp();
+    }
+    if (*abort_flag) {
+      // A wait ran out somewhere: MMAs already issued may still be running.  One more commit and a
+      // bounded poll on it, so that nothing writes tensor memory after it has been freed below.
+      if (leader) umma_commit(bar_drain);
+      __syncwarp();
+      for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar_drain, 0); ++spin) {
+      }
     }
   }
   } else {

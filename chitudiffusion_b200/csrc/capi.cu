@@ -86,6 +86,40 @@ int grid_for(long long work_items, int per_block, int max_blocks) {
 
 int elem_size(int dtype) { return dtype == CHITU_DTYPE_FP32 ? 4 : 2; }
 
+// The opt-in to more than 48 KB of dynamic shared memory belongs to the function IN THE CURRENT
+// DEVICE'S CONTEXT, so a process that drives several GPUs has to make it once per device.
+constexpr int kMaxDevices = 64;
+template <typename Kernel>
+cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, bool (&done)[kMaxDevices], std::mutex& mu) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    done[dev] = true;
+  }
+  return cudaSuccess;
+}
+
+// How the key tiles of one attention call are cut into ranges: the requested count is clamped to
+// the number of tiles and then shrunk until no range is empty.
+struct SplitPlan {
+  int n_splits, tiles_per_split;
+};
+SplitPlan plan_key_splits(int Sk, int requested) {
+  const int tiles = (Sk + chitu::kTileN - 1) / chitu::kTileN;
+  int n = requested < tiles ? requested : tiles;
+  if (n < 1) n = 1;
+  const int per = (tiles + n - 1) / n;
+  return SplitPlan{(tiles + per - 1) / per, per};
+}
+
+// Clock budget of the flag waits (peer barrier, arrival flags); about a second by default.
+long long g_flag_wait_cycles = 1ll << 31;
+
 }  // namespace
 
 #ifdef CHITU_ATTN_TIMING
@@ -153,12 +187,9 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     return fail(CHITU_E_INVALID, "attn_fwd: out must be 16-byte aligned");
   if (H > 65535 || B > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: H and B must be below 65536");
 
-  const int n_kv_tiles = (Sk + chitu::kTileN - 1) / chitu::kTileN;
-  int n_splits = ks.n_splits;
-  if (n_splits < 1 || n_splits > 64) return fail(CHITU_E_INVALID, "attn_fwd: n_splits must be in 1..64");
-  if (n_splits > n_kv_tiles) n_splits = n_kv_tiles;
-  int tiles_per_split = (n_kv_tiles + n_splits - 1) / n_splits;
-  n_splits = (n_kv_tiles + tiles_per_split - 1) / tiles_per_split;  // no empty split
+  if (ks.n_splits < 1 || ks.n_splits > 64) return fail(CHITU_E_INVALID, "attn_fwd: n_splits must be in 1..64");
+  const SplitPlan plan = plan_key_splits(Sk, ks.n_splits);
+  const int n_splits = plan.n_splits, tiles_per_split = plan.tiles_per_split;
   if (n_splits > 1) {
     if (!ks.workspace || (reinterpret_cast<uintptr_t>(ks.workspace) & 15))
       return fail(CHITU_E_INVALID, "attn_fwd: split over keys needs a 16-byte aligned workspace");
@@ -198,15 +229,11 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   p.dbg = g_dbg;
 #endif
 
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(chitu::attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    chitu::kAttnSmemBytes);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(chitu::attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      chitu::kAttnSmemBytes);
-  });
+  static bool attr_done[2][kMaxDevices] = {};
+  static std::mutex attr_mu;
+  const cudaError_t attr_err =
+      p.is_fp16 ? ensure_dynamic_smem(chitu::attn_fwd_kernel<true>, chitu::kAttnSmemBytes, attr_done[1], attr_mu)
+                : ensure_dynamic_smem(chitu::attn_fwd_kernel<false>, chitu::kAttnSmemBytes, attr_done[0], attr_mu);
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
 
   dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B * n_splits);
@@ -526,11 +553,17 @@ int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* sta
   p.rank = rank;
   p.world = world;
   p.status = status;
-  p.timeout_cycles = 1ll << 31;  // about a second
+  p.timeout_cycles = g_flag_wait_cycles;
   chitu::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "peer_barrier: launch");
   return CHITU_OK;
+}
+
+long long chitu_b200_set_flag_wait_cycles(long long cycles) {
+  const long long old = g_flag_wait_cycles;
+  if (cycles > 0) g_flag_wait_cycles = cycles;
+  return old;
 }
 
 int chitu_b200_strided_copy(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t n3,
@@ -717,7 +750,6 @@ namespace {
 constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB, resident on every GPU that loads the library
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 void* g_static_scratch_ptr[kMaxDevices] = {};
 std::mutex g_static_scratch_mutex;
 
@@ -749,10 +781,7 @@ extern "C" int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, 
   if (B <= 0 || Sq <= 0 || Sk <= 0 || H <= 0 || D <= 0)
     return fail(CHITU_E_INVALID, "attn_fwd_splitkv_static: B, Sq, Sk, H, D must be positive");
   // the same clamping the general path applies, so the size check below is the real requirement
-  const int tiles = (Sk + chitu::kTileN - 1) / chitu::kTileN;
-  int n = n_splits < tiles ? n_splits : tiles;
-  const int per = (tiles + n - 1) / n;
-  n = (tiles + per - 1) / per;
+  const int n = plan_key_splits(Sk, n_splits).n_splits;
   const int64_t need = splitkv_workspace_bytes(B, Sq, H, D, n);
   if (need > static_cast<int64_t>(kStaticScratchBytes))
     return fail(CHITU_E_INVALID,
@@ -911,15 +940,11 @@ extern "C" int chitu_b200_attn_fwd_q8(const void* q, const void* k, const void* 
 #ifdef CHITU_ATTN_TIMING
   p.dbg = g_dbg;
 #endif
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(chitu::attn_q8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    chitu::kQ8SmemBytes);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(chitu::attn_q8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      chitu::kQ8SmemBytes);
-  });
+  static bool attr_done[2][kMaxDevices] = {};
+  static std::mutex attr_mu;
+  const cudaError_t attr_err =
+      p.is_fp16 ? ensure_dynamic_smem(chitu::attn_q8_kernel<true>, chitu::kQ8SmemBytes, attr_done[1], attr_mu)
+                : ensure_dynamic_smem(chitu::attn_q8_kernel<false>, chitu::kQ8SmemBytes, attr_done[0], attr_mu);
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd_q8: cudaFuncSetAttribute");
   dim3 grid((Sq + 255) / 256, H, B);
   if (p.is_fp16)

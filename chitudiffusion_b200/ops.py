@@ -8,6 +8,7 @@ on a CUDA device - there is no CPU path.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -57,7 +58,52 @@ def check_status(device: Optional[torch.device] = None) -> None:
         raise _lib.ChituB200Error(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
 
 
+_status_mirrors = {}
+
+
+def poll_status(device: Optional[torch.device] = None) -> None:
+    """Deferred, non-blocking form of :func:`check_status` for the product path.
+
+    Each call first looks at the copy of the status word that the PREVIOUS call sent to pinned host
+    memory (if that copy has landed) and raises when it is non-zero, then enqueues a fresh copy behind
+    the work just launched.  A timed-out device wait therefore surfaces as an exception one call later
+    instead of as silently wrong output, and no call ever synchronises.  ``CHITU_B200_CHECK=1`` makes
+    every poll a full synchronising check.  Nothing is enqueued while the stream is being captured.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if torch.cuda.is_current_stream_capturing():
+        return  # event queries and host copies have no place inside a capture
+    if os.environ.get("CHITU_B200_CHECK", "0") == "1":
+        check_status(dev)
+        return
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    mirror = _status_mirrors.get(key)
+    if mirror is None:
+        mirror = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "event": None}
+        _status_mirrors[key] = mirror
+    ev = mirror["event"]
+    if ev is not None and ev.query():
+        code = int(mirror["host"][0])
+        if code != 0:
+            mirror["host"].zero_()
+            mirror["event"] = None
+            status_word(dev).zero_()
+            raise _lib.ChituB200Error(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+    if ev is None or ev.query():
+        mirror["host"].copy_(status_word(dev), non_blocking=True)
+        if ev is None:
+            ev = torch.cuda.Event()
+            mirror["event"] = ev
+        ev.record(torch.cuda.current_stream(dev))
+
+
+def set_flag_wait_cycles(cycles: int) -> int:
+    """Clock budget of the cross-GPU flag waits; returns the previous one (see ``chitu_b200_set_flag_wait_cycles``)."""
+    return int(_lib.load().chitu_b200_set_flag_wait_cycles(int(cycles)))
+
+
 _workspaces = {}
+_retired_workspaces = []
 NUM_SMS = 148
 
 
@@ -70,13 +116,29 @@ def auto_key_splits(B: int, Sq: int, Sk: int, H: int) -> int:
 
 
 def splitkv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Per-device scratch for key-split partials, grown on demand and reused by later calls on the same stream."""
-    key = torch.device(device).index
+    """Scratch for key-split partials, one buffer per (device, stream), grown on demand.
+
+    A buffer that has been handed out may be baked into a captured CUDA graph, so a superseded buffer
+    is never freed: it is parked for the life of the process and the larger replacement serves later
+    calls.  Streams do not share a buffer (two streams of one GPU may run key-split calls at once).
+    Objects that own long-lived graphs (the peer exchanges) allocate their own scratch instead and pass
+    it as ``workspace=``.
+    """
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+           int(torch.cuda.current_stream(dev).cuda_stream))
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
         _workspaces[key] = ws
     return ws
+
+
+def splitkv_workspace_bytes(B: int, Sq: int, H: int, D: int, n_splits: int) -> int:
+    """Bytes of scratch a key-split call of this shape needs (0 for one split)."""
+    return int(_lib.load().chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, int(n_splits)))
 
 
 def attn_fwd(
@@ -87,10 +149,12 @@ def attn_fwd(
     return_lse: bool = False,
     out: Optional[torch.Tensor] = None,
     n_splits: Optional[int] = None,
+    workspace: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """``softmax(scale * q k^T) v`` for ``[B,S,H,128]`` bf16/fp16 tensors of any (16-byte aligned) strides.
 
-    Returns ``(out [B,Sq,H,D] contiguous, lse [B,H,Sq] fp32 | None)``.
+    Returns ``(out [B,Sq,H,D] contiguous, lse [B,H,Sq] fp32 | None)``.  ``workspace`` is an optional
+    caller-owned uint8 scratch for the key-split partials (see :func:`splitkv_workspace`).
     """
     _require_cuda(q, k, v)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
@@ -120,7 +184,9 @@ def attn_fwd(
     with torch.cuda.device(q.device):
         if n_splits > 1:
             need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
-            ws = splitkv_workspace(q.device, need)
+            ws = workspace if workspace is not None else splitkv_workspace(q.device, need)
+            if ws.numel() * ws.element_size() < need or ws.device != q.device:
+                raise ValueError(f"attn_fwd: workspace must hold {need} bytes on {q.device}")
             rc = lib.chitu_b200_attn_fwd_splitkv(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                 lse.data_ptr() if lse is not None else None, B, Sq, Sk, H, D, _lib.i64_array(q.stride()),
@@ -480,6 +546,7 @@ def attn_fwd_scatter(
     dest_head_offset: int,
     softmax_scale: Optional[float] = None,
     n_splits: Optional[int] = None,
+    workspace: Optional[torch.Tensor] = None,
 ) -> None:
     """Attention whose query row ``r`` is stored to ``out_ptrs[r // rows_per_dest]``; see ``chitu_b200_attn_fwd_scatter``."""
     _require_cuda(q, k, v)
@@ -494,7 +561,9 @@ def attn_fwd_scatter(
     ws_ptr, ws_bytes = None, 0
     if n_splits > 1:
         need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
-        ws = splitkv_workspace(q.device, need)
+        ws = workspace if workspace is not None else splitkv_workspace(q.device, need)
+        if ws.numel() * ws.element_size() < need or ws.device != q.device:
+            raise ValueError(f"attn_fwd_scatter: workspace must hold {need} bytes on {q.device}")
         ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         rc = lib.chitu_b200_attn_fwd_scatter(

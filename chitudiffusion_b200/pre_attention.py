@@ -67,7 +67,7 @@ def axis_rope_table(ids: torch.Tensor, axes_dims: Sequence[int], theta: float = 
     return table.to(device) if device is not None else table
 
 
-_TABLE_CACHE: Dict[Tuple[int, str], torch.Tensor] = {}
+_TABLE_CACHE: Dict[tuple, torch.Tensor] = {}
 
 
 def rope_apply(x: torch.Tensor, grid_sizes, freqs: torch.Tensor, cp_size: int = 1, cp_rank: int = 0) -> torch.Tensor:
@@ -81,7 +81,9 @@ def rope_apply(x: torch.Tensor, grid_sizes, freqs: torch.Tensor, cp_size: int = 
     if any(list(g) != list(grids[0]) for g in grids):
         raise NotImplementedError("b200 rope_apply needs one (f, h, w) grid for the whole batch")
     B, s, H, D = x.shape
-    key = (id(freqs), str(x.device))
+    # keyed by the storage the table was built from (address, shape, version), not by id(): ids are
+    # reused once a tensor has been freed
+    key = (freqs.data_ptr(), tuple(freqs.shape), freqs._version, str(freqs.device), str(x.device))
     table = _TABLE_CACHE.get(key)
     if table is None:
         table = table_from_complex(freqs, x.device)

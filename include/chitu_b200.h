@@ -96,7 +96,12 @@ int chitu_b200_attn_fwd_splitkv(const void* q, const void* k, const void* v, voi
  *     in chitu_b200_last_error().  Arguments and results are those of chitu_b200_attn_fwd_splitkv.
  *   - First call on a device: looks up the array's device address (cudaGetSymbolAddress, with the
  *     caller's current device current) and caches it.  Make that first call before starting any
- *     stream capture on that device.
+ *     stream capture on that device.  With CUDA's default lazy module loading this first call is also
+ *     the moment the library's device image - the 32 MiB array included - becomes resident on that
+ *     GPU, so a host that hands all free memory to its own pool must make the first call (or load the
+ *     process with CUDA_MODULE_LOADING=EAGER and touch the library once) BEFORE it commits that pool;
+ *     afterwards nothing more is taken.  cudaDeviceReset() destroys the array and invalidates the
+ *     cached address: a process that resets a device must not call this entry point on it again.
  *   - One array per GPU, shared by every call: it keeps the previous call's partial results and nothing
  *     in it needs clearing, because each call overwrites every row it later reads.  Two calls that run
  *     at the same time on one GPU (different streams, or different threads) race on it; serialise them.
@@ -295,6 +300,16 @@ int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, voi
                                 float softmax_scale, int dtype, int n_splits, void* workspace,
                                 int64_t workspace_bytes, int* status, void* stream);
 int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream);
+
+/*
+ * Clock budget (GPU cycles) of the flag waits in chitu_b200_peer_barrier and in the arrival-flag
+ * polls of the fused exchange; applies to launches made after the call, process-wide.  Returns the
+ * previous budget; a non-positive argument only queries.  The default, 2^31 cycles, is about a second -
+ * the order of the process-group timeouts the reference relies on to notice a lost rank
+ * (chitu_diffusion/core/distributed/comm_group.py:149); tests shorten it so that a wait nobody answers
+ * gives up within milliseconds and reports status 5.
+ */
+long long chitu_b200_set_flag_wait_cycles(long long cycles);
 
 #ifdef __cplusplus
 }

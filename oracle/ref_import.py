@@ -19,11 +19,12 @@ import os
 import sys
 import types
 
-DEFAULT_ROOT = os.environ.get("CHITU_REFERENCE_ROOT", "/root/reference")
+# where the ChituDiffusion tree is mounted: taken from the environment only
+DEFAULT_ROOT = os.environ.get("CHITU_REFERENCE_ROOT", "")
 
 
 def available(root: str = DEFAULT_ROOT) -> bool:
-    return os.path.isdir(os.path.join(root, "chitu_diffusion"))
+    return bool(root) and os.path.isdir(os.path.join(root, "chitu_diffusion"))
 
 
 def _stub(name: str, **attrs) -> types.ModuleType:

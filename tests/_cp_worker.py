@@ -27,7 +27,7 @@ class OracleBackend:
 
     def __call__(self, q, k, v, *_, softmax_scale=None, return_attn_probs=False, **__):
         out, lse = oracle.sdpa_fp32(q, k, v, softmax_scale, return_lse=True)
-        return out, (lse if return_attn_probs else None), None
+        return out.to(q.dtype), (lse if return_attn_probs else None), None
 
 
 class OracleMerger:
@@ -124,7 +124,13 @@ def main():
             ok = ok and torch.equal(back, tokens * 2.0)
             ok = ok and torch.equal(SequencePadder.remove_sequence_padding_and_concat(ref_parts, 1, "hidden_states"), tokens)
             if cfg_size == 2:
-                cfg = CfgDispatcher()
+                def host_combine(cond, uncond, scale, rescale):  # stands in for the CUDA kernel on gloo ranks
+                    out = uncond + scale * (cond - uncond)
+                    if rescale:
+                        out = out * (torch.norm(cond, dim=-1, keepdim=True) / torch.norm(out, dim=-1, keepdim=True))
+                    return out
+
+                cfg = CfgDispatcher(combine=host_combine)
                 branch = cfg.group.rank_in_group
                 gen2 = torch.Generator().manual_seed(7 + r)  # both branches of one CP rank share the generator
                 preds = [torch.randn(1, 9, 16, generator=gen2) for _ in range(2)]
@@ -135,6 +141,34 @@ def main():
                 want = comb * (torch.norm(preds[0], dim=-1, keepdim=True) / torch.norm(comb, dim=-1, keepdim=True))
                 ok = ok and torch.allclose(guided, want, atol=1e-6)
             print(f"rank {rank} dispatch ok={ok}", flush=True)
+        elif mode.startswith("golden:"):
+            # replay of a fixture that the reference's own DiffusionAttention_with_CP produced on gloo ranks
+            # (tests/golden/make_golden_cp.py): same values, same dtype, same shape on every rank
+            case = torch.load(os.path.join(ROOT, "tests", "golden", "cp_layouts_golden.pt"))[mode.split(":", 1)[1]]
+            assert case["ranks"] == world and case["up"] == up and case["cp_backend"] == cp_backend
+            inp, want = case["inputs"], case["per_rank"][r]
+            if case["kind"] == "plain":
+                n = inp["q"].shape[1] // cp_size
+                sl = slice(r * n, (r + 1) * n)
+                got = {"out": wrapper(inp["q"][:, sl].contiguous(), inp["k"][:, sl].contiguous(),
+                                      inp["v"][:, sl].contiguous())[0]}
+            else:
+                sh = [oracle.split_sequence_padding(inp[key], cp_size, 1)[r].contiguous()
+                      for key in ("img_q", "img_k", "img_v")]
+                t_out, i_out = wrapper.cp_attn_with_full_txt(inp["txt_q"], inp["txt_k"], inp["txt_v"], *sh,
+                                                             image_seq_len=inp["img_q"].shape[1])
+                got = {"txt_out": t_out, "img_out": i_out}
+                # rows of the zero-padded tail are computed from padding and carry no meaning: compare valid rows
+                ls = sh[0].shape[1]
+                valid = max(0, min(ls, inp["img_q"].shape[1] - r * ls))
+                got["img_out"], want = got["img_out"][:, :valid], dict(want, img_out=want["img_out"][:, :valid])
+                assert tuple(i_out.shape) == tuple(case["per_rank"][r]["img_out"].shape)
+            for key, ref in want.items():
+                same_meta = got[key].dtype == ref.dtype and tuple(got[key].shape) == tuple(ref.shape)
+                tol = 2e-6 if ref.dtype == torch.float32 else 2 ** -7  # 16-bit: one rounding step of the backend's cast
+                err = (got[key].float() - ref.float()).abs().max().item() if ref.numel() else 0.0
+                ok = ok and same_meta and err <= tol * max(1.0, ref.float().abs().max().item() if ref.numel() else 1.0)
+                print(f"rank {rank} {mode} {key} dtype {got[key].dtype} err {err:.2e} ok={ok}", flush=True)
         elif mode == "fused":
             S = s * cp_size
             q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))

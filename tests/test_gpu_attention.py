@@ -221,3 +221,70 @@ def test_attention_state_composes(backend):
         assert (st.lse.cpu().squeeze(-1).transpose(1, 2) - ref_lse).abs().max().item() <= 2e-3
     shifted = chain.corrected(torch.ones_like(chain.out), torch.zeros_like(chain.lse))
     assert torch.allclose(shifted.out, chain.out + 1.0) and AttentionState().corrected(chain.out, chain.lse).is_empty()
+
+
+@pytest.mark.parametrize("Sq,Sk,H", [(256, 75600, 1), (256, 32760, 2), (4608, 4608, 2)])
+def test_long_key_and_full_size_shapes_against_oracle(backend, Sq, Sk, H):
+    """The Wan 720p / 480p key lengths (591 and 256 key tiles: every ring slot and barrier phase wraps
+    hundreds of times) on a query block, and the full Flux sequence on two of its heads, against the
+    fp32 oracle - output and log-sum-exp."""
+    gen = torch.Generator().manual_seed(Sk + H)
+    q = _rand((1, Sq, H, 128), torch.bfloat16, gen)
+    k = _rand((1, Sk, H, 128), torch.bfloat16, gen)
+    v = _rand((1, Sk, H, 128), torch.bfloat16, gen)
+    ref, ref_lse = oracle.sdpa_fp32(q, k, v, return_lse=True)
+    out, lse, _ = backend(q.cuda(), k.cuda(), v.cuda(), return_attn_probs=True)
+    _check(out, ref, lse, ref_lse)
+    if Sq != Sk:
+        # the same problem without the key split the small grid would pick by itself
+        from chitudiffusion_b200 import ops
+
+        one, lse1 = ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), return_lse=True, n_splits=1)
+        _check(one, ref, lse1, ref_lse)
+
+
+def test_key_split_scratch_survives_regrow_under_a_graph(backend):
+    """A captured graph keeps the address of the key-split scratch it was captured with.  A later,
+    larger eager call makes the shared scratch grow; the superseded buffer must stay alive (and not be
+    handed to anyone else), so replaying the old graph still gives the right answer."""
+    from chitudiffusion_b200 import ops
+
+    gen = torch.Generator().manual_seed(5)
+    q, k, v = (_rand((1, 130, 2, 128), torch.bfloat16, gen) for _ in range(3))
+    ref = oracle.sdpa_fp32(q, k, v)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ops.attn_fwd(qc, kc, vc, n_splits=2)  # warm-up on the capture stream: its scratch exists
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out, _ = ops.attn_fwd(qc, kc, vc, n_splits=2)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    _check(out, ref)
+    with torch.cuda.stream(stream):
+        big = [_rand((2, 700, 4, 128), torch.bfloat16, gen).cuda() for _ in range(3)]
+        ops.attn_fwd(*big, n_splits=8)  # needs far more scratch on the same (device, stream): regrow
+        churn = [torch.full((1 << 20,), 7.0, device="cuda") for _ in range(8)]  # allocator churn over freed blocks
+    torch.cuda.synchronize()
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    _check(out, ref)
+    del churn
+
+
+def test_two_devices_in_one_process(backend):
+    """The opt-in to large dynamic shared memory is per device: a process that drives two GPUs must be
+    able to launch on both."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in one process")
+    gen = torch.Generator().manual_seed(77)
+    q, k, v = (_rand((1, 200, 2, 128), torch.bfloat16, gen) for _ in range(3))
+    ref = oracle.sdpa_fp32(q, k, v)
+    for dev in ("cuda:0", "cuda:1"):
+        out = backend(q.to(dev), k.to(dev), v.to(dev))[0]
+        torch.cuda.synchronize(dev)
+        _check(out, ref)
