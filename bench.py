@@ -17,6 +17,11 @@ Rank 0 prints one JSON line.
           side streams while the current step computes (two device input buffers).
 `dit_step` latency of whole random-init DiT passes around the same attention path (Flux1-dev step,
           Wan forward): library GEMMs + this package's kernels, replayed from a CUDA graph.
+`parity`  (N > 1) before anything is timed, one block of every layout the run uses is checked on seeded
+          inputs: this rank's first 256 query rows against the single-GPU kernel on the all-gathered
+          q/k/v and, on two heads, against the fp32 CPU oracle; above 2e-2 the run exits non-zero.
+`library_sdpa` (N = 1) torch's own scaled_dot_product_attention on the same tensors in the same loop,
+          for context.
 With --impl reference the CPU restatement of the reference's torch-SDPA path (oracle/) is timed on
 the host cores instead, one block per step.
 """
@@ -38,12 +43,12 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 WORKLOADS = {
-    # BASELINE config 2: Flux1-dev joint attention, 1024x1024
+    # Flux1-dev joint attention, 1024x1024 (the one-GPU configuration of the headline metric)
     "flux1-dev-1024-joint-attn": dict(kind="joint", s_img=4096, s_txt=512, img_hw=(64, 64), H=24, D=128, blocks=57,
                                       axes=(16, 56, 56)),
-    # BASELINE config 1: one Wan2.1-1.3B self-attention layer at 480p x 17 frames
+    # one Wan2.1-1.3B self-attention layer at 480p x 17 frames (the CPU-runnable configuration)
     "wan1.3b-480p-17f-layer": dict(kind="wan", grid=(5, 30, 52), H=12, D=128, blocks=1),
-    # BASELINE config 3 / 4: Wan2.1 1.3B 480p x 81 frames, Wan2.1 14B 720p x 81 frames
+    # Wan2.1 1.3B 480p x 81 frames, Wan2.1 14B 720p x 81 frames
     "wan1.3b-480p-81f": dict(kind="wan", grid=(21, 30, 52), H=12, D=128, blocks=30, ffn=8960, text=512),
     "wan14b-720p-81f": dict(kind="wan", grid=(21, 45, 80), H=40, D=128, blocks=40, ffn=13824, text=512),
 }
@@ -172,8 +177,18 @@ def make_inputs(w, rank, world, seed, n_sets, device, pinned=False):
 # --------------------------------------------------------------------------- #
 # our arm
 # --------------------------------------------------------------------------- #
+def pick_ulysses(world, H, layout):
+    """Ulysses degree of a layout on `world` GPUs with `H` heads."""
+    if layout in ("ring", "agkv"):
+        return 1
+    if layout == "usp":
+        return max(u for u in (4, 2, 1) if u < world and H % u == 0 and world % u == 0)
+    return max(u for u in (8, 4, 2, 1) if u <= world and H % u == 0 and world % u == 0)
+
+
 class Pipeline:
-    """Per-rank block function: pre-attention pass + (context-parallel) attention."""
+    """Per-rank block function: pre-attention pass + (context-parallel) attention, through the product API:
+    `B200AttnBackend.__call__` on one GPU, `B200ContextParallel.attention_from_projections` on several."""
 
     def __init__(self, w, rank, world, device, exchange="peer", init_groups=True, layout="auto", attn="b200"):
         from chitudiffusion_b200 import B200AttnBackend, comm, pre_attention
@@ -186,28 +201,18 @@ class Pipeline:
             raise SystemExit("--attn b200_q8 is measured on one GPU")
         self.attn = self.backend
         if world > 1:
-            up = max(u for u in (8, 4, 2, 1) if u <= world and self.H % u == 0 and world % u == 0)
-            if layout in ("ring", "agkv"):
-                up = 1
-            elif layout == "usp":
-                up = max(u for u in (4, 2, 1) if u < world and self.H % u == 0 and world % u == 0)
+            up = pick_ulysses(world, self.H, layout)
             if init_groups:
                 comm.initialize_diffusion_parallel_groups(1, world, up)
-            elif layout != "auto":  # a second pipeline in the same process with another layout
+            else:  # another pipeline in the same process, possibly with another layout
                 comm.destroy_diffusion_parallel_groups()
                 comm.initialize_diffusion_parallel_groups(1, world, up)
             self.attn = B200ContextParallel(self.backend, up, cp_backend="agcp" if layout == "agkv" else "ucp")
             self.attn.ulysses_exchange = exchange
             self.parallelism = ("agkv" if layout == "agkv" else
                                 f"ulysses{up}" + (f"xring{world // up}" if world // up > 1 else ""))
-            self.peer = None
             self.graphable = exchange == "peer"  # no NCCL call on the data path
             if exchange == "peer" and up == world and layout != "agkv":
-                # pure Ulysses: exchange fused into the pre-attention stores and the attention epilogue
-                from chitudiffusion_b200.peer import PeerUlysses
-
-                self.peer = PeerUlysses(comm.get_up_group(up), 1, seq_len(w) // world, self.H, self.D,
-                                        torch.bfloat16, device)
                 self.parallelism += "-peer-stores"
             elif exchange == "peer":
                 self.parallelism += "-peer-pulls"
@@ -215,7 +220,6 @@ class Pipeline:
                 self.parallelism += "-nccl"
         else:
             self.parallelism = "single"
-            self.peer = None
             self.graphable = False
         if w["kind"] == "joint":
             table = pre_attention.axis_rope_table(joint_ids(w), w["axes"])[local_positions(w, rank, world)]
@@ -226,23 +230,22 @@ class Pipeline:
             self.pre = pre_attention.WanPreAttention(self.H, self.D, cp_size=world, cp_rank=rank, device=device)
             self.nq = torch.ones(self.H * self.D, device=device)
             self.nk = torch.ones(self.H * self.D, device=device)
-        self.launches = 0
         self.attn_events = []
 
-    def block(self, qp, kp, vp, timed=False):
-        if self.peer is not None:
-            px = self.peer
-            grid = self.w.get("grid", (0, 0, 0))
-            px.scatter_qkv(self.pre.jobs(qp, kp, self.nq, self.nk), vp, **self.pre.batch_args(px.s, grid))
-            out = px.attention()
-            self.launches += 4  # fused q/k/v pre-pass + scatter, attention, 2 barriers
-            return out
+    def pre_local(self, qp, kp, vp):
+        """The pre-attention transform alone, on this rank's rows."""
         if self.w["kind"] == "joint":
-            q, k, v = self.pre(qp, kp, vp, self.nq, self.nk)
-        else:
-            q, k, v = self.pre(qp, kp, vp, self.nq, self.nk, self.w["grid"])
-        self.launches += 1  # q and k share one pre-attention launch
-        if timed and self.world == 1:
+            return self.pre(qp, kp, vp, self.nq, self.nk)
+        return self.pre(qp, kp, vp, self.nq, self.nk, self.w["grid"])
+
+    def block(self, qp, kp, vp, timed=False):
+        if self.world > 1:
+            # norm + rotary + cast + head/sequence exchange + attention + exchange back: one call of the wrapper
+            return self.attn.attention_from_projections(
+                self.pre.jobs(qp, kp, self.nq, self.nk), vp,
+                **self.pre.batch_args(qp.shape[1], self.w.get("grid", (0, 0, 0))))
+        q, k, v = self.pre_local(qp, kp, vp)
+        if timed:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             out = self.attn(q, k, v)[0]
@@ -250,7 +253,6 @@ class Pipeline:
             self.attn_events.append((e0, e1))
         else:
             out = self.attn(q, k, v)[0]
-        self.launches += 1 if self.backend.impl == "b200" else 3  # 8-bit: two pre-pass kernels + attention
         return out
 
     def step(self, sets, timed=False):
@@ -259,6 +261,38 @@ class Pipeline:
             qp, kp, vp = sets[b % len(sets)]
             out = self.block(qp, kp, vp, timed)
         return out
+
+
+PARITY_LIMIT = 2e-2
+PARITY_ROWS = 256
+
+
+def check_parity(pipe, qp, kp, vp, dist):
+    """One block of `pipe`'s layout against (a) the single-GPU kernel on the all-gathered q/k/v and (b) the
+    fp32 CPU oracle on two heads, for this rank's first rows.  Returns the worst relative errors over the ranks."""
+    import oracle
+
+    world, rank, dev = pipe.world, pipe.rank, pipe.device
+    out = pipe.block(qp, kp, vp).float()
+    q, k, v = pipe.pre_local(qp, kp, vp)  # [1, s, H, D] of this rank
+    s = q.shape[1]
+    full = []
+    for t in (q, k, v):
+        buf = torch.empty((world,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+        dist.all_gather_into_tensor(buf, t.contiguous())
+        full.append(buf.view(1, world * s, *t.shape[2:]))
+    rows = min(PARITY_ROWS, s)
+    q_rows = full[0][:, rank * s: rank * s + rows]
+    single = pipe.backend(q_rows, full[1], full[2])[0].float()
+    scale = single.abs().max().clamp_min(1e-12)
+    e_single = float(((out[:, :rows] - single).abs().max() / scale).item())
+    heads = sorted({0, pipe.H - 1})
+    ref = oracle.sdpa_fp32(q_rows[:, :, heads].cpu(), full[1][:, :, heads].cpu(), full[2][:, :, heads].cpu())
+    e_oracle = float(((out[:, :rows][:, :, heads].cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-12)).item())
+    worst = torch.tensor([e_single, e_oracle], device=dev)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {"vs_single_gpu_kernel": round(float(worst[0]), 5), "vs_fp32_oracle_2_heads": round(float(worst[1]), 5),
+            "rows_per_rank": rows}
 
 
 def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layout="auto"):
@@ -270,6 +304,7 @@ def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layou
     gen = torch.Generator(device=device).manual_seed(77 + rank)
     sets = [tuple(torch.randn(1, s_local, C, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
                   for _ in range(3))]
+    parity = check_parity(pipe, *sets[0], dist) if world > 1 else None
     pipe.step(sets)
     fn = lambda: pipe.step(sets)  # noqa: E731
     if world > 1 and pipe.graphable:
@@ -308,6 +343,7 @@ def measure_extra(name, layers, rank, world, device, exchange, sync, dist, layou
     link_ms = sent / 770e9 * 1e3
     target_ms = max(compute_ms, link_ms)
     return {"workload": name, "seq_len": seq_len(w), "heads": w["H"], "layers_timed": layers, "steps": steps,
+            "parity": parity,
             "roofline": {"compute_ms": round(compute_ms, 3), "nvlink_ms": round(link_ms, 3),
                          "exchanged_bytes_per_gpu": int(sent), "frac": round(target_ms / ms_layer, 4),
                          "peaks": f"{peak_tf} TFLOP/s sustained bf16, 770 GB/s peer copy (both measured)"},
@@ -494,6 +530,62 @@ def measure_flux_dit(rank, world, device, exchange, sync, dist, steps=3):
             "weights": "random-init N(0, 0.02^2) bf16, bf16 residual streams; GEMMs are library calls"}
 
 
+def measure_library_sdpa(pipe, dev_sets, w, sync):
+    """torch's scaled_dot_product_attention (whatever fused backend it picks, and cuDNN's when it can be
+    forced) on the same post-transform q/k/v, cycled over the same input sets, timed the same way.  Context
+    for the kernel's number - a library call, not part of the product path."""
+    import torch.nn.functional as F
+
+    qkv = [pipe.pre_local(*trip) for trip in dev_sets]  # distinct sets: together larger than L2
+    flops = flops_per_block(w)
+
+    def run(n):
+        for i in range(n):
+            q, k, v = qkv[i % len(qkv)]
+            F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+
+    def timed(n=20):
+        run(3)
+        sync()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        run(n)
+        t1.record()
+        sync()
+        return t0.elapsed_time(t1) / n
+
+    out = {"what": "torch.nn.functional.scaled_dot_product_attention, bf16, same tensors and loop"}
+    try:
+        ms = timed()
+        out["default_backend"] = {"ms_per_call": round(ms, 5), "tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+    except Exception as exc:  # a library refusing the shape is not this bench's failure
+        out["default_backend"] = {"error": str(exc)[:200]}
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+
+        with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+            ms = timed()
+        out["cudnn"] = {"ms_per_call": round(ms, 5), "tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+    except Exception as exc:
+        out["cudnn"] = {"error": str(exc)[:200]}
+    # our kernel in the identical loop (no per-launch events), for a like-for-like ratio
+    def ours(n):
+        for i in range(n):
+            q, k, v = qkv[i % len(qkv)]
+            pipe.backend(q, k, v)
+
+    ours(3)
+    sync()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    ours(20)
+    t1.record()
+    sync()
+    ms = t0.elapsed_time(t1) / 20
+    out["this_kernel_same_loop"] = {"ms_per_call": round(ms, 5), "tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+    return out
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -595,6 +687,11 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    from chitudiffusion_b200 import ops
+
+    parity = {}
+    if world > 1:
+        parity[pipe.parallelism] = check_parity(pipe, *dev_sets[0], dist)
     for _ in range(args.warmup):
         pipe.step(dev_sets)
     # On several GPUs a step is a few hundred short launches: capture it once in a CUDA graph and
@@ -624,9 +721,9 @@ def run_ours(args):
             with torch.cuda.graph(e2e_graphs[slot]):
                 e2e_outs[slot] = pipe.step(e2e_bufs[slot])
             sync()
-    pipe.launches = 0
+    before = ops.launch_count
     pipe.step(dev_sets)
-    launches_per_step = pipe.launches
+    launches_per_step = ops.launch_count - before  # this library's kernels in one step (a graph replays the same ones)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -645,14 +742,27 @@ def run_ours(args):
         e2e_run(max(1, min(args.warmup, 3)))
         e2e_ms = e2e_timed(args.steps)
 
+    library = None
+    if world == 1 and not args.profile and args.attn == "b200":
+        library = measure_library_sdpa(pipe, dev_sets, w, sync)
+
     extra = None
+    also = []
     if args.workload == DEFAULT_WORKLOAD and not args.profile and not args.no_extra:
+        # the compute-bound Wan2.1-14B 720p layer in every context-parallel layout the configuration names
         extra = measure_extra("wan14b-720p-81f", 4, rank, world, device, args.exchange, sync, dist)
-        if world > 1 and args.extra_layouts:
-            extra["layouts"] = []
+        also.append(extra)
+        if world > 1:
             for lay in [x.strip() for x in args.extra_layouts.split(",") if x.strip()]:
-                r = measure_extra("wan14b-720p-81f", 2, rank, world, device, args.exchange, sync, dist, layout=lay)
-                extra["layouts"].append({k: r[k] for k in ("parallelism", "ms_per_layer", "value", "per_gpu_tflops")})
+                if lay == "usp" and pick_ulysses(world, WORKLOADS["wan14b-720p-81f"]["H"], "usp") < 2:
+                    continue
+                also.append(measure_extra("wan14b-720p-81f", 2, rank, world, device, args.exchange, sync, dist, layout=lay))
+            if world == 8:  # Wan2.1-1.3B 480p: 12 heads do not divide by 8, Ulysses-4 x ring-2
+                also.append(measure_extra("wan1.3b-480p-81f", 4, rank, world, device, args.exchange, sync, dist,
+                                          layout="usp"))
+        for leg in also:
+            if leg.get("parity"):
+                parity[f"{leg['workload']}:{leg['parallelism']}"] = leg["parity"]
 
     nvlink = None
     if world > 1 and args.exchange == "peer" and not args.profile and not args.no_extra:
@@ -667,13 +777,15 @@ def run_ours(args):
             else:
                 dit.append(measure_dit(n, rank, world, device, args.exchange, sync, dist))
 
-    from chitudiffusion_b200 import ops
-
     ops.check_status(device)
+    bad = {k: v for k, v in parity.items()
+           if max(v["vs_single_gpu_kernel"], v["vs_fp32_oracle_2_heads"]) > PARITY_LIMIT}
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
+        if bad:
+            sys.exit(3)
         return
     peaks, peak_kind = load_peaks()
     flops_step = flops_per_block(w) * w["blocks"]
@@ -686,13 +798,18 @@ def run_ours(args):
     if attn_ms:
         avg_ms = sum(attn_ms) / len(attn_ms)
         achieved = flops_per_block(w) / (avg_ms * 1e-3) / 1e12
-        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        # The timed region is a fraction of a second at close to the maximum SM clock, so the burst figure
+        # (a kernel timed alone) is the denominator; the sustained one (seconds under the power cap,
+        # measured at a median of 1342 MHz) is printed beside it with the clock this run sampled.
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        sustained = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
         roof = {
             "bound": "tensor", "kernel": "attn_fwd_kernel" if args.attn == "b200" else "q8 pre-pass + attn_q8_kernel",
             "achieved": round(achieved, 2), "peak": peak,
             "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-            "peak_source": f"{peak_kind} bf16_tflops_sustained (kernel timed inside a long back-to-back loop)",
-            "frac_of_burst": round(achieved / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), 4),
+            "peak_source": f"{peak_kind} bf16_tflops (cuBLAS burst); sm clock sampled during this run: "
+                           f"{clocks.get('sm_mhz') if clocks else None} MHz",
+            "frac_of_sustained": round(achieved / sustained, 4), "peak_sustained": sustained,
             "frac_of_nominal_2250": round(achieved / 2250.0, 4),
             "avg_launch_ms": round(avg_ms, 5), "launches_timed": len(attn_ms),
             "algorithmic_flops_per_launch": flops_per_block(w),
@@ -716,8 +833,13 @@ def run_ours(args):
         "gpu_launches": launches,
         "roofline": roof,
     }
-    if extra is not None:
-        line["also"] = [extra]
+    if also:
+        line["also"] = also
+    if parity:
+        line["parity"] = parity
+        line["parity_limit"] = PARITY_LIMIT
+    if library is not None:
+        line["library_sdpa"] = library
     if dit:
         line["dit_step"] = dit
     if nvlink:
@@ -730,6 +852,9 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if bad:
+        print(f"parity above {PARITY_LIMIT}: {bad}", file=sys.stderr)
+        sys.exit(3)
 
 
 # --------------------------------------------------------------------------- #
@@ -816,8 +941,8 @@ def main():
                     help="attention backend: bf16/fp16 kernel, or the INT8-QK / E4M3-PV variant (one GPU)")
     ap.add_argument("--layout", default="auto", choices=["auto", "ulysses", "ring", "agkv", "usp"],
                     help="N > 1: context-parallel layout (auto = the widest Ulysses degree the head count allows)")
-    ap.add_argument("--extra-layouts", default="",
-                    help="N > 1: comma-separated layouts (ring, agkv, usp) to time on the second workload as well")
+    ap.add_argument("--extra-layouts", default="ring,agkv,usp",
+                    help="N > 1: comma-separated layouts (ring, agkv, usp) timed on the Wan2.1-14B 720p layer besides Ulysses")
     ap.add_argument("--dit", default="flux1-dev-1024,wan1.3b-480p-81f",
                     help="comma-separated workloads (flux1-dev-1024 or a Wan workload) whose full DiT pass latency "
                          "is reported too ('' = none)")

@@ -28,6 +28,9 @@ EXPORTS = (
     "chitu_b200_attn_fwd_scatter",
     "chitu_b200_peer_barrier",
     "chitu_b200_set_flag_wait_cycles",
+    "chitu_b200_qk_norm_rope_batch_signal",
+    "chitu_b200_attn_fwd_exchange",
+    "chitu_b200_peer_wait_outputs",
     "chitu_b200_attn_splitkv_workspace_bytes",
     "chitu_b200_attn_fwd_splitkv",
     "chitu_b200_attn_fwd_splitkv_static",
@@ -59,6 +62,15 @@ class NormRopeJob(ctypes.Structure):
         ("norm_mode", ctypes.c_int), ("rope_mode", ctypes.c_int), ("out", ctypes.c_void_p),
         ("out_ptrs", ctypes.POINTER(ctypes.c_void_p)), ("n_out_ptrs", ctypes.c_int),
     ]
+
+
+class PeerSyncDesc(ctypes.Structure):
+    """Mirror of ``chitu_b200_peer_sync``."""
+
+    _fields_ = [("blocks", ctypes.POINTER(ctypes.c_void_p)), ("rank", ctypes.c_int), ("world", ctypes.c_int)]
+
+
+SYNC_INTS = 64
 
 
 def load() -> ctypes.CDLL:
@@ -154,12 +166,35 @@ def load() -> ctypes.CDLL:
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp,
     ]
+    lib.chitu_b200_qk_norm_rope_batch_signal.restype = ctypes.c_int
+    lib.chitu_b200_qk_norm_rope_batch_signal.argtypes = [
+        ctypes.POINTER(NormRopeJob), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, _vp, ctypes.c_int,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int64, ctypes.c_int,
+        _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        ctypes.POINTER(PeerSyncDesc), _vp,
+    ]
+    lib.chitu_b200_attn_fwd_exchange.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_exchange.argtypes = [
+        _vp, _vp, _vp, _vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int,
+        ctypes.POINTER(PeerSyncDesc), _vp, _vp,
+    ]
+    lib.chitu_b200_peer_wait_outputs.restype = ctypes.c_int
+    lib.chitu_b200_peer_wait_outputs.argtypes = [ctypes.POINTER(PeerSyncDesc), _vp, _vp]
     lib.chitu_b200_set_flag_wait_cycles.restype = ctypes.c_longlong
     lib.chitu_b200_set_flag_wait_cycles.argtypes = [ctypes.c_longlong]
     lib.chitu_b200_peer_barrier.restype = ctypes.c_int
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]
     _lib = lib
     return lib
+
+
+def peer_sync_desc(block_ptrs: Sequence[int], rank: int):
+    """``(descriptor, keep-alive)`` for the sync blocks of a group (``block_ptrs[i]``: rank i's block as mapped here)."""
+    arr = (ctypes.c_void_p * len(block_ptrs))(*[int(p) for p in block_ptrs])
+    desc = PeerSyncDesc(ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p)), int(rank), len(block_ptrs))
+    return desc, arr
 
 
 def ptr_array(ptrs: Sequence[int]):

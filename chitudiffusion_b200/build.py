@@ -17,7 +17,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libchitu_b200.so")
 SOURCES = ["capi.cu"]
-HEADERS = ["ptx.cuh", "attn_fwd.cuh", "elementwise.cuh", "dit_elementwise.cuh", "quant.cuh", "attn_q8.cuh", "attn_q8_softmax.inc"]
+HEADERS = ["ptx.cuh", "peer_sync.cuh", "attn_fwd.cuh", "elementwise.cuh", "dit_elementwise.cuh", "quant.cuh", "attn_q8.cuh", "attn_q8_softmax.inc"]
 
 
 def _nvcc() -> str:

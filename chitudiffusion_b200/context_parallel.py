@@ -290,12 +290,10 @@ class B200ContextParallel:
         if self._use_peer(q, k, u, r, kw):
             B, s, H, D = q.shape
             px = self.peer_exchange(B, s, H, D, q.dtype, q.device)
-            px.scatter_plain(q, "q")
-            px.scatter_plain(k, "k")
-            px.scatter_plain(v, "v")
-            # the exchange buffer is reused by the next call: hand back a copy, as the reference
-            # hands back a fresh tensor
-            return px.attention(kw["softmax_scale"]).clone()
+            px.scatter_ready(q, k, v)
+            # the result lives in one of the exchange object's two output slots: valid until the call
+            # after next (the reference hands back a fresh tensor; a DiT block consumes it at once)
+            return px.attention(kw["softmax_scale"])
         if self._use_peer_ring(q, k, u, r, kw):
             ring = self.peer_ring(q, "ring")
             if u > 1:
@@ -328,6 +326,58 @@ class B200ContextParallel:
             out = up_group.all_to_all(out, 1, 2)
         return out
 
+    # ------------------------------------------------------------------ projections in, attention out
+    def attention_from_projections(self, jobs, v_proj: torch.Tensor, *, row_offset: int = 0, last: bool = True,
+                                   softmax_scale: Optional[float] = None, **batch_args):
+        """Pre-attention transform and context-parallel attention of one layer in one go.
+
+        ``jobs`` are the q and k jobs of ``ops.qk_norm_rope_batch`` (projection output ``[B, rows, H*D]``,
+        norm weight, norm / rotary modes), ``v_proj`` the value projection, ``batch_args`` the shared
+        arguments (``num_heads``, ``eps``, ``rope_table``, ``grid``, ``axis_split``, ``pos_offset``, ``round_mid``:
+        what ``WanPreAttention.batch_args`` / ``JointPreAttention.batch_args`` return).  On the
+        pure-Ulysses peer path the transform's stores ARE the head/sequence exchange: RMSNorm, rotary and
+        cast are written straight into the peers' buffers, the attention kernel picks the rows up as
+        they arrive.  It is the fused form of what ``WanSelfAttention.forward`` does between the QKV
+        projection and ``attn_func`` (chitu_diffusion/models/model_wan.py:152-156,194-203).  Other layouts
+        run the transform locally and go through ``__call__``.
+
+        A layer whose rows are projected in several pieces (Flux's text and image streams) calls this
+        once per piece with ``row_offset`` and ``last=False`` on all but the final piece; only the final
+        call returns the attention output ``[B, s, H, D]`` (``None`` before).
+        """
+        from . import ops
+
+        pieces = getattr(self, "_pending_pieces", None) or []
+        pieces.append((jobs, v_proj, row_offset, dict(batch_args)))
+        self._pending_pieces = pieces
+        if not last:
+            return None
+        self._pending_pieces = []
+        x0 = jobs[0]["x"]
+        B, _, C = x0.shape
+        num_heads = int(batch_args["num_heads"])
+        D = C // num_heads
+        s_total = max(off + jb[0]["x"].shape[1] for jb, _, off, _ in pieces)
+        dtype = batch_args.get("out_dtype", torch.bfloat16)
+        u, r = self._split()
+        kw = dict(dropout_p=0.0, softmax_scale=softmax_scale, causal=False, window_size=(-1, -1), deterministic=False)
+        probe = torch.empty((B, 0, num_heads, D), dtype=dtype, device=x0.device)
+        if (not self.uses_agcp() and r == 1 and u > 1 and num_heads % u == 0 and x0.is_cuda
+                and self._peer_ok(probe, probe, kw)):
+            px = self.peer_exchange(B, s_total, num_heads, D, dtype, x0.device)
+            for i, (jb, vp, off, args) in enumerate(pieces):
+                px.scatter_qkv(jb, vp, row_offset=off, last=(i + 1 == len(pieces)), **args)
+            out = px.attention(softmax_scale)
+            ops.poll_status(x0.device)
+            return out
+        q, k, v = (torch.empty((B, s_total, num_heads, D), dtype=dtype, device=x0.device) for _ in range(3))
+        for jb, vp, off, args in pieces:
+            n = jb[0]["x"].shape[1]
+            jj = [dict(j, out=t[:, off:off + n]) for j, t in zip(jb, (q, k))]
+            ops.qk_norm_rope_batch(jj, out_strides=(s_total * C, C, 0, D), heads_per_group=num_heads, **args)
+            v[:, off:off + n].copy_(vp.reshape(B, n, num_heads, D))
+        return self(q, k, v, softmax_scale=softmax_scale)[0]
+
     # ------------------------------------------------------------------ producer-callback form
     @torch.compiler.disable
     def attention_fused(self, *, produce_q, produce_k, produce_v, dropout_p: float = 0.0,
@@ -345,10 +395,22 @@ class B200ContextParallel:
             return self(q, k, v, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
                         window_size=window_size, deterministic=deterministic, return_attn_probs=return_attn_probs)
         u, _ = self._split()
-        up_group = self._up_group_lookup(u)
         kw = dict(dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal, window_size=window_size,
                   deterministic=deterministic)
         k = produce_k()
+        if self._use_peer(k, k, u, 1, kw):
+            # peer-store exchange: the three tensors go out in one launch whose stores are the exchange;
+            # there is no collective left to hide behind the projections, so the producers simply run
+            v, q = produce_v(), produce_q()
+            B, s, H, D = q.shape
+            px = self.peer_exchange(B, s, H, D, q.dtype, q.device)
+            px.scatter_ready(q, k, v)
+            out = px.attention(softmax_scale)
+            from . import ops
+
+            ops.poll_status(q.device)
+            return out, None, None
+        up_group = self._up_group_lookup(u)
         side = self._side_stream(k.device)
         cur = torch.cuda.current_stream(k.device)
         side.wait_stream(cur)

@@ -20,6 +20,7 @@
 // complete and O may be touched.
 #pragma once
 
+#include "peer_sync.cuh"
 #include "ptx.cuh"
 
 namespace chitu {
@@ -62,6 +63,19 @@ struct AttnParams {
   int n_splits, tiles_per_split;
   float* part_o;
   float* part_lse;
+  // Fused exchange (in_flags != nullptr): the rows of q / k / v were stored into this GPU's buffers by
+  // n_src ranks, rows_per_src consecutive rows each, and rank s announces them in in_flags[s] (see
+  // peer_sync.cuh).  The TMA producer waits - bounded - for a rank's flag to reach *in_epoch before
+  // the first copy that touches its rows, and visits the key tiles that are wholly local_src's first,
+  // so the tensor pipe starts on rows that are already here.  With signal_out the last CTA tells
+  // every peer that this rank's output rows have landed (only when the keys are not split: a split
+  // call leaves that to the merge kernel).
+  const int* in_flags;
+  const int* in_epoch;
+  int rows_per_src, local_src;
+  long long flag_timeout;
+  PeerSync sync;
+  int signal_out;
 #ifdef CHITU_ATTN_TIMING
   long long* dbg;   // per-phase clock totals of CTA 0 (development builds only)
 #endif
@@ -135,6 +149,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int kv0 = split * p.tiles_per_split;                      // first key tile of this CTA
   const int n_kv = min(p.tiles_per_split, n_kv_total - kv0);      // >= 1 (the host sizes the splits)
   const int n_qt = (q0 + kTileM < p.Sq) ? 2 : 1;
+  // step j of this CTA works on key tile kv0 + (j + rot) % n_kv: with the fused exchange the walk
+  // starts at the first tile made only of this rank's own rows
+  int rot = 0;
+  if (p.in_flags != nullptr) {
+    const int first_local = (p.local_src * p.rows_per_src + kTileN - 1) / kTileN;
+    if (first_local >= kv0 && first_local < kv0 + n_kv && (first_local + 1) * kTileN <= (p.local_src + 1) * p.rows_per_src)
+      rot = first_local - kv0;
+  }
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -172,7 +194,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
+    // arrival flags of the fused exchange: lane 0 remembers which source ranks it has already seen
+    uint32_t src_ready = 0;
+    const int flag_epoch = (p.in_flags != nullptr && lane == 0) ? *reinterpret_cast<const volatile int*>(p.in_epoch) : 0;
+    auto wait_rows = [&](int row_lo, int row_hi, int rows_total) {  // rows [row_lo, row_hi) of a gathered tensor
+      if (p.in_flags == nullptr) return;
+      const int last = min(row_hi, rows_total) - 1;
+      for (int src = row_lo / p.rows_per_src; src <= last / p.rows_per_src; ++src) {
+        if ((src_ready >> src) & 1u) continue;
+        if (!wait_flag(p.in_flags + src, flag_epoch, p.flag_timeout, p.status)) *abort_flag = 1;
+        src_ready |= 1u << src;
+        // the rows were written by a peer's ordinary stores and are about to be read by the copy engine
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
+    };
     if (lane == 0) {
+      wait_rows(q0, q0 + n_qt * kTileM, p.Sq);
       for (int t = 0; t < n_qt; ++t) {
         mbar_arrive_expect_tx(bar_q_full + 8 * t, kTileBytes);
         tma_load_4d(q_smem + t * kTileBytes, &tm_q, bar_q_full + 8 * t, 0, head, q0 + t * kTileM, batch);
@@ -187,7 +224,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (round > 0) mbar_wait(bar_kv_empty + 8 * slot, (round - 1) & 1, abort_flag, p.status, kDevTimeoutLoad);
       if (lane == 0) {
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
-        const int row = (kv0 + (i >> 1)) * kTileN;
+        const int row = (kv0 + ((i >> 1) + rot) % n_kv) * kTileN;
+        wait_rows(row, row + kTileN, p.Sk);
         const uint32_t dst = kv_smem + slot * kTileBytes;
         const uint32_t bar = bar_kv_full + 8 * slot;
         mbar_arrive_expect_tx(bar, kTileBytes);
@@ -339,7 +377,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // Row of 128 scores into registers, 32 columns per load; the load of chunk
         // c+1 is in flight while the running maximum of chunk c is taken.
         uint32_t s[4][32];
-        const bool last_tile = (kv0 + j == n_kv_total - 1 && tail_valid < kTileN);
+        const bool last_tile = (kv0 + (j + rot) % n_kv == n_kv_total - 1 && tail_valid < kTileN);
         float mx0 = -INFINITY, mx1 = -INFINITY;
         tmem_ld32(t_s, s[0]);
 #pragma unroll
@@ -497,6 +535,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+  if (p.signal_out && threadIdx.x == 0)
+    publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, gridDim.x * gridDim.y * gridDim.z);
 }
 
 }  // namespace chitu

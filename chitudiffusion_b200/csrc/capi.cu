@@ -155,6 +155,26 @@ struct KeySplit {
   int64_t workspace_bytes = 0;
 };
 
+// Fused-exchange synchronisation of one call: wait for the arrival flags of the ranks whose rows are
+// read (rows_per_src rows each) and, at the end, announce this rank's output rows.
+struct Exchange {
+  const chitu_b200_peer_sync* sync = nullptr;
+  int rows_per_src = 0;
+};
+
+int fill_peer_sync(chitu::PeerSync* ps, const chitu_b200_peer_sync* sync, const char* what) {
+  if (!sync || !sync->blocks || sync->world < 1 || sync->world > 8 || sync->rank < 0 || sync->rank >= sync->world)
+    return fail(CHITU_E_INVALID, "%s: need a sync descriptor with 1..8 ranks and a rank inside the group", what);
+  for (int i = 0; i < 8; ++i) ps->blocks[i] = i < sync->world ? sync->blocks[i] : nullptr;
+  for (int i = 0; i < sync->world; ++i)
+    if (!ps->blocks[i] || (reinterpret_cast<uintptr_t>(ps->blocks[i]) & 3))
+      return fail(CHITU_E_INVALID, "%s: sync block of rank %d null or misaligned", what, i);
+  ps->rank = sync->rank;
+  ps->world = sync->world;
+  ps->timeout_cycles = g_flag_wait_cycles;
+  return CHITU_OK;
+}
+
 int64_t splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits) {
   if (n_splits <= 1) return 0;
   const int64_t rows = static_cast<int64_t>(B) * Sq * H;
@@ -164,7 +184,7 @@ int64_t splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits) {
 int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const OutScatter& sc, float* lse, int B,
                   int Sq, int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
                   const int64_t* v_strides, float softmax_scale, int dtype, int* status, void* stream,
-                  const KeySplit& ks = KeySplit{}) {
+                  const KeySplit& ks = KeySplit{}, const Exchange& ex = Exchange{}) {
   if (!q || !k || !v || (!out && sc.n_dest == 0) || !q_strides || !k_strides || !v_strides)
     return fail(CHITU_E_INVALID, "attn_fwd: null pointer argument");
   if (sc.n_dest != 0) {
@@ -225,6 +245,24 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   p.tiles_per_split = tiles_per_split;
   p.part_o = static_cast<float*>(ks.workspace);
   p.part_lse = p.part_o ? p.part_o + static_cast<size_t>(n_splits) * B * Sq * H * D : nullptr;
+  p.in_flags = nullptr;
+  p.in_epoch = nullptr;
+  p.rows_per_src = p.local_src = 0;
+  p.flag_timeout = g_flag_wait_cycles;
+  p.signal_out = 0;
+  for (int i = 0; i < 8; ++i) p.sync.blocks[i] = nullptr;
+  p.sync.rank = p.sync.world = 0;
+  p.sync.timeout_cycles = g_flag_wait_cycles;
+  if (ex.sync != nullptr) {
+    if ((rc = fill_peer_sync(&p.sync, ex.sync, "attn_fwd_exchange")) != CHITU_OK) return rc;
+    if (ex.rows_per_src <= 0 || static_cast<int64_t>(ex.rows_per_src) * p.sync.world < (Sq > Sk ? Sq : Sk))
+      return fail(CHITU_E_INVALID, "attn_fwd_exchange: rows_per_src * world must cover the sequence");
+    p.in_flags = p.sync.blocks[p.sync.rank] + chitu::kSyncInFlag;
+    p.in_epoch = p.sync.blocks[p.sync.rank] + chitu::kSyncInEpoch;
+    p.rows_per_src = ex.rows_per_src;
+    p.local_src = p.sync.rank;
+    p.signal_out = n_splits == 1;
+  }
 #ifdef CHITU_ATTN_TIMING
   p.dbg = g_dbg;
 #endif
@@ -262,6 +300,8 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     c.dest_row_bytes = p.dest_row_bytes;
     c.dest_head_bytes = p.dest_head_bytes;
     for (int i = 0; i < 8; ++i) c.out_ptrs[i] = p.out_ptrs[i];
+    c.sync = p.sync;
+    c.signal_out = ex.sync != nullptr;
     const long long rows = static_cast<long long>(B) * Sq * H;
     chitu::splitkv_combine_kernel<<<grid_for(rows, 8, 148 * 16), 256, 0, st>>>(c);
     e = cudaGetLastError();
@@ -319,6 +359,43 @@ int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, voi
                        dtype, status, stream, ks);
 }
 
+int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
+                                 int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
+                                 int64_t dest_head_offset, int B, int Sq, int Sk, int H, int D,
+                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                 float softmax_scale, int dtype, int n_splits, void* workspace,
+                                 int64_t workspace_bytes, int rows_per_src, const chitu_b200_peer_sync* sync,
+                                 int* status, void* stream) {
+  KeySplit ks;
+  ks.n_splits = n_splits;
+  ks.workspace = workspace;
+  ks.workspace_bytes = workspace_bytes;
+  OutScatter sc;
+  sc.ptrs = out_ptrs;
+  sc.n_dest = n_dest;
+  sc.rows_per_dest = rows_per_dest;
+  sc.batch_stride = dest_batch_stride;
+  sc.row_stride = dest_row_stride;
+  sc.head_offset = dest_head_offset;
+  if (n_dest <= 0) return fail(CHITU_E_INVALID, "attn_fwd_exchange: n_dest must be positive");
+  if (!sync) return fail(CHITU_E_INVALID, "attn_fwd_exchange: sync descriptor missing");
+  Exchange ex;
+  ex.sync = sync;
+  ex.rows_per_src = rows_per_src;
+  return attn_fwd_impl(q, k, v, nullptr, sc, nullptr, B, Sq, Sk, H, D, q_strides, k_strides, v_strides, softmax_scale,
+                       dtype, status, stream, ks, ex);
+}
+
+int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, void* stream) {
+  chitu::PeerSync ps;
+  int rc = fill_peer_sync(&ps, sync, "peer_wait_outputs");
+  if (rc != CHITU_OK) return rc;
+  chitu::peer_wait_outputs_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "peer_wait_outputs: launch");
+  return CHITU_OK;
+}
+
 int chitu_b200_lse_combine(float* acc_out, float* acc_lse, const void* block_out, const float* block_lse, int B, int S,
                            int H, int D, int block_dtype, int first, void* final_out, int final_dtype, void* stream) {
   if (!acc_out || !acc_lse || !block_out || !block_lse) return fail(CHITU_E_INVALID, "lse_combine: null pointer");
@@ -354,7 +431,8 @@ struct NormRopeShared {
   int heads_per_group, B, S, H, D, round_mid;
 };
 
-int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, const NormRopeShared& sh, void* stream) {
+int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, const NormRopeShared& sh, void* stream,
+                            const chitu_b200_peer_sync* sync = nullptr) {
   if (!jobs || n_jobs < 1 || n_jobs > 3) return fail(CHITU_E_INVALID, "qk_norm_rope: 1..3 jobs per launch");
   if (!sh.out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
   const int B = sh.B, S = sh.S, H = sh.H, D = sh.D;
@@ -377,6 +455,15 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
   if (tokens > 2147483647LL) return fail(CHITU_E_UNSUPPORTED, "qk_norm_rope: too many tokens");
 
   chitu::NormRopeBatch batch;
+  batch.signal = 0;
+  for (int i = 0; i < 8; ++i) batch.sync.blocks[i] = nullptr;
+  batch.sync.rank = batch.sync.world = 0;
+  batch.sync.timeout_cycles = g_flag_wait_cycles;
+  if (sync != nullptr) {
+    const int rc = fill_peer_sync(&batch.sync, sync, "qk_norm_rope_batch_signal");
+    if (rc != CHITU_OK) return rc;
+    batch.signal = 1;
+  }
   for (int j = 0; j < n_jobs; ++j) {
     const chitu_b200_norm_rope_job& jb = jobs[j];
     chitu::NormRopeParams& p = batch.job[j];
@@ -541,6 +628,17 @@ int chitu_b200_qk_norm_rope_batch(const chitu_b200_norm_rope_job* jobs, int n_jo
   NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
                     out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
   return qk_norm_rope_batch_impl(jobs, n_jobs, sh, stream);
+}
+
+int chitu_b200_qk_norm_rope_batch_signal(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
+                                         float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                                         const int* axis_split, int64_t pos_offset, int out_dtype,
+                                         const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                                         int round_mid, const chitu_b200_peer_sync* sync, void* stream) {
+  if (!sync) return fail(CHITU_E_INVALID, "qk_norm_rope_batch_signal: sync descriptor missing");
+  NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
+                    out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
+  return qk_norm_rope_batch_impl(jobs, n_jobs, sh, stream, sync);
 }
 
 int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream) {

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "peer_sync.cuh"
+
 namespace chitu {
 
 enum : int { kBF16 = 0, kFP16 = 1, kFP32 = 2 };
@@ -117,6 +119,9 @@ struct SplitCombineParams {
   void* out_ptrs[8];
   int n_dest, rows_per_dest;
   long long dest_batch_bytes, dest_row_bytes, dest_head_bytes;
+  // when signal_out is set, the last CTA tells every peer that this rank's output rows have landed
+  PeerSync sync;
+  int signal_out;
 };
 
 __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitCombineParams p) {
@@ -162,6 +167,10 @@ __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitCombine
       *reinterpret_cast<uint2*>(orow + d * 2) = raw;
     }
     if (lane == 0 && p.lse != nullptr) p.lse[lidx] = mx + logf(wsum);
+  }
+  if (p.signal_out) {
+    __syncthreads();
+    if (threadIdx.x == 0) publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, gridDim.x);
   }
 }
 
@@ -251,6 +260,9 @@ __device__ __forceinline__ void unpack8(const RawVec8<kInDtype>& r, float (&v)[8
 // scatter (the v tensor).
 struct NormRopeBatch {
   NormRopeParams job[3];
+  // when signal is set, the last CTA of the launch tells every peer that this rank's rows have landed
+  PeerSync sync;
+  int signal;
 };
 
 // tokens per iteration: 4 for 16-bit inputs, 2 for fp32 (the same bytes in flight)
@@ -452,8 +464,8 @@ __device__ __forceinline__ void qk_norm_rope_job(const NormRopeParams& p, float 
 // Picks the instance of the job blockIdx.y points at: a job whose own modes are (2, 0) is a plain
 // cast / scatter whatever the launch's template modes are.
 template <int kInDtype, int kNormModeT, int kRopeModeT>
-__device__ __forceinline__ void qk_norm_rope_body(const NormRopeBatch& batch) {
-  __shared__ float red[2][NormRopeTokens<kInDtype>::value][kNormMaxThreads / 32];
+__device__ __forceinline__ void qk_norm_rope_dispatch(const NormRopeBatch& batch,
+                                                      float (*red)[NormRopeTokens<kInDtype>::value][kNormMaxThreads / 32]) {
   const NormRopeParams& p = batch.job[blockIdx.y];
   const bool out_bf16 = p.out_dtype == kBF16;
   if (p.norm_mode == 2 && p.rope_mode == 0) {
@@ -474,6 +486,20 @@ __device__ __forceinline__ void qk_norm_rope_body(const NormRopeBatch& batch) {
     if (round == 0) qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 0, false>(p, red);
     else if (round == 1) qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 1, false>(p, red);
     else qk_norm_rope_job<kInDtype, kNormModeT, kRopeModeT, 2, false>(p, red);
+  }
+}
+
+// Picks the instance of the job blockIdx.y points at: a job whose own modes are (2, 0) is a plain
+// cast / scatter whatever the launch's template modes are.  A launch that feeds the fused exchange
+// ends by publishing "my rows have landed" to every peer (last-block pattern).
+template <int kInDtype, int kNormModeT, int kRopeModeT>
+__device__ __forceinline__ void qk_norm_rope_body(const NormRopeBatch& batch) {
+  __shared__ float red[2][NormRopeTokens<kInDtype>::value][kNormMaxThreads / 32];
+  qk_norm_rope_dispatch<kInDtype, kNormModeT, kRopeModeT>(batch, red);
+  if (batch.signal) {
+    __syncthreads();
+    if (threadIdx.x == 0)
+      publish_when_last(batch.sync, kSyncScatterDone, kSyncInEpoch, kSyncInFlag, gridDim.x * gridDim.y);
   }
 }
 

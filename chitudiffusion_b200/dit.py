@@ -108,8 +108,13 @@ class WanBlock:
         # self-attention
         h = ops.layernorm_modulate(x, mod[:, 1], mod[:, 0], add_one=True, eps=self.eps, out_dtype=self.dtype)
         qkv = F.linear(h, w["qkv.weight"], w["qkv.bias"])
-        q, k, v = pre(qkv[..., :C], qkv[..., C:2 * C], qkv[..., 2 * C:], w["norm_q"], w["norm_k"], grid)
-        o = attn(q, k, v)[0]
+        if hasattr(attn, "attention_from_projections"):
+            # context-parallel wrapper: norm + rotary + cast are written straight into the exchange
+            o = attn.attention_from_projections(pre.jobs(qkv[..., :C], qkv[..., C:2 * C], w["norm_q"], w["norm_k"]),
+                                                qkv[..., 2 * C:], **pre.batch_args(L, grid))
+        else:
+            q, k, v = pre(qkv[..., :C], qkv[..., C:2 * C], qkv[..., 2 * C:], w["norm_q"], w["norm_k"], grid)
+            o = attn(q, k, v)[0]
         if o.dtype != self.dtype:  # ring layouts hand back fp32 (the caller casts, model_wan.py:203)
             o = o.to(self.dtype)
         ops.gate_residual(x, F.linear(o.reshape(B, L, C), w["o.weight"], w["o.bias"]), mod[:, 2])

@@ -110,14 +110,26 @@ class FluxDoubleBlock:
         n_txt = txt.shape[1]
         D = C // H
         streams = (("txt", txt, 0), ("img", img, n_txt))
-        joint = tuple(torch.empty((B, n_txt + n_img, H, D), dtype=self.dtype, device=img.device) for _ in range(3))
+        fused = hasattr(attn, "attention_from_projections")  # context-parallel wrapper: stores go straight into the exchange
+        joint = None if fused else tuple(
+            torch.empty((B, n_txt + n_img, H, D), dtype=self.dtype, device=img.device) for _ in range(3))
         mods = {}
+        o = None
         for s, x, off in streams:
             mods[s] = _mod(temb, w[f"{s}.mod.weight"], w[f"{s}.mod.bias"], 6)
             h = ops.layernorm_modulate(x, mods[s][:, 1], mods[s][:, 0], add_one=True, eps=self.eps, out_dtype=self.dtype)
             qkv = F.linear(h, w[f"{s}.qkv.weight"], w[f"{s}.qkv.bias"])
-            _pre_attention(qkv, H, w[f"{s}.norm_q"], w[f"{s}.norm_k"], table, off, joint, self.eps)
-        o = attn(*joint)[0].reshape(B, n_txt + n_img, C)
+            if fused:
+                jobs = [dict(x=qkv[..., :C], weight=w[f"{s}.norm_q"], norm_mode=1, rope_mode=2),
+                        dict(x=qkv[..., C:2 * C], weight=w[f"{s}.norm_k"], norm_mode=1, rope_mode=2)]
+                o = attn.attention_from_projections(jobs, qkv[..., 2 * C:], row_offset=off, last=(s == "img"),
+                                                    num_heads=H, eps=self.eps, rope_table=table, pos_offset=off,
+                                                    out_dtype=self.dtype, round_mid=False)
+            else:
+                _pre_attention(qkv, H, w[f"{s}.norm_q"], w[f"{s}.norm_k"], table, off, joint, self.eps)
+        if not fused:
+            o = attn(*joint)[0]
+        o = o.reshape(B, n_txt + n_img, C)
         for s, x, off in streams:
             m = mods[s]
             o_s = o[:, off:off + x.shape[1]]
@@ -181,8 +193,12 @@ class FluxSingleBlock:
         mlp = torch._addmm_activation(w["mlp.bias"], h.view(-1, C), w["mlp.weight"].t(), use_gelu=True)
         jobs = [dict(x=qkv[..., :C], weight=w["norm_q"], norm_mode=1, rope_mode=2),
                 dict(x=qkv[..., C:2 * C], weight=w["norm_k"], norm_mode=1, rope_mode=2)]
-        q, k = ops.qk_norm_rope_batch(jobs, H, self.eps, table, out_dtype=self.dtype, round_mid=False)
-        o = attn(q, k, qkv[..., 2 * C:].view(B, S, H, D))[0]
+        if hasattr(attn, "attention_from_projections"):
+            o = attn.attention_from_projections(jobs, qkv[..., 2 * C:], num_heads=H, eps=self.eps, rope_table=table,
+                                                out_dtype=self.dtype, round_mid=False)
+        else:
+            q, k = ops.qk_norm_rope_batch(jobs, H, self.eps, table, out_dtype=self.dtype, round_mid=False)
+            o = attn(q, k, qkv[..., 2 * C:].view(B, S, H, D))[0]
         y = torch.addmm(w["out.bias"], o.reshape(B * S, C), w["out_attn.weight"].t())
         y = torch.addmm(y, mlp, w["out_mlp.weight"].t())
         ops.gate_residual(x, y.view(B, S, C), m[:, 2])

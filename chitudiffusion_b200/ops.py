@@ -27,6 +27,14 @@ _STATUS_NAMES = {
 
 _status_words = {}
 
+# kernels of this library launched so far by this process (the bench reports the count of a timed region)
+launch_count = 0
+
+
+def _launched(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
 
 def _stream_ptr(device: torch.device) -> int:
     return int(torch.cuda.current_stream(device).cuda_stream)
@@ -201,6 +209,7 @@ def attn_fwd(
                 status_word(q.device).data_ptr(), _stream_ptr(q.device),
             )
     _lib.check(rc, "attn_fwd")
+    _launched(2 if n_splits > 1 and Sk > 128 else 1)
     return out, lse
 
 
@@ -238,6 +247,7 @@ def attn_fwd_q8(
             scale, _DTYPES[q.dtype], base, need, status_word(q.device).data_ptr(), _stream_ptr(q.device),
         )
     _lib.check(rc, "attn_fwd_q8")
+    _launched(3)
     return out, lse
 
 
@@ -275,6 +285,7 @@ def lse_combine(
             _DTYPES[final_out.dtype] if final_out is not None else 0, _stream_ptr(acc_out.device),
         )
     _lib.check(rc, "lse_combine")
+    _launched()
 
 
 def qk_norm_rope(
@@ -347,6 +358,7 @@ def qk_norm_rope(
         else:
             rc = lib.chitu_b200_qk_norm_rope(*common, out.data_ptr(), _DTYPES[out.dtype], *tail)
     _lib.check(rc, "qk_norm_rope")
+    _launched()
     return out
 
 
@@ -362,8 +374,12 @@ def qk_norm_rope_batch(
     heads_per_group: Optional[int] = None,
     out_dtype: torch.dtype = torch.bfloat16,
     round_mid: bool = True,
+    sync=None,
 ):
     """Up to three pre-attention jobs (q, k, v) in one launch; see ``chitu_b200_qk_norm_rope_batch``.
+
+    With ``sync`` (a ``_lib.peer_sync_desc`` pair) the launch ends by announcing this rank's rows to its
+    peers (``chitu_b200_qk_norm_rope_batch_signal``).
 
     Each job is a dict with ``x [B,S,H*D]``, optional ``weight``, ``norm_mode``, ``rope_mode`` and
     either ``out`` (tensor), ``out_ptrs`` (list of device addresses) or neither (a contiguous
@@ -417,15 +433,22 @@ def qk_norm_rope_batch(
         raise ValueError("rope_table must be a contiguous fp32 [rows, D/2, 2] tensor")
     split = (ctypes.c_int * 2)(int(axis_split[0]), int(axis_split[1]))
     lib = _lib.load()
+    args = (
+        arr, len(jobs), _DTYPES[x0.dtype], _DTYPES[w_dtype] if w_dtype is not None else _lib.DTYPE_FP32,
+        float(eps), rope_table.data_ptr() if rope_table is not None else None,
+        int(rope_table.shape[0]) if rope_table is not None else 0, int(grid[0]), int(grid[1]), int(grid[2]),
+        split, int(pos_offset), _DTYPES[out_dtype], _lib.i64_array(out_strides), int(heads_per_group),
+        B, S, num_heads, D, 1 if round_mid else 0,
+    )
     with torch.cuda.device(x0.device):
-        rc = lib.chitu_b200_qk_norm_rope_batch(
-            arr, len(jobs), _DTYPES[x0.dtype], _DTYPES[w_dtype] if w_dtype is not None else _lib.DTYPE_FP32,
-            float(eps), rope_table.data_ptr() if rope_table is not None else None,
-            int(rope_table.shape[0]) if rope_table is not None else 0, int(grid[0]), int(grid[1]), int(grid[2]),
-            split, int(pos_offset), _DTYPES[out_dtype], _lib.i64_array(out_strides), int(heads_per_group),
-            B, S, num_heads, D, 1 if round_mid else 0, _stream_ptr(x0.device),
-        )
+        if sync is not None:
+            import ctypes as _ct
+
+            rc = lib.chitu_b200_qk_norm_rope_batch_signal(*args, _ct.byref(sync[0]), _stream_ptr(x0.device))
+        else:
+            rc = lib.chitu_b200_qk_norm_rope_batch(*args, _stream_ptr(x0.device))
     _lib.check(rc, "qk_norm_rope_batch")
+    _launched()
     return outs
 
 
@@ -442,6 +465,7 @@ def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
             _lib.i64_array([s * es for s in src.stride()[:4]]), _stream_ptr(src.device),
         )
     _lib.check(rc, "strided_copy")
+    _launched()
     return dst
 
 
@@ -471,6 +495,7 @@ def layernorm_modulate(x: torch.Tensor, mul: Optional[torch.Tensor] = None, add:
             m.data_ptr() if m is not None else None, ms,
             a.data_ptr() if a is not None else None, as_, int(add_one), float(eps), _stream_ptr(x.device))
     _lib.check(rc, "layernorm_modulate")
+    _launched()
     return out
 
 
@@ -491,6 +516,7 @@ def gate_residual(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor]
         rc = lib.chitu_b200_gate_residual(x.data_ptr(), _DTYPES[x.dtype], y.data_ptr(), _DTYPES[y.dtype], B * L, L, C,
                                           g.data_ptr() if g is not None else None, gs, _stream_ptr(x.device))
     _lib.check(rc, "gate_residual")
+    _launched()
     return x
 
 
@@ -507,6 +533,7 @@ def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, scale: float, rescale:
         rc = lib.chitu_b200_cfg_combine(cond.data_ptr(), uncond.data_ptr(), out.data_ptr(), _DTYPES[cond.dtype],
                                         cond.numel() // C, C, float(scale), int(rescale), _stream_ptr(cond.device))
     _lib.check(rc, "cfg_combine")
+    _launched()
     return out
 
 
@@ -533,6 +560,7 @@ def scatter_rows(src: torch.Tensor, dst_ptrs: Sequence[int], rows: int, dst_batc
                                          int(rows), int(row_bytes), int(dst_batch_stride_bytes),
                                          int(dst_row_stride_bytes), _stream_ptr(src.device))
     _lib.check(rc, "scatter_rows")
+    _launched()
 
 
 def attn_fwd_scatter(
@@ -574,6 +602,7 @@ def attn_fwd_scatter(
             _stream_ptr(q.device),
         )
     _lib.check(rc, "attn_fwd_scatter")
+    _launched(2 if n_splits > 1 and Sk > 128 else 1)
 
 
 def peer_barrier(flag_ptrs: Sequence[int], rank: int, world: int, device: torch.device) -> None:
@@ -583,3 +612,61 @@ def peer_barrier(flag_ptrs: Sequence[int], rank: int, world: int, device: torch.
         rc = lib.chitu_b200_peer_barrier(_lib.ptr_array(flag_ptrs), int(rank), int(world),
                                          status_word(device).data_ptr(), _stream_ptr(device))
     _lib.check(rc, "peer_barrier")
+    _launched()
+
+
+def attn_fwd_exchange(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out_ptrs: Sequence[int],
+    rows_per_dest: int,
+    dest_batch_stride: int,
+    dest_row_stride: int,
+    dest_head_offset: int,
+    rows_per_src: int,
+    sync,
+    softmax_scale: Optional[float] = None,
+    n_splits: Optional[int] = None,
+    workspace: Optional[torch.Tensor] = None,
+) -> None:
+    """:func:`attn_fwd_scatter` over exchange buffers guarded by arrival flags; see ``chitu_b200_attn_fwd_exchange``."""
+    import ctypes
+
+    _require_cuda(q, k, v)
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError("attention kernel takes bf16 or fp16 q/k/v of one dtype")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    lib = _lib.load()
+    if n_splits is None:
+        n_splits = auto_key_splits(B, Sq, Sk, H)
+    ws_ptr, ws_bytes = None, 0
+    if n_splits > 1:
+        need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
+        ws = workspace if workspace is not None else splitkv_workspace(q.device, need)
+        if ws.numel() * ws.element_size() < need or ws.device != q.device:
+            raise ValueError(f"attn_fwd_exchange: workspace must hold {need} bytes on {q.device}")
+        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+    with torch.cuda.device(q.device):
+        rc = lib.chitu_b200_attn_fwd_exchange(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr_array(out_ptrs), len(out_ptrs), int(rows_per_dest),
+            int(dest_batch_stride), int(dest_row_stride), int(dest_head_offset), B, Sq, Sk, H, D,
+            _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale,
+            _DTYPES[q.dtype], int(n_splits), ws_ptr, ws_bytes, int(rows_per_src), ctypes.byref(sync[0]),
+            status_word(q.device).data_ptr(), _stream_ptr(q.device),
+        )
+    _lib.check(rc, "attn_fwd_exchange")
+    _launched(2 if n_splits > 1 and Sk > 128 else 1)
+
+
+def peer_wait_outputs(sync, device: torch.device) -> None:
+    """Enqueue the bounded wait for every rank's output flag; see ``chitu_b200_peer_wait_outputs``."""
+    import ctypes
+
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        rc = lib.chitu_b200_peer_wait_outputs(ctypes.byref(sync[0]), status_word(device).data_ptr(), _stream_ptr(device))
+    _lib.check(rc, "peer_wait_outputs")
+    _launched()

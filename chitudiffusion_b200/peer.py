@@ -33,10 +33,24 @@ def _align(n: int, a: int = 256) -> int:
 
 
 class PeerUlysses:
-    """Exchange buffers and per-layer schedule for one ``(B, s, H, D, dtype)`` problem shape."""
+    """Exchange buffers and per-layer schedule for one ``(B, s, H, D, dtype)`` problem shape.
+
+    Per layer: ONE pre-attention launch stores this rank's q / k / v rows into every peer and announces
+    them (arrival flags, ``csrc/peer_sync.cuh``); the attention kernel's copy warp waits per source rank
+    for exactly the rows it is about to load - its own rows first - and its last CTA (or the key-split
+    merge kernel's) announces the output rows; a one-warp kernel waits for every rank's output flag.
+    Three launches per layer (four when the keys are split), no barrier launch, no NCCL call.
+
+    The q / k / v buffers need no double buffering: a rank announces its outputs only when its whole
+    attention grid has finished, and nobody scatters the next layer before having seen every rank's
+    output flag.  The output buffer alternates between two slots, so the tensor handed back stays valid
+    until the call after next (the reference hands back a fresh tensor; no copy is made here).
+    """
 
     def __init__(self, group: CommGroup, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device):
         import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
 
         U = group.group_size
         if H % U:
@@ -49,18 +63,20 @@ class PeerUlysses:
         es = torch.empty((), dtype=dtype).element_size()
         self.es = es
         tile = B * U * s * self.hc * D * es  # one of q / k / v in the gathered layout
+        out_bytes = _align(B * s * H * D * es)
         self.off_q = 0
         self.off_k = _align(tile)
         self.off_v = self.off_k + _align(tile)
-        self.off_out = self.off_v + _align(tile)
-        self.off_flags = self.off_out + _align(B * s * H * D * es)
-        total = self.off_flags + 256
+        self.off_out = self.off_v + _align(tile)  # two output slots
+        self.off_flags = self.off_out + 2 * out_bytes
+        self._out_bytes = out_bytes
+        total = self.off_flags + 4 * _lib.SYNC_INTS
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group.gpu_group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         torch.cuda.synchronize(device)
-        dist.barrier(group=group.gpu_group)  # every flag array is zero before anyone signals
+        dist.barrier(group=group.gpu_group)  # every sync block is zero before anyone signals
 
         def view(off, shape):
             n = 1
@@ -70,48 +86,77 @@ class PeerUlysses:
 
         gathered = (B, U * s, self.hc, D)
         self.q, self.k, self.v = view(self.off_q, gathered), view(self.off_k, gathered), view(self.off_v, gathered)
-        self.out = view(self.off_out, (B, s, H, D))
+        self.outs = [view(self.off_out + i * out_bytes, (B, s, H, D)) for i in range(2)]
+        self.out = self.outs[0]
+        self._out_slot = 0
         self.flag_ptrs = [p + self.off_flags for p in self.ptrs]
+        self.sync = _lib.peer_sync_desc(self.flag_ptrs, self.rank)
         # element strides (b, s, -, h) of the gathered layout; this rank's rows start at rank * s
         self.gather_strides = (U * s * self.hc * D, self.hc * D, 0, D)
-        self._row0 = self.rank * s * self.hc * D * es
+        self._row_bytes = self.hc * D * es
+        self._row0 = self.rank * s * self._row_bytes
+        # key-split scratch owned by this object: graphs captured over it keep a valid address
+        self.n_splits = ops.auto_key_splits(B, U * s, U * s, self.hc)
+        need = ops.splitkv_workspace_bytes(B, U * s, self.hc, D, self.n_splits)
+        self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=device) if self.n_splits > 1 else None
 
-    def dest_ptrs(self, which: str):
-        """Per-destination base addresses for this rank's rows of q / k / v."""
+    def dest_ptrs(self, which: str, row_offset: int = 0):
+        """Per-destination base addresses for this rank's rows (from local row ``row_offset`` on) of q / k / v."""
         off = {"q": self.off_q, "k": self.off_k, "v": self.off_v}[which]
-        return [p + off + self._row0 for p in self.ptrs]
+        return [p + off + self._row0 + row_offset * self._row_bytes for p in self.ptrs]
 
     def barrier(self) -> None:
         ops.peer_barrier(self.flag_ptrs, self.rank, self.U, self.device)
 
     def scatter_plain(self, x: torch.Tensor, which: str = "v") -> None:
-        """``x [B, s, H*D]`` (or ``[B,s,H,D]``) 16-bit: copy each head group to its owner."""
+        """``x [B, s, H*D]`` (or ``[B,s,H,D]``) 16-bit: copy each head group to its owner (no announcement)."""
         flat = x.reshape(self.B, self.s, self.H * self.D)
         ops.qk_norm_rope(flat, self.H, None, 0.0, norm_mode=2, rope_mode=0, rope_table=None,
                          out_ptrs=self.dest_ptrs(which), out_strides=self.gather_strides,
                          heads_per_group=self.hc, out_dtype=self.dtype)
 
-    def scatter_qkv(self, jobs, v: torch.Tensor, **batch_args) -> None:
-        """One launch: the q and k jobs of a pre-attention object plus the plain scatter of ``v``."""
+    def scatter_qkv(self, jobs, v: torch.Tensor, row_offset: int = 0, last: bool = True, **batch_args) -> None:
+        """One launch: the q and k jobs of a pre-attention object plus the plain scatter of ``v``.
+
+        The jobs cover local rows ``[row_offset, row_offset + rows)`` (a layer whose streams are projected
+        separately - Flux's text and image streams - scatters them with one call each).  The call with
+        ``last=True`` announces the rank's rows of this layer to its peers.
+        """
         jobs = [dict(j) for j in jobs]
+        batch_args.pop("out_dtype", None)  # the exchange buffers fix the store type
+        rows = jobs[0]["x"].shape[1]
         if v.dtype == jobs[0]["x"].dtype:
-            jobs.append(dict(x=v.reshape(self.B, self.s, self.H * self.D), norm_mode=2, rope_mode=0))
+            jobs.append(dict(x=v.reshape(self.B, rows, self.H * self.D), norm_mode=2, rope_mode=0))
         else:  # a launch shares one input dtype
-            self.scatter_plain(v, "v")
+            flat = v.reshape(self.B, rows, self.H * self.D)
+            ops.qk_norm_rope(flat, self.H, None, 0.0, norm_mode=2, rope_mode=0, rope_table=None,
+                             out_ptrs=self.dest_ptrs("v", row_offset), out_strides=self.gather_strides,
+                             heads_per_group=self.hc, out_dtype=self.dtype)
         for j, which in zip(jobs, ("q", "k", "v")):
-            j["out_ptrs"] = self.dest_ptrs(which)
+            j["out_ptrs"] = self.dest_ptrs(which, row_offset)
         ops.qk_norm_rope_batch(jobs, out_strides=self.gather_strides, heads_per_group=self.hc, out_dtype=self.dtype,
-                               **batch_args)
+                               sync=self.sync if last else None, **batch_args)
+
+    def scatter_ready(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        """q, k, v ``[B, s, H, D]`` that are already normalised and rotated: one launch of three plain jobs."""
+        jobs = [dict(x=t.reshape(self.B, self.s, self.H * self.D), norm_mode=2, rope_mode=0,
+                     out_ptrs=self.dest_ptrs(w)) for t, w in ((q, "q"), (k, "k"), (v, "v"))]
+        ops.qk_norm_rope_batch(jobs, num_heads=self.H, eps=0.0, rope_table=None, out_strides=self.gather_strides,
+                               heads_per_group=self.hc, out_dtype=self.dtype, sync=self.sync)
 
     def attention(self, softmax_scale: Optional[float] = None) -> torch.Tensor:
-        """Barrier, attention over the gathered q/k/v with the output scattered to its owners, barrier."""
-        self.barrier()
-        ops.attn_fwd_scatter(
-            self.q, self.k, self.v, [p + self.off_out for p in self.ptrs], rows_per_dest=self.s,
+        """Attention over the gathered q/k/v as their rows arrive, output rows stored to their owners, then the
+        wait for every rank's outputs.  Returns this rank's ``[B, s, H, D]`` result (valid until the call after next)."""
+        self._out_slot ^= 1
+        slot_off = self.off_out + self._out_slot * self._out_bytes
+        ops.attn_fwd_exchange(
+            self.q, self.k, self.v, [p + slot_off for p in self.ptrs], rows_per_dest=self.s,
             dest_batch_stride=self.s * self.H * self.D, dest_row_stride=self.H * self.D,
-            dest_head_offset=self.rank * self.hc * self.D, softmax_scale=softmax_scale,
+            dest_head_offset=self.rank * self.hc * self.D, rows_per_src=self.s, sync=self.sync,
+            softmax_scale=softmax_scale, n_splits=self.n_splits, workspace=self.workspace,
         )
-        self.barrier()
+        ops.peer_wait_outputs(self.sync, self.device)
+        self.out = self.outs[self._out_slot]
         return self.out
 
 

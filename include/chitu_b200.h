@@ -302,6 +302,47 @@ int chitu_b200_attn_fwd_scatter(const void* q, const void* k, const void* v, voi
 int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream);
 
 /*
+ * The same exchange without barrier launches: arrival flags.  (Same reference lines as above; what they
+ * replace in addition is the stream-order wait the reference gets from NCCL between its all-to-all and the
+ * attention kernel.)
+ *
+ * Every rank owns a "sync block" of CHITU_SYNC_INTS int32 in peer-mapped memory, zero before first use;
+ * sync->blocks[i] is rank i's block as mapped into this process.  All counters in it are per-layer epochs
+ * kept on the device, so the three calls below take no per-layer argument and replay from a CUDA graph;
+ * every rank must issue the same sequence of them.
+ *
+ * chitu_b200_qk_norm_rope_batch_signal: chitu_b200_qk_norm_rope_batch whose last CTA, once all of the
+ *   launch's stores are ordered, writes the new epoch into every peer's "rows of rank r have landed" flag.
+ *   One signalling launch per layer (put q, k and v in it).
+ * chitu_b200_attn_fwd_exchange: chitu_b200_attn_fwd_scatter over buffers filled that way.  Rows
+ *   [s*rows_per_src, (s+1)*rows_per_src) of q, k and v came from rank s: the kernel's copy warp waits
+ *   (bounded, status 5 on timeout) for rank s's flag before its first copy that touches them, and walks
+ *   the key tiles starting with this rank's own rows.  When the last output row has been stored it writes
+ *   the new epoch into every peer's "outputs of rank r have landed" flag.
+ * chitu_b200_peer_wait_outputs: one warp that waits (bounded) until every rank's output flag has reached
+ *   the next epoch: after it, this rank's output buffer is complete, and - because a rank signals only
+ *   when its whole attention grid has finished - its q / k / v buffers may be overwritten by the next layer.
+ */
+#define CHITU_SYNC_INTS 64
+typedef struct {
+  int* const* blocks;
+  int rank, world;
+} chitu_b200_peer_sync;
+int chitu_b200_qk_norm_rope_batch_signal(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
+                                         float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                                         const int* axis_split, int64_t pos_offset, int out_dtype,
+                                         const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                                         int round_mid, const chitu_b200_peer_sync* sync, void* stream);
+int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
+                                 int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
+                                 int64_t dest_head_offset, int B, int Sq, int Sk, int H, int D,
+                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                 float softmax_scale, int dtype, int n_splits, void* workspace,
+                                 int64_t workspace_bytes, int rows_per_src, const chitu_b200_peer_sync* sync,
+                                 int* status, void* stream);
+int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, void* stream);
+
+/*
  * Clock budget (GPU cycles) of the flag waits in chitu_b200_peer_barrier and in the arrival-flag
  * polls of the fused exchange; applies to launches made after the call, process-wide.  Returns the
  * previous budget; a non-positive argument only queries.  The default, 2^31 cycles, is about a second -

@@ -115,14 +115,29 @@ def main():
     place = dict(out_strides=px.gather_strides, heads_per_group=px.hc)
     for rep in range(3):  # buffers and barriers are reused call after call
         lq, lk, lv = (t[:, sl].contiguous().to(dev) for t in (xq, xk, xv))
-        if rep == 0:  # tensor by tensor
-            pre.one(lq, wq.to(dev), grid, out_ptrs=px.dest_ptrs("q"), **place)
-            pre.one(lk, wk.to(dev), grid, out_ptrs=px.dest_ptrs("k"), **place)
-            px.scatter_plain(lv, "v")
-        else:  # q, k and v in one launch
+        if rep == 0:  # transform locally, then one launch of three plain scatters that announces the rows
+            tq, tk, tv = pre(lq, lk, lv, wq.to(dev), wk.to(dev), grid)
+            px.scatter_ready(tq, tk, tv)
+        else:  # norm + rotary + scatter of q, k and v in one launch
             px.scatter_qkv(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
         out = px.attention()
         results[f"peer{rep}"] = rel_err(out, ref2[:, sl])
+    # the same through the wrapper's projections-in entry, whole and in two row pieces (as Flux's two streams arrive)
+    wrapper = B200ContextParallel(backend, world, cp_backend="ucp")
+    lq, lk, lv = (t[:, sl].contiguous().to(dev) for t in (xq, xk, xv))
+    out = wrapper.attention_from_projections(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
+    results["from_proj"] = rel_err(out, ref2[:, sl])
+    h = s // 2
+    args = pre.batch_args(s, grid)
+    first = wrapper.attention_from_projections(pre.jobs(lq[:, :h], lk[:, :h], wq.to(dev), wk.to(dev)), lv[:, :h],
+                                               row_offset=0, last=False, **args)
+    assert first is None
+    args2 = dict(args, pos_offset=args["pos_offset"] + h)
+    out = wrapper.attention_from_projections(pre.jobs(lq[:, h:], lk[:, h:], wq.to(dev), wk.to(dev)), lv[:, h:],
+                                             row_offset=h, last=True, **args2)
+    results["from_proj_pieces"] = rel_err(out, ref2[:, sl])
+    out = wrapper.attention_fused(produce_q=lambda: tq, produce_k=lambda: tk, produce_v=lambda: tv, num_heads=H)[0]
+    results["attention_fused"] = rel_err(out, ref2[:, sl])
     torch.cuda.synchronize()
     ops.check_status(dev)
     ok = all(e <= REL for e in results.values())
