@@ -11,7 +11,8 @@ import os
 from typing import Optional, Sequence
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libchitu_b200.so")
+# CHITU_B200_LIB points at another build of the same library (A/B measurements of kernel variants)
+LIB_PATH = os.environ.get("CHITU_B200_LIB") or os.path.join(_PKG_DIR, "libchitu_b200.so")
 
 OK, E_INVALID, E_UNSUPPORTED, E_CUDA = 0, -1, -2, -3
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2

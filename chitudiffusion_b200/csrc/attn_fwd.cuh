@@ -205,7 +205,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!wait_flag(p.in_flags + src, flag_epoch, p.flag_timeout, p.status)) *abort_flag = 1;
         src_ready |= 1u << src;
         // the rows were written by a peer's ordinary stores and are about to be read by the copy engine
-        asm volatile("fence.proxy.async.global;" ::: "memory");
+        #if CHITU_FLAG_VARIANT != 3
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+#endif
       }
     };
     if (lane == 0) {
@@ -224,7 +226,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (round > 0) mbar_wait(bar_kv_empty + 8 * slot, (round - 1) & 1, abort_flag, p.status, kDevTimeoutLoad);
       if (lane == 0) {
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
-        const int row = (kv0 + ((i >> 1) + rot) % n_kv) * kTileN;
+        const int rel = (i >> 1) + rot;  // tile of this item relative to kv0, wrapped without a division
+        const int row = (kv0 + (rel >= n_kv ? rel - n_kv : rel)) * kTileN;
         wait_rows(row, row + kTileN, p.Sk);
         const uint32_t dst = kv_smem + slot * kTileBytes;
         const uint32_t bar = bar_kv_full + 8 * slot;
@@ -367,6 +370,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #else
 #define TICK(acc)
 #endif
+      int jt = rot;                                // key tile of step j relative to kv0 (advanced without a division)
+      const int last_rel = n_kv_total - 1 - kv0;   // the tile whose tail may need masking
       for (int j = 0; j < n_kv; ++j) {
 #ifdef CHITU_ATTN_TIMING
         c0 = clock64();
@@ -377,7 +382,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // Row of 128 scores into registers, 32 columns per load; the load of chunk
         // c+1 is in flight while the running maximum of chunk c is taken.
         uint32_t s[4][32];
-        const bool last_tile = (kv0 + (j + rot) % n_kv == n_kv_total - 1 && tail_valid < kTileN);
+        const bool last_tile = (jt == last_rel && tail_valid < kTileN);
+        if (++jt == n_kv) jt = 0;
         float mx0 = -INFINITY, mx1 = -INFINITY;
         tmem_ld32(t_s, s[0]);
 #pragma unroll
@@ -464,7 +470,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         l_sum += (la.x + la.y) + (lb.x + lb.y);
       }
 #ifdef CHITU_ATTN_TIMING
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
+      if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
         p.dbg[t * 4 + 0] = tw; p.dbg[t * 4 + 1] = tl; p.dbg[t * 4 + 2] = tm; p.dbg[t * 4 + 3] = ts;
       }
 #endif

@@ -9,6 +9,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -51,7 +52,8 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 // Tensor map over a [B, S, H, 128] 16-bit tensor with element strides {b, s, h, 1}:
 // dims (innermost first) d, h, s, b; box = 64 x 1 x 128 x 1 with 128-byte swizzle,
 // i.e. one 128-row x 128-byte panel per copy; rows past S read as zero.
-int make_qkv_map(CUtensorMap* map, const void* base, int B, int S, int H, const int64_t* st, const char* name) {
+int make_qkv_map(CUtensorMap* map, const void* base, int B, int S, int H, const int64_t* st, const char* name,
+                 int box_rows = 128) {
   auto encode = get_encode_fn();
   if (!encode) return fail(CHITU_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
   if (reinterpret_cast<uintptr_t>(base) & 15) return fail(CHITU_E_INVALID, "%s: base must be 16-byte aligned", name);
@@ -68,7 +70,7 @@ int make_qkv_map(CUtensorMap* map, const void* base, int B, int S, int H, const 
   };
   cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {stride_bytes(2, H), stride_bytes(1, S), stride_bytes(0, B)};
-  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t elem[4] = {1, 1, 1, 1};
   CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

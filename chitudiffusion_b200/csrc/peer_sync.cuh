@@ -13,9 +13,11 @@
 //   [41]      attention / merge CTAs that have finished in the running launch (local)
 //   [42]      wait_epoch      layers whose outputs this rank has waited for    (local)
 //
-// Publishing uses the last-block pattern: every CTA orders its peer stores with a system-scope
-// fence and bumps the local counter; the CTA that sees the full count fences again and then writes
-// the new epoch into each peer's flag slot with a system-scope release store.  Every wait is a
+// Publishing uses the last-block pattern: every CTA orders its stores with a device-scope fence and
+// bumps the local counter; the CTA that sees the full count issues ONE system-scope fence - which is
+// cumulative over everything the counter chain made happen before it - and then writes the new
+// epoch into each peer's flag slot with a system-scope release store.  (A system-scope fence in
+// every CTA was measured to cost tens of microseconds per CTA while peer stores are in flight.)  Every wait is a
 // bounded acquire poll that records status 5 and returns when its clock budget runs out.
 #pragma once
 
@@ -49,7 +51,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __device__ __forceinline__ void publish_when_last(const PeerSync& ps, int done_slot, int epoch_slot, int flag_base,
                                                   unsigned total_ctas) {
   int* mine = ps.blocks[ps.rank];
-  __threadfence_system();
+  __threadfence();
   const unsigned prev = atomicAdd(reinterpret_cast<unsigned*>(mine + done_slot), 1u);
   if (prev + 1 == total_ctas) {
     __threadfence_system();
@@ -62,17 +64,33 @@ __device__ __forceinline__ void publish_when_last(const PeerSync& ps, int done_s
 
 // Bounded wait until `*flag` has reached `epoch` (wrap-safe).  Returns false on timeout after
 // recording status 5.
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Polls are relaxed loads with a short back-off (many CTAs may be polling the same word while a
+// peer is still writing rows into this GPU's memory); one acquire fence follows the successful poll.
+#ifndef CHITU_FLAG_VARIANT
+#define CHITU_FLAG_VARIANT 1
+#endif
 __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long long timeout_cycles, int* status) {
-  if (ld_acquire_sys(flag) - epoch >= 0) return true;
-  const long long t0 = clock64();
-  unsigned spins = 0;
-  while (true) {
-    if (ld_acquire_sys(flag) - epoch >= 0) return true;
-    if ((++spins & 0x3f) == 0 && clock64() - t0 > timeout_cycles) {
-      if (status) atomicCAS(status, 0, 5);
-      return false;
+#if CHITU_FLAG_VARIANT == 1
+#define CHITU_FLAG_LD ld_acquire_sys
+#else
+#define CHITU_FLAG_LD ld_relaxed_sys
+#endif
+  if (CHITU_FLAG_LD(flag) - epoch < 0) {
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (CHITU_FLAG_LD(flag) - epoch < 0) {
+      if ((++spins & 0x3f) == 0 && clock64() - t0 > timeout_cycles) {
+        if (status) atomicCAS(status, 0, 5);
+        return false;
+      }
     }
   }
+  return true;
 }
 
 // One warp: lane i waits for peer i's output flag of the next layer, then the epoch advances.
