@@ -239,21 +239,13 @@ class Pipeline:
         return self.pre(qp, kp, vp, self.nq, self.nk, self.w["grid"])
 
     def block(self, qp, kp, vp, timed=False):
-        if self.world > 1:
-            # norm + rotary + cast + head/sequence exchange + attention + exchange back: one call of the wrapper
-            return self.attn.attention_from_projections(
-                self.pre.jobs(qp, kp, self.nq, self.nk), vp,
-                **self.pre.batch_args(qp.shape[1], self.w.get("grid", (0, 0, 0))))
-        q, k, v = self.pre_local(qp, kp, vp)
-        if timed:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            out = self.attn(q, k, v)[0]
-            e1.record()
-            self.attn_events.append((e0, e1))
-        else:
-            out = self.attn(q, k, v)[0]
-        return out
+        # One call of the product API on one GPU as on many.  One GPU: k's norm + rotary pre-pass, then the
+        # attention kernel, which transforms q itself.  Several GPUs: norm + rotary + cast + head/sequence
+        # exchange + attention + exchange back.
+        self.backend.event_log = self.attn_events if (timed and self.world == 1) else None
+        return self.attn.attention_from_projections(
+            self.pre.jobs(qp, kp, self.nq, self.nk), vp,
+            **self.pre.batch_args(qp.shape[1], self.w.get("grid", (0, 0, 0))))
 
     def step(self, sets, timed=False):
         out = None
@@ -743,8 +735,19 @@ def run_ours(args):
         e2e_ms = e2e_timed(args.steps)
 
     library = None
+    pre_modes = None
     if world == 1 and not args.profile and args.attn == "b200":
         library = measure_library_sdpa(pipe, dev_sets, w, sync)
+        # the two placements of q's norm + rotary transform, same step, same inputs: inside the attention
+        # kernel against the pre-pass kernel doing q and k (the default: it is the faster one)
+        pre_modes = {}
+        for mode in ("fused", "prepass"):
+            os.environ["CHITU_B200_Q_PRELOAD"] = mode
+            pipe.step(dev_sets)
+            pre_modes["q_in_attention_kernel_ms_per_step" if mode == "fused" else "q_in_pre_pass_ms_per_step"] = round(
+                timed_region(lambda: pipe.step(dev_sets), args.steps) / args.steps, 4)
+        os.environ["CHITU_B200_Q_PRELOAD"] = "prepass"
+        pre_modes["default"] = "q_in_pre_pass"
 
     extra = None
     also = []
@@ -840,6 +843,8 @@ def run_ours(args):
         line["parity_limit"] = PARITY_LIMIT
     if library is not None:
         line["library_sdpa"] = library
+    if pre_modes is not None:
+        line["pre_attention_placement"] = pre_modes
     if dit:
         line["dit_step"] = dit
     if nvlink:

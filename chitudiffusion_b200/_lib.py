@@ -31,6 +31,7 @@ EXPORTS = (
     "chitu_b200_set_flag_wait_cycles",
     "chitu_b200_qk_norm_rope_batch_signal",
     "chitu_b200_attn_fwd_exchange",
+    "chitu_b200_attn_fwd_qpre",
     "chitu_b200_peer_wait_outputs",
     "chitu_b200_attn_splitkv_workspace_bytes",
     "chitu_b200_attn_fwd_splitkv",
@@ -61,7 +62,7 @@ class NormRopeJob(ctypes.Structure):
     _fields_ = [
         ("x", ctypes.c_void_p), ("x_row_stride", ctypes.c_int64), ("weight", ctypes.c_void_p),
         ("norm_mode", ctypes.c_int), ("rope_mode", ctypes.c_int), ("out", ctypes.c_void_p),
-        ("out_ptrs", ctypes.POINTER(ctypes.c_void_p)), ("n_out_ptrs", ctypes.c_int),
+        ("out_ptrs", ctypes.POINTER(ctypes.c_void_p)), ("n_out_ptrs", ctypes.c_int), ("rstd_out", ctypes.c_void_p),
     ]
 
 
@@ -69,6 +70,17 @@ class PeerSyncDesc(ctypes.Structure):
     """Mirror of ``chitu_b200_peer_sync``."""
 
     _fields_ = [("blocks", ctypes.POINTER(ctypes.c_void_p)), ("rank", ctypes.c_int), ("world", ctypes.c_int)]
+
+
+class QPre(ctypes.Structure):
+    """Mirror of ``chitu_b200_q_pre``."""
+
+    _fields_ = [
+        ("norm_mode", ctypes.c_int), ("rope_mode", ctypes.c_int), ("round_mid", ctypes.c_int), ("w_dtype", ctypes.c_int),
+        ("weight", ctypes.c_void_p), ("rstd", ctypes.c_void_p), ("eps", ctypes.c_float), ("rope_table", ctypes.c_void_p),
+        ("table_rows", ctypes.c_int), ("gf", ctypes.c_int), ("gh", ctypes.c_int), ("gw", ctypes.c_int),
+        ("n_t", ctypes.c_int), ("n_h", ctypes.c_int), ("pos_offset", ctypes.c_int64),
+    ]
 
 
 SYNC_INTS = 64
@@ -180,6 +192,13 @@ def load() -> ctypes.CDLL:
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int,
         ctypes.POINTER(PeerSyncDesc), _vp, _vp,
+    ]
+    lib.chitu_b200_attn_fwd_qpre.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_qpre.argtypes = [
+        _vp, _vp, _vp, _vp, _vp,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.POINTER(QPre), ctypes.c_int, _vp, ctypes.c_int64,
+        _vp, _vp,
     ]
     lib.chitu_b200_peer_wait_outputs.restype = ctypes.c_int
     lib.chitu_b200_peer_wait_outputs.argtypes = [ctypes.POINTER(PeerSyncDesc), _vp, _vp]

@@ -370,12 +370,9 @@ class B200ContextParallel:
             out = px.attention(softmax_scale)
             ops.poll_status(x0.device)
             return out
-        q, k, v = (torch.empty((B, s_total, num_heads, D), dtype=dtype, device=x0.device) for _ in range(3))
-        for jb, vp, off, args in pieces:
-            n = jb[0]["x"].shape[1]
-            jj = [dict(j, out=t[:, off:off + n]) for j, t in zip(jb, (q, k))]
-            ops.qk_norm_rope_batch(jj, out_strides=(s_total * C, C, 0, D), heads_per_group=num_heads, **args)
-            v[:, off:off + n].copy_(vp.reshape(B, n, num_heads, D))
+        from .pre_attention import transform_pieces
+
+        q, k, v = transform_pieces(pieces, dtype)
         return self(q, k, v, softmax_scale=softmax_scale)[0]
 
     # ------------------------------------------------------------------ producer-callback form

@@ -20,6 +20,7 @@
 // complete and O may be touched.
 #pragma once
 
+#include "elementwise.cuh"
 #include "peer_sync.cuh"
 #include "ptx.cuh"
 
@@ -76,6 +77,19 @@ struct AttnParams {
   long long flag_timeout;
   PeerSync sync;
   int signal_out;
+  // Pre-attention transform of Q inside the kernel (q_norm_mode != 2 or q_rope_mode != 0): q is the RAW
+  // projection output.  Once a query tile has landed in shared memory, the softmax warps - idle until
+  // the first scores arrive - apply RMSNorm, weight, rotary embedding and the 16-bit rounding to it in
+  // place, with exactly the arithmetic (and summation order) of qk_norm_rope_kernel, and only then is
+  // the MMA warp released.  Modes as in NormRopeParams, except norm mode 0: the full-width statistic
+  // cannot be formed from one head, so the caller passes rstd[b * Sq + s] computed elsewhere.
+  int q_norm_mode, q_rope_mode, q_round_mid, q_w_dtype;
+  const void* q_weight;   // [128] (mode 1) or [H * 128] (mode 0), or nullptr
+  const float* q_rstd;    // [B, Sq] fp32 (mode 0)
+  float q_eps;
+  const float2* q_table;  // (cos, sin) pairs, [rows][64]
+  int q_table_rows, q_gf, q_gh, q_gw, q_n_t, q_n_h;
+  long long q_pos_offset;
 #ifdef CHITU_ATTN_TIMING
   long long* dbg;   // per-phase clock totals of CTA 0 (development builds only)
 #endif
@@ -116,6 +130,119 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   return r;
 }
 
+// The four softmax warps of a query tile rewrite it in shared memory.  As in the pre-pass kernel a
+// thread owns one 8-value vector (16 threads per row, so a warp works on two rows at a time and the
+// tile takes 16 rounds); the sum of squares is the same 16-lane butterfly, so the numbers match the
+// pre-pass bit for bit.  Rotary factors and weights do not depend on the tile's data: they are
+// fetched (coalesced) BEFORE waiting for the tile, so their latency hides behind the tile copy.
+template <bool kFp16, typename WaitFn>
+__device__ __forceinline__ void transform_q_tile(uint8_t* tile, int warp_in_tile, int lane, int head, int batch,
+                                                 int row0, const AttnParams& p, WaitFn wait_for_tile) {
+  constexpr int kIn = kFp16 ? kFP16 : kBF16;
+  constexpr int kRounds = kTileM / 8;  // 4 warps x 2 rows per round
+  const int sub = lane >> 4;   // which of the warp's two rows
+  const int l16 = lane & 15;   // vector inside the row: channels [8 l16, 8 l16 + 8)
+  const int panel = l16 >> 3, chunk = l16 & 7;
+  const bool normed = p.q_norm_mode != 2;
+  const int round = !normed || !p.q_round_mid ? 0 : ((p.q_weight != nullptr && p.q_w_dtype != kFP32) ? 2 : 1);
+  float wgt[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) wgt[e] = 1.f;
+  if (normed && p.q_weight != nullptr) {
+    const int w0 = (p.q_norm_mode == 0 ? head * kHeadDim : 0) + l16 * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wgt[e] = ld_as_float(p.q_weight, p.q_w_dtype, w0 + e);
+  }
+  // rotary factors (4 pairs per vector) and full-width factors of this thread's 16 rows
+  float4 cs[kRounds][2];
+  float rstd_row[kRounds];
+  unsigned rotate_mask = 0;
+  const long long grid_tokens = static_cast<long long>(p.q_gf) * p.q_gh * p.q_gw;
+#pragma unroll
+  for (int it = 0; it < kRounds; ++it) {
+    const int r = it * 8 + warp_in_tile * 2 + sub;
+    const int row = row0 + r;
+    const long long n = p.q_pos_offset + row;
+    rstd_row[it] = 1.f;
+    if (p.q_norm_mode == 0) rstd_row[it] = __ldg(&p.q_rstd[static_cast<size_t>(batch) * p.Sq + min(row, p.Sq - 1)]);
+    cs[it][0] = cs[it][1] = make_float4(1.f, 0.f, 1.f, 0.f);
+    if (p.q_rope_mode == 2) {
+      if (n < p.q_table_rows) {
+        rotate_mask |= 1u << it;
+        const float4* trow = reinterpret_cast<const float4*>(p.q_table + n * (kHeadDim / 2) + l16 * 4);
+        cs[it][0] = __ldg(trow);
+        cs[it][1] = __ldg(trow + 1);
+      }
+    } else if (p.q_rope_mode == 1) {
+      if (n < grid_tokens) {
+        rotate_mask |= 1u << it;
+        const int ni = static_cast<int>(n);
+        const int r2 = ni / p.q_gw;
+        const int pw = ni - r2 * p.q_gw;
+        const int pf = r2 / p.q_gh;
+        const int ph = r2 - pf * p.q_gh;
+        float2 f[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int j = l16 * 4 + q;
+          const int trow = (j < p.q_n_t) ? pf : ((j < p.q_n_t + p.q_n_h) ? ph : pw);
+          f[q] = __ldg(&p.q_table[trow * (kHeadDim / 2) + j]);
+        }
+        cs[it][0] = make_float4(f[0].x, f[0].y, f[1].x, f[1].y);
+        cs[it][1] = make_float4(f[2].x, f[2].y, f[3].x, f[3].y);
+      }
+    }
+  }
+  wait_for_tile();
+#pragma unroll
+  for (int it = 0; it < kRounds; ++it) {
+    const int r = it * 8 + warp_in_tile * 2 + sub;
+    uint8_t* addr = tile + panel * kHalfTileBytes + r * 128 + ((chunk ^ (r & 7)) << 4);
+    RawVec8<kIn> raw;
+    raw.a = *reinterpret_cast<const uint4*>(addr);
+    float v[8];
+    unpack8<kIn>(raw, v);
+    float rstd = rstd_row[it];
+    if (p.q_norm_mode == 1) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      rstd = rsqrtf(ss * (1.0f / kHeadDim) + p.q_eps);
+    }
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float t = v[e];
+      if (normed) {
+        t *= rstd;
+        if (round >= 1) t = round_to(t, kIn);
+        t *= wgt[e];
+        if (round == 2) t = round_to(t, p.q_w_dtype);
+      }
+      y[e] = t;
+    }
+    if ((rotate_mask >> it) & 1u) {
+      const float rc[4] = {cs[it][0].x, cs[it][0].z, cs[it][1].x, cs[it][1].z};
+      const float rs[4] = {cs[it][0].y, cs[it][0].w, cs[it][1].y, cs[it][1].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float re = y[2 * q] * rc[q] - y[2 * q + 1] * rs[q];
+        const float im = y[2 * q] * rs[q] + y[2 * q + 1] * rc[q];
+        y[2 * q] = re;
+        y[2 * q + 1] = im;
+      }
+    }
+    uint4 o;
+    o.x = pack16(y[0], y[1], kIn);
+    o.y = pack16(y[2], y[3], kIn);
+    o.z = pack16(y[4], y[5], kIn);
+    o.w = pack16(y[6], y[7], kIn);
+    *reinterpret_cast<uint4*>(addr) = o;
+  }
+}
+
 template <bool kFp16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -138,6 +265,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
   const uint32_t bar_drain = smem_u32(tail + 16);  // only used when a wait has run out (see the MMA warp's exit)
+  const uint32_t bar_q_ready = smem_u32(tail + 24);  // [2] a query tile has been transformed in place (128 arrivals)
+  const bool q_fuse = p.q_norm_mode != 2 || p.q_rope_mode != 0;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -173,6 +302,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_o_final + 8 * t, 1);
     }
     mbar_init(bar_drain, 1);
+    mbar_init(bar_q_ready, kTileM);
+    mbar_init(bar_q_ready + 8, kTileM);
     mbar_fence_init();
   }
   if (warp == 8) {
@@ -288,7 +419,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_wait(bar_kv_full + 8 * (i % kStages), (i / kStages) & 1, abort_flag, p.status, kDevTimeoutMma);
     };
 
-    mbar_wait(bar_q_full, 0, abort_flag, p.status, kDevTimeoutMma);
+    mbar_wait(q_fuse ? bar_q_ready : bar_q_full, 0, abort_flag, p.status, kDevTimeoutMma);
     wait_item(0);
     tc_fence_after_sync();
     if (leader) {
@@ -297,7 +428,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     __syncwarp();
     if (n_qt > 1) {
-      mbar_wait(bar_q_full + 8, 0, abort_flag, p.status, kDevTimeoutMma);
+      mbar_wait((q_fuse ? bar_q_ready : bar_q_full) + 8, 0, abort_flag, p.status, kDevTimeoutMma);
       tc_fence_after_sync();
       if (leader) {
         issue_qk(1, 0);
@@ -359,6 +490,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
       const uint32_t t_s = tmem_base + lane_base + t * kTileN;
       const uint32_t t_o = tmem_base + lane_base + 2 * kTileN + t * kHeadDim;
+      if (q_fuse) {
+        // this tile's four warps: fetch rotary factors, wait for the tile, rewrite it, hand it to the MMA warp
+#ifdef CHITU_ATTN_TIMING
+        long long qt0 = clock64(), qt1 = 0;
+#endif
+        transform_q_tile<kFp16>(smem_gen + t * kTileBytes, quad, lane, head, batch, q0 + t * kTileM, p, [&] {
+#ifdef CHITU_ATTN_TIMING
+          qt1 = clock64();
+#endif
+          mbar_wait(bar_q_full + 8 * t, 0, abort_flag, p.status, kDevTimeoutSoftmax);
+#ifdef CHITU_ATTN_TIMING
+          if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+            p.dbg[24] = qt1 - qt0;
+            p.dbg[25] = clock64() - qt1;
+            qt1 = clock64();
+          }
+#endif
+        });
+        fence_proxy_async_smem();  // the rewritten tile is read by the tensor core through the async proxy
+        mbar_arrive(bar_q_ready + 8 * t);
+#ifdef CHITU_ATTN_TIMING
+        if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0)
+          p.dbg[26] = clock64() - qt1;
+#endif
+      }
       const float sl2 = p.scale_log2;
       const int tail_valid = p.Sk - (n_kv_total - 1) * kTileN;  // 1..128 valid keys in the last tile of K
       float m_used = -INFINITY;

@@ -186,7 +186,8 @@ int64_t splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits) {
 int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const OutScatter& sc, float* lse, int B,
                   int Sq, int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
                   const int64_t* v_strides, float softmax_scale, int dtype, int* status, void* stream,
-                  const KeySplit& ks = KeySplit{}, const Exchange& ex = Exchange{}) {
+                  const KeySplit& ks = KeySplit{}, const Exchange& ex = Exchange{},
+                  const chitu_b200_q_pre* qpre = nullptr) {
   if (!q || !k || !v || (!out && sc.n_dest == 0) || !q_strides || !k_strides || !v_strides)
     return fail(CHITU_E_INVALID, "attn_fwd: null pointer argument");
   if (sc.n_dest != 0) {
@@ -247,6 +248,50 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   p.tiles_per_split = tiles_per_split;
   p.part_o = static_cast<float*>(ks.workspace);
   p.part_lse = p.part_o ? p.part_o + static_cast<size_t>(n_splits) * B * Sq * H * D : nullptr;
+  p.q_norm_mode = 2;
+  p.q_rope_mode = 0;
+  p.q_round_mid = 0;
+  p.q_w_dtype = CHITU_DTYPE_FP32;
+  p.q_weight = nullptr;
+  p.q_rstd = nullptr;
+  p.q_eps = 0.f;
+  p.q_table = nullptr;
+  p.q_table_rows = p.q_gf = p.q_gh = p.q_gw = p.q_n_t = p.q_n_h = 0;
+  p.q_pos_offset = 0;
+  if (qpre != nullptr) {
+    if (qpre->norm_mode < 0 || qpre->norm_mode > 2 || qpre->rope_mode < 0 || qpre->rope_mode > 2)
+      return fail(CHITU_E_INVALID, "attn_fwd_qpre: bad mode");
+    if (qpre->norm_mode == 0 && !qpre->rstd)
+      return fail(CHITU_E_INVALID, "attn_fwd_qpre: full-width norm needs the per-token rstd vector");
+    if (qpre->w_dtype < 0 || qpre->w_dtype > 2) return fail(CHITU_E_INVALID, "attn_fwd_qpre: bad weight dtype");
+    if (qpre->rope_mode != 0) {
+      if (!qpre->rope_table || qpre->table_rows <= 0) return fail(CHITU_E_INVALID, "attn_fwd_qpre: rope table missing");
+      if (qpre->pos_offset < 0 || qpre->pos_offset + Sq >= (1LL << 31))
+        return fail(CHITU_E_UNSUPPORTED, "attn_fwd_qpre: positions must stay below 2^31");
+      if (qpre->rope_mode == 1) {
+        if (qpre->gf <= 0 || qpre->gh <= 0 || qpre->gw <= 0 || qpre->n_t < 0 || qpre->n_h < 0 ||
+            qpre->n_t + qpre->n_h > D / 2)
+          return fail(CHITU_E_INVALID, "attn_fwd_qpre: grid / axis split out of range");
+        if (qpre->gf > qpre->table_rows || qpre->gh > qpre->table_rows || qpre->gw > qpre->table_rows)
+          return fail(CHITU_E_INVALID, "attn_fwd_qpre: rope table has fewer rows than the grid extent");
+      }
+    }
+    p.q_norm_mode = qpre->norm_mode;
+    p.q_rope_mode = qpre->rope_mode;
+    p.q_round_mid = qpre->round_mid;
+    p.q_w_dtype = qpre->w_dtype;
+    p.q_weight = qpre->weight;
+    p.q_rstd = qpre->rstd;
+    p.q_eps = qpre->eps;
+    p.q_table = reinterpret_cast<const float2*>(qpre->rope_table);
+    p.q_table_rows = qpre->table_rows;
+    p.q_gf = qpre->gf;
+    p.q_gh = qpre->gh;
+    p.q_gw = qpre->gw;
+    p.q_n_t = qpre->n_t;
+    p.q_n_h = qpre->n_h;
+    p.q_pos_offset = qpre->pos_offset;
+  }
   p.in_flags = nullptr;
   p.in_epoch = nullptr;
   p.rows_per_src = p.local_src = 0;
@@ -388,6 +433,19 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
                        dtype, status, stream, ks, ex);
 }
 
+int chitu_b200_attn_fwd_qpre(const void* q_raw, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                             int H, int D, const int64_t* q_strides, const int64_t* k_strides,
+                             const int64_t* v_strides, float softmax_scale, int dtype, const chitu_b200_q_pre* q_pre,
+                             int n_splits, void* workspace, int64_t workspace_bytes, int* status, void* stream) {
+  if (!q_pre) return fail(CHITU_E_INVALID, "attn_fwd_qpre: transform descriptor missing");
+  KeySplit ks;
+  ks.n_splits = n_splits;
+  ks.workspace = workspace;
+  ks.workspace_bytes = workspace_bytes;
+  return attn_fwd_impl(q_raw, k, v, out, OutScatter{}, lse, B, Sq, Sk, H, D, q_strides, k_strides, v_strides,
+                       softmax_scale, dtype, status, stream, ks, Exchange{}, q_pre);
+}
+
 int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, void* stream) {
   chitu::PeerSync ps;
   int rc = fill_peer_sync(&ps, sync, "peer_wait_outputs");
@@ -469,7 +527,10 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
   for (int j = 0; j < n_jobs; ++j) {
     const chitu_b200_norm_rope_job& jb = jobs[j];
     chitu::NormRopeParams& p = batch.job[j];
-    if (!jb.x || (!jb.out && jb.n_out_ptrs == 0)) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+    if (!jb.x || (!jb.out && jb.n_out_ptrs == 0 && !jb.rstd_out))
+      return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
+    if (jb.rstd_out && jb.norm_mode != 0)
+      return fail(CHITU_E_INVALID, "qk_norm_rope: a statistics-only job needs norm_mode 0");
     if (jb.n_out_ptrs != 0) {
       if (jb.n_out_ptrs < 0 || jb.n_out_ptrs > 8 || !jb.out_ptrs || jb.n_out_ptrs * sh.heads_per_group != H)
         return fail(CHITU_E_INVALID, "qk_norm_rope: need one destination per head group (at most 8)");
@@ -530,6 +591,7 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
     p.round_mid = sh.round_mid;
     p.n_out_ptrs = jb.n_out_ptrs;
     for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < jb.n_out_ptrs ? jb.out_ptrs[i] : nullptr;
+    p.rstd_out = jb.rstd_out;
   }
   // one 8-channel vector per thread, whole warps; the grid fills the 148 SMs a few CTAs deep
   const int threads = static_cast<int>(((C / 8) + 31) / 32 * 32);
@@ -592,6 +654,7 @@ int qk_norm_rope_impl(const void* x, int in_dtype, int64_t x_row_stride, const v
   job.out = out;
   job.out_ptrs = out_ptrs;
   job.n_out_ptrs = n_out_ptrs;
+  job.rstd_out = nullptr;
   NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
                     out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
   return qk_norm_rope_batch_impl(&job, 1, sh, stream);

@@ -201,6 +201,10 @@ struct NormRopeParams {
   // buffer) instead of out + g * os_g.
   void* out_ptrs[8];
   int n_out_ptrs;
+  // Statistics-only job (norm_mode 0): when rstd_out is set the job writes rstd_out[b * S + s] =
+  // rsqrt(mean_C(x^2) + eps) - the factor the attention kernel needs to normalise q in place - and
+  // stores nothing else.
+  float* rstd_out;
 };
 
 constexpr int kNormMaxThreads = 1024;  // one 8-channel vector per thread: up to 8192 channels per token
@@ -359,6 +363,18 @@ __device__ __forceinline__ void qk_norm_rope_job(const NormRopeParams& p, float 
       pw = n - row * p.gw;
       pf = row / p.gh;
       ph = row - pf * p.gh;
+    }
+    if constexpr (kNormMode == 0) {
+      if (p.rstd_out != nullptr) {
+        if (threadIdx.x == 0) {
+#pragma unroll
+          for (int i = 0; i < kTok; ++i)
+            if (base + i < tokens) p.rstd_out[base + i] = rstd_full[i];
+        }
+#pragma unroll
+        for (int i = 0; i < kTok; ++i) cur[i] = nxt[i];
+        continue;
+      }
     }
 #pragma unroll
     for (int i = 0; i < kTok; ++i) {

@@ -158,11 +158,15 @@ def attn_fwd(
     out: Optional[torch.Tensor] = None,
     n_splits: Optional[int] = None,
     workspace: Optional[torch.Tensor] = None,
+    q_pre: Optional[dict] = None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """``softmax(scale * q k^T) v`` for ``[B,S,H,128]`` bf16/fp16 tensors of any (16-byte aligned) strides.
 
     Returns ``(out [B,Sq,H,D] contiguous, lse [B,H,Sq] fp32 | None)``.  ``workspace`` is an optional
-    caller-owned uint8 scratch for the key-split partials (see :func:`splitkv_workspace`).
+    caller-owned uint8 scratch for the key-split partials (see :func:`splitkv_workspace`).  With ``q_pre``
+    (keys ``norm_mode, rope_mode, weight, rstd, eps, rope_table, grid, axis_split, pos_offset, round_mid``)
+    ``q`` is the raw projection and its pre-attention transform runs inside the kernel
+    (``chitu_b200_attn_fwd_qpre``).
     """
     _require_cuda(q, k, v)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
@@ -189,6 +193,35 @@ def attn_fwd(
     lib = _lib.load()
     if n_splits is None:
         n_splits = auto_key_splits(B, Sq, Sk, H)
+    if q_pre is not None:
+        import ctypes
+
+        w, rstd, table = q_pre.get("weight"), q_pre.get("rstd"), q_pre.get("rope_table")
+        _require_cuda(w, rstd, table)
+        if w is not None:
+            w = w.contiguous()
+        grid = q_pre.get("grid", (0, 0, 0))
+        split = q_pre.get("axis_split", (0, 0))
+        desc = _lib.QPre(
+            int(q_pre.get("norm_mode", 2)), int(q_pre.get("rope_mode", 0)), 1 if q_pre.get("round_mid", True) else 0,
+            _DTYPES[w.dtype] if w is not None else _lib.DTYPE_FP32, w.data_ptr() if w is not None else None,
+            rstd.data_ptr() if rstd is not None else None, float(q_pre.get("eps", 1e-6)),
+            table.data_ptr() if table is not None else None, int(table.shape[0]) if table is not None else 0,
+            int(grid[0]), int(grid[1]), int(grid[2]), int(split[0]), int(split[1]), int(q_pre.get("pos_offset", 0)))
+        ws_ptr, ws_bytes = None, 0
+        if n_splits > 1:
+            need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
+            ws = workspace if workspace is not None else splitkv_workspace(q.device, need)
+            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+        with torch.cuda.device(q.device):
+            rc = lib.chitu_b200_attn_fwd_qpre(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+                B, Sq, Sk, H, D, _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()),
+                scale, _DTYPES[q.dtype], ctypes.byref(desc), int(n_splits), ws_ptr, ws_bytes,
+                status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        _lib.check(rc, "attn_fwd_qpre")
+        _launched(2 if n_splits > 1 and Sk > 128 else 1)
+        return out, lse
     with torch.cuda.device(q.device):
         if n_splits > 1:
             need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, D, n_splits))
@@ -407,8 +440,14 @@ def qk_norm_rope_batch(
             if w_dtype is not None and w.dtype != w_dtype:
                 raise ValueError("batched pre-attention jobs must share the weight dtype")
             w_dtype = w.dtype
-        out, ptrs = jb.get("out"), jb.get("out_ptrs")
-        if ptrs is None and out is None:
+        out, ptrs, rstd = jb.get("out"), jb.get("out_ptrs"), jb.get("rstd_out")
+        if rstd is not None:
+            if rstd.dtype != torch.float32 or rstd.numel() != B * S or not rstd.is_contiguous():
+                raise ValueError("rstd_out must be a contiguous fp32 tensor of B*S elements")
+            out = ptrs = None
+            keep.append(rstd)
+        arr[i].rstd_out = rstd.data_ptr() if rstd is not None else None
+        if ptrs is None and out is None and rstd is None:
             if out_strides is not None:
                 raise ValueError("explicit out_strides need out or out_ptrs in every job")
             out = torch.empty((B, S, num_heads, D), dtype=out_dtype, device=x.device)

@@ -150,3 +150,34 @@ class JointPreAttention:
         if v.dtype not in (torch.bfloat16, torch.float16):
             v = v.to(torch.bfloat16)
         return q, k, v
+
+
+def transform_pieces(pieces, dtype: torch.dtype = torch.bfloat16):
+    """Run the pre-attention jobs of a layer given in row pieces and return contiguous ``(q, k, v)``.
+
+    ``pieces`` is a list of ``(jobs, v_proj, row_offset, batch_args)`` as collected by the
+    ``attention_from_projections`` entries: each piece is transformed straight into its rows of the
+    joint ``[B, S, H, D]`` tensors (one launch per piece).
+    """
+    x0 = pieces[0][0][0]["x"]
+    B, _, C = x0.shape
+    H = int(pieces[0][3]["num_heads"])
+    D = C // H
+    S = max(off + jb[0]["x"].shape[1] for jb, _, off, _ in pieces)
+    if len(pieces) == 1 and pieces[0][2] == 0 and pieces[0][1].dtype == dtype:
+        # one piece covering every row: v needs no copy, the attention kernel reads the projection view
+        jb, vp, _, args = pieces[0]
+        args = {key: val for key, val in args.items() if key != "out_dtype"}
+        q, k = ops.qk_norm_rope_batch(jb, out_dtype=dtype, **args)
+        return q, k, (vp.unflatten(2, (H, D)) if vp.dim() == 3 else vp)
+    q, k, v = (torch.empty((B, S, H, D), dtype=dtype, device=x0.device) for _ in range(3))
+    for jb, vp, off, args in pieces:
+        n = jb[0]["x"].shape[1]
+        args = {key: val for key, val in args.items() if key != "out_dtype"}
+        jobs = [dict(j, out=t[:, off:off + n]) for j, t in zip(jb, (q, k))]
+        if vp.dtype == x0.dtype:
+            jobs.append(dict(x=vp.reshape(B, n, C), norm_mode=2, rope_mode=0, out=v[:, off:off + n]))
+        else:
+            v[:, off:off + n].copy_(vp.reshape(B, n, H, D))
+        ops.qk_norm_rope_batch(jobs, out_strides=(S * C, C, 0, D), heads_per_group=H, out_dtype=dtype, **args)
+    return q, k, v

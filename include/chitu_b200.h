@@ -112,6 +112,39 @@ int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, const void*
                                        int dtype, int n_splits, int* status, void* stream);
 
 /*
+ * Attention whose QUERY pre-attention transform runs inside the kernel: q_raw is the projection output
+ * ([B, Sq, H, 128], strides as for chitu_b200_attn_fwd); once a query tile has landed in shared memory the
+ * kernel applies RMSNorm, weight, rotary embedding and the 16-bit rounding to it in place - the arithmetic
+ * and summation order of chitu_b200_qk_norm_rope, so the result equals transforming q with that call first
+ * - and only then starts the tensor-core work.  The q half of the pre-pass (one read and one write of q)
+ * disappears; k still goes through chitu_b200_qk_norm_rope, because every query block of a head re-reads
+ * every key tile and would repeat its transform.  Replaces the q chain of WanSelfAttention.forward
+ * (chitu_diffusion/models/model_wan.py:152-153,194-195,198) and of the Flux / Qwen processors
+ * (chitu_diffusion/modules/attention/flux_attention.py:139-151) together with the attention call.
+ *
+ *   norm_mode   1 = per-head RMSNorm over the 128 channels (weight: [128] or NULL);
+ *               0 = full-width RMSNorm whose per-token factor the caller supplies: rstd[b * Sq + s] fp32
+ *                   (one head cannot form a statistic over all heads; weight: [H * 128] or NULL);
+ *               2 = none
+ *   rope_mode, rope_table, table_rows, gf, gh, gw, n_t, n_h, pos_offset, round_mid, eps, w_dtype:
+ *               as in chitu_b200_qk_norm_rope (n_t, n_h = its axis_split)
+ *   n_splits, workspace: as in chitu_b200_attn_fwd_splitkv (1 and NULL for no key split)
+ */
+typedef struct {
+  int norm_mode, rope_mode, round_mid, w_dtype;
+  const void* weight;
+  const float* rstd;
+  float eps;
+  const float* rope_table;
+  int table_rows, gf, gh, gw, n_t, n_h;
+  int64_t pos_offset;
+} chitu_b200_q_pre;
+int chitu_b200_attn_fwd_qpre(const void* q_raw, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                             int H, int D, const int64_t* q_strides, const int64_t* k_strides,
+                             const int64_t* v_strides, float softmax_scale, int dtype, const chitu_b200_q_pre* q_pre,
+                             int n_splits, void* workspace, int64_t workspace_bytes, int* status, void* stream);
+
+/*
  * Quantised attention: per-block INT8 Q K^T, E4M3 P V, fp32 accumulation, 16-bit output.
  * Stands in for the SageAttention backend call sageattn(q, k, v, tensor_layout="NHD", ...)
  * (chitu_diffusion/modules/attention/diffusion_attn_backend.py:242-268).  The call runs the
@@ -193,6 +226,8 @@ typedef struct {
   void* out;
   void* const* out_ptrs;
   int n_out_ptrs;
+  float* rstd_out; /* NULL, or (norm_mode 0): write only rstd_out[b * S + s] = rsqrt(mean_C(x^2) + eps), the factor
+                      chitu_b200_attn_fwd_qpre takes for q; nothing else is stored by this job */
 } chitu_b200_norm_rope_job;
 int chitu_b200_qk_norm_rope_batch(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
                                   float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,

@@ -288,3 +288,48 @@ def test_two_devices_in_one_process(backend):
         out = backend(q.to(dev), k.to(dev), v.to(dev))[0]
         torch.cuda.synchronize(dev)
         _check(out, ref)
+
+
+def test_query_transform_inside_the_kernel_equals_the_pre_pass(backend):
+    """q normalised / rotated / rounded in shared memory by the attention kernel gives bit-for-bit the result of
+    running the pre-pass kernel on q first: per-head norm + per-token rotary table (Flux / Qwen form), and
+    full-width norm (factor from a statistics-only job) + three-axis rotary (Wan form)."""
+    from chitudiffusion_b200 import ops, pre_attention
+
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(91)
+    H, D = 3, 128
+    C = H * D
+    # Flux form: ragged length, strided views of a fused qkv projection, learned per-head weights
+    S = 333
+    qkv = _rand((2, S, 3 * C), torch.bfloat16, gen, 0.7).to(dev)
+    ids = torch.stack([torch.zeros(S, dtype=torch.long), torch.arange(S) // 19, torch.arange(S) % 19], 1)
+    table = pre_attention.axis_rope_table(ids, (16, 56, 56)).to(dev)
+    wq = (1.0 + 0.1 * torch.randn(D, generator=gen)).to(dev)
+    wk = (1.0 + 0.1 * torch.randn(D, generator=gen)).to(dev)
+    pre = pre_attention.JointPreAttention(H, D, table)
+    jobs = pre.jobs(qkv[..., :C], qkv[..., C:2 * C], wq, wk)
+    backend.q_in_kernel = True
+    fused = backend.attention_from_projections(jobs, qkv[..., 2 * C:], **pre.batch_args())
+    q, k, v = pre(qkv[..., :C], qkv[..., C:2 * C], qkv[..., 2 * C:], wq, wk)
+    plain = backend(q, k, v)[0]
+    assert torch.equal(fused, plain)
+    ref = oracle.sdpa_fp32(q.cpu(), k.cpu(), v.cpu())
+    _check(fused, ref)
+    # Wan form: full-width statistics, grid rotary, fp32 weights with the intermediate rounding of the reference
+    grid = (3, 10, 13)
+    S = grid[0] * grid[1] * grid[2] + 5  # five padding tokens past the grid pass through unrotated
+    qkv = _rand((1, S, 3 * C), torch.bfloat16, gen, 0.7).to(dev)
+    nq = (1.0 + 0.1 * torch.randn(C, generator=gen)).to(dev)
+    nk = (1.0 + 0.1 * torch.randn(C, generator=gen)).to(dev)
+    wan = pre_attention.WanPreAttention(H, D, device=dev)
+    fused = backend.attention_from_projections(wan.jobs(qkv[..., :C], qkv[..., C:2 * C], nq, nk), qkv[..., 2 * C:],
+                                               **wan.batch_args(S, grid))
+    q, k, v = wan(qkv[..., :C], qkv[..., C:2 * C], qkv[..., 2 * C:], nq, nk, grid)
+    plain = backend(q, k, v)[0]
+    assert torch.equal(fused, plain)
+    backend.q_in_kernel = False
+    default = backend.attention_from_projections(wan.jobs(qkv[..., :C], qkv[..., C:2 * C], nq, nk), qkv[..., 2 * C:],
+                                                 **wan.batch_args(S, grid))
+    assert torch.equal(default, plain)
+    ops.check_status(dev)
