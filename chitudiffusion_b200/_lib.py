@@ -191,6 +191,7 @@ def load() -> ctypes.CDLL:
         _vp, _vp, _vp, _vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int,
+        ctypes.c_int, _vpp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
         ctypes.POINTER(PeerSyncDesc), _vp, _vp,
     ]
     lib.chitu_b200_attn_fwd_qpre.restype = ctypes.c_int

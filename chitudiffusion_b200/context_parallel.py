@@ -245,15 +245,16 @@ class B200ContextParallel:
                 g.p2p_wait()
         return nk, nv, done
 
-    def peer_exchange(self, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device):
+    def peer_exchange(self, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device,
+                      prefix_rows: int = 0):
         """Cached peer-store exchange for one problem shape (collective on first use: every rank must call it)."""
         from .peer import PeerUlysses
 
-        key = (B, s, H, D, dtype, str(device))
+        key = (B, s, H, D, dtype, str(device), prefix_rows)
         px = self._peer_cache.get(key)
         if px is None:
             u, _ = self._split()
-            px = PeerUlysses(self._up_group_lookup(u), B, s, H, D, dtype, device)
+            px = PeerUlysses(self._up_group_lookup(u), B, s, H, D, dtype, device, prefix_rows=prefix_rows)
             self._peer_cache[key] = px
         return px
 
@@ -458,6 +459,22 @@ class B200ContextParallel:
         u, r = self._split()
         if r > 1 and getattr(self.attn, "impl", "") in {"sage", "sparge", "torch_sdpa_math", "b200_q8"}:
             raise NotImplementedError(f"{self.attn.impl} cannot provide LSE for Qwen full-text ring attention.")
+        if (self._use_peer(img_q, img_k, u, r, kw) and txt_q.dtype == img_q.dtype and txt_q.shape[1] % 8 == 0
+                and txt_q.shape[0] == img_q.shape[0]):
+            # Pure Ulysses over peer memory: every rank keeps its own head group of the (replicated) text rows
+            # in front of the gathered image rows; the attention kernel reads the text rows at once and the
+            # image rows as they arrive, never attends the zero-padded tail, returns each image row to its
+            # owner and stores the text rows of its heads to every rank.  Four launches, no NCCL call.
+            B, s, H, D = img_q.shape
+            n_img = int(image_seq_len if image_seq_len is not None else s * self.cp_size)
+            px = self.peer_exchange(B, s, H, D, img_q.dtype, img_q.device, prefix_rows=txt_len)
+            px.scatter_prefix(txt_q, txt_k, txt_v)
+            px.scatter_ready(img_q, img_k, img_v)
+            txt_out, img_out = px.attention_full_txt(n_img, softmax_scale)
+            from . import ops
+
+            ops.poll_status(img_q.device)
+            return txt_out, img_out
         up_group = None
         if u > 1:
             up_group = self._up_group_lookup(u)

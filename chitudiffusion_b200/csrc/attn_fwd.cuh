@@ -77,6 +77,13 @@ struct AttnParams {
   long long flag_timeout;
   PeerSync sync;
   int signal_out;
+  // Replicated prefix (the text tokens of the Qwen-Image layout): rows [0, prefix_rows) of q, k and v
+  // are this rank's own copies (no arrival flag to wait for; the exchanged rows start at prefix_rows),
+  // and the output rows of the prefix are stored to EVERY rank's prefix_ptrs buffer - each rank computes
+  // them for its own heads only and all ranks need all heads.
+  int prefix_rows;
+  void* prefix_ptrs[8];
+  long long prefix_batch_bytes, prefix_row_bytes, prefix_head_bytes;
   // Pre-attention transform of Q inside the kernel (q_norm_mode != 2 or q_rope_mode != 0): q is the RAW
   // projection output.  Once a query tile has landed in shared memory, the softmax warps - idle until
   // the first scores arrive - apply RMSNorm, weight, rotary embedding and the 16-bit rounding to it in
@@ -282,8 +289,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // starts at the first tile made only of this rank's own rows
   int rot = 0;
   if (p.in_flags != nullptr) {
-    const int first_local = (p.local_src * p.rows_per_src + kTileN - 1) / kTileN;
-    if (first_local >= kv0 && first_local < kv0 + n_kv && (first_local + 1) * kTileN <= (p.local_src + 1) * p.rows_per_src)
+    const int first_local = (p.prefix_rows + p.local_src * p.rows_per_src + kTileN - 1) / kTileN;
+    if (first_local >= kv0 && first_local < kv0 + n_kv &&
+        (first_local + 1) * kTileN <= p.prefix_rows + (p.local_src + 1) * p.rows_per_src)
       rot = first_local - kv0;
   }
 
@@ -330,8 +338,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int flag_epoch = (p.in_flags != nullptr && lane == 0) ? *reinterpret_cast<const volatile int*>(p.in_epoch) : 0;
     auto wait_rows = [&](int row_lo, int row_hi, int rows_total) {  // rows [row_lo, row_hi) of a gathered tensor
       if (p.in_flags == nullptr) return;
-      const int last = min(row_hi, rows_total) - 1;
-      for (int src = row_lo / p.rows_per_src; src <= last / p.rows_per_src; ++src) {
+      const int last = min(row_hi, rows_total) - 1 - p.prefix_rows;  // rows of the prefix are local
+      if (last < 0) return;
+      for (int src = max(row_lo - p.prefix_rows, 0) / p.rows_per_src; src <= last / p.rows_per_src; ++src) {
         if ((src_ready >> src) & 1u) continue;
         if (!wait_flag(p.in_flags + src, flag_epoch, p.flag_timeout, p.status)) *abort_flag = 1;
         src_ready |= 1u << src;
@@ -637,12 +646,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int row = q0 + t * kTileM + row_in_tile;
       const float inv_l = 1.0f / l_sum;
       uint4* dst;
+      const bool in_prefix = p.n_dest != 0 && row < p.prefix_rows;
       if (p.n_dest == 0) {
         dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) +
                                        ((static_cast<size_t>(batch) * p.Sq + row) * p.H + head) * (kHeadDim * 2));
+      } else if (in_prefix) {
+        dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.prefix_ptrs[0]) + batch * p.prefix_batch_bytes +
+                                       row * p.prefix_row_bytes + p.prefix_head_bytes + head * (kHeadDim * 2));
       } else {
-        const int dest = min(row / p.rows_per_dest, p.n_dest - 1);
-        const long long local_row = row - static_cast<long long>(dest) * p.rows_per_dest;
+        const int si = row - p.prefix_rows;
+        const int dest = min(si / p.rows_per_dest, p.n_dest - 1);
+        const long long local_row = si - static_cast<long long>(dest) * p.rows_per_dest;
         dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_ptrs[dest]) + batch * p.dest_batch_bytes +
                                        local_row * p.dest_row_bytes + p.dest_head_bytes + head * (kHeadDim * 2));
       }
@@ -680,6 +694,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             v.z = pack2<kFp16>(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
             v.w = pack2<kFp16>(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
             dst[c * 4 + (i >> 3)] = v;
+            if (in_prefix) {  // the same row for the other ranks
+              const long long off = reinterpret_cast<uint8_t*>(dst) - static_cast<uint8_t*>(p.prefix_ptrs[0]);
+              for (int d = 1; d < p.n_dest; ++d)
+                reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.prefix_ptrs[d]) + off)[c * 4 + (i >> 3)] = v;
+            }
           }
         }
       }

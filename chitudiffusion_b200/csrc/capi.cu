@@ -162,6 +162,10 @@ struct KeySplit {
 struct Exchange {
   const chitu_b200_peer_sync* sync = nullptr;
   int rows_per_src = 0;
+  // replicated prefix rows (local copies; their outputs go to every rank)
+  int prefix_rows = 0;
+  void* const* prefix_ptrs = nullptr;
+  int64_t prefix_batch_stride = 0, prefix_row_stride = 0, prefix_head_offset = 0;  // elements
 };
 
 int fill_peer_sync(chitu::PeerSync* ps, const chitu_b200_peer_sync* sync, const char* what) {
@@ -192,7 +196,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     return fail(CHITU_E_INVALID, "attn_fwd: null pointer argument");
   if (sc.n_dest != 0) {
     if (sc.n_dest < 0 || sc.n_dest > 8 || !sc.ptrs) return fail(CHITU_E_INVALID, "attn_fwd: 1..8 destinations");
-    if (sc.rows_per_dest <= 0 || static_cast<int64_t>(sc.rows_per_dest) * sc.n_dest < Sq)
+    if (sc.rows_per_dest <= 0 || static_cast<int64_t>(sc.rows_per_dest) * sc.n_dest + ex.prefix_rows < Sq)
       return fail(CHITU_E_INVALID, "attn_fwd: destinations do not cover the query rows");
     if ((sc.batch_stride | sc.row_stride | sc.head_offset) & 7)
       return fail(CHITU_E_INVALID, "attn_fwd: destination strides must be multiples of 8 elements");
@@ -292,6 +296,9 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     p.q_n_h = qpre->n_h;
     p.q_pos_offset = qpre->pos_offset;
   }
+  p.prefix_rows = 0;
+  for (int i = 0; i < 8; ++i) p.prefix_ptrs[i] = nullptr;
+  p.prefix_batch_bytes = p.prefix_row_bytes = p.prefix_head_bytes = 0;
   p.in_flags = nullptr;
   p.in_epoch = nullptr;
   p.rows_per_src = p.local_src = 0;
@@ -302,8 +309,21 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   p.sync.timeout_cycles = g_flag_wait_cycles;
   if (ex.sync != nullptr) {
     if ((rc = fill_peer_sync(&p.sync, ex.sync, "attn_fwd_exchange")) != CHITU_OK) return rc;
-    if (ex.rows_per_src <= 0 || static_cast<int64_t>(ex.rows_per_src) * p.sync.world < (Sq > Sk ? Sq : Sk))
-      return fail(CHITU_E_INVALID, "attn_fwd_exchange: rows_per_src * world must cover the sequence");
+    if (ex.rows_per_src <= 0 ||
+        static_cast<int64_t>(ex.rows_per_src) * p.sync.world + ex.prefix_rows < (Sq > Sk ? Sq : Sk))
+      return fail(CHITU_E_INVALID, "attn_fwd_exchange: prefix_rows + rows_per_src * world must cover the sequence");
+    if (ex.prefix_rows < 0 || (ex.prefix_rows > 0 && (!ex.prefix_ptrs || sc.n_dest <= 0)))
+      return fail(CHITU_E_INVALID, "attn_fwd_exchange: a replicated prefix needs its destination buffers");
+    if ((ex.prefix_batch_stride | ex.prefix_row_stride | ex.prefix_head_offset) & 7)
+      return fail(CHITU_E_INVALID, "attn_fwd_exchange: prefix strides must be multiples of 8 elements");
+    for (int i = 0; i < sc.n_dest && ex.prefix_rows > 0; ++i)
+      if (!ex.prefix_ptrs[i] || (reinterpret_cast<uintptr_t>(ex.prefix_ptrs[i]) & 15))
+        return fail(CHITU_E_INVALID, "attn_fwd_exchange: prefix destination %d null or not 16-byte aligned", i);
+    p.prefix_rows = ex.prefix_rows;
+    for (int i = 0; i < sc.n_dest && ex.prefix_rows > 0; ++i) p.prefix_ptrs[i] = ex.prefix_ptrs[i];
+    p.prefix_batch_bytes = ex.prefix_batch_stride * 2;
+    p.prefix_row_bytes = ex.prefix_row_stride * 2;
+    p.prefix_head_bytes = ex.prefix_head_offset * 2;
     p.in_flags = p.sync.blocks[p.sync.rank] + chitu::kSyncInFlag;
     p.in_epoch = p.sync.blocks[p.sync.rank] + chitu::kSyncInEpoch;
     p.rows_per_src = ex.rows_per_src;
@@ -349,6 +369,11 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     for (int i = 0; i < 8; ++i) c.out_ptrs[i] = p.out_ptrs[i];
     c.sync = p.sync;
     c.signal_out = ex.sync != nullptr;
+    c.prefix_rows = p.prefix_rows;
+    for (int i = 0; i < 8; ++i) c.prefix_ptrs[i] = p.prefix_ptrs[i];
+    c.prefix_batch_bytes = p.prefix_batch_bytes;
+    c.prefix_row_bytes = p.prefix_row_bytes;
+    c.prefix_head_bytes = p.prefix_head_bytes;
     const long long rows = static_cast<long long>(B) * Sq * H;
     chitu::splitkv_combine_kernel<<<grid_for(rows, 8, 148 * 16), 256, 0, st>>>(c);
     e = cudaGetLastError();
@@ -411,8 +436,10 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
                                  int64_t dest_head_offset, int B, int Sq, int Sk, int H, int D,
                                  const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                                  float softmax_scale, int dtype, int n_splits, void* workspace,
-                                 int64_t workspace_bytes, int rows_per_src, const chitu_b200_peer_sync* sync,
-                                 int* status, void* stream) {
+                                 int64_t workspace_bytes, int rows_per_src, int prefix_rows,
+                                 void* const* prefix_ptrs, int64_t prefix_batch_stride, int64_t prefix_row_stride,
+                                 int64_t prefix_head_offset, const chitu_b200_peer_sync* sync, int* status,
+                                 void* stream) {
   KeySplit ks;
   ks.n_splits = n_splits;
   ks.workspace = workspace;
@@ -429,6 +456,11 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
   Exchange ex;
   ex.sync = sync;
   ex.rows_per_src = rows_per_src;
+  ex.prefix_rows = prefix_rows;
+  ex.prefix_ptrs = prefix_ptrs;
+  ex.prefix_batch_stride = prefix_batch_stride;
+  ex.prefix_row_stride = prefix_row_stride;
+  ex.prefix_head_offset = prefix_head_offset;
   return attn_fwd_impl(q, k, v, nullptr, sc, nullptr, B, Sq, Sk, H, D, q_strides, k_strides, v_strides, softmax_scale,
                        dtype, status, stream, ks, ex);
 }
@@ -534,9 +566,13 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
     if (jb.n_out_ptrs != 0) {
       if (jb.n_out_ptrs < 0 || jb.n_out_ptrs > 8 || !jb.out_ptrs || jb.n_out_ptrs * sh.heads_per_group != H)
         return fail(CHITU_E_INVALID, "qk_norm_rope: need one destination per head group (at most 8)");
-      for (int i = 0; i < jb.n_out_ptrs; ++i)
-        if (!jb.out_ptrs[i] || (reinterpret_cast<uintptr_t>(jb.out_ptrs[i]) & 15))
-          return fail(CHITU_E_INVALID, "qk_norm_rope: destination %d null or not 16-byte aligned", i);
+      bool any = false;
+      for (int i = 0; i < jb.n_out_ptrs; ++i) {
+        if (reinterpret_cast<uintptr_t>(jb.out_ptrs[i]) & 15)
+          return fail(CHITU_E_INVALID, "qk_norm_rope: destination %d not 16-byte aligned", i);
+        any = any || jb.out_ptrs[i] != nullptr;  // a null entry drops that head group
+      }
+      if (!any) return fail(CHITU_E_INVALID, "qk_norm_rope: every destination is null");
     }
     if (jb.norm_mode < 0 || jb.norm_mode > 2 || jb.rope_mode < 0 || jb.rope_mode > 2)
       return fail(CHITU_E_INVALID, "qk_norm_rope: bad mode");

@@ -122,6 +122,10 @@ struct SplitCombineParams {
   // when signal_out is set, the last CTA tells every peer that this rank's output rows have landed
   PeerSync sync;
   int signal_out;
+  // replicated prefix (see AttnParams): rows [0, prefix_rows) go to EVERY rank's prefix_ptrs buffer
+  int prefix_rows;
+  void* prefix_ptrs[8];
+  long long prefix_batch_bytes, prefix_row_bytes, prefix_head_bytes;
 };
 
 __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitCombineParams p) {
@@ -143,12 +147,16 @@ __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitCombine
     for (int i = 0; i < p.n; ++i) wsum += expf(p.part_lse[i * lstride + lidx] - mx);
     const float inv = 1.0f / wsum;
     uint8_t* orow;
+    const bool in_prefix = s < p.prefix_rows;
     if (p.n_dest == 0) {
       orow = static_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.D * 2;
+    } else if (in_prefix) {
+      orow = nullptr;  // stored to every rank below
     } else {
-      const int dest = min(s / p.rows_per_dest, p.n_dest - 1);
+      const int si = s - p.prefix_rows;
+      const int dest = min(si / p.rows_per_dest, p.n_dest - 1);
       orow = static_cast<uint8_t*>(p.out_ptrs[dest]) + b * p.dest_batch_bytes +
-             (s - static_cast<long long>(dest) * p.rows_per_dest) * p.dest_row_bytes + p.dest_head_bytes +
+             (si - static_cast<long long>(dest) * p.rows_per_dest) * p.dest_row_bytes + p.dest_head_bytes +
              static_cast<long long>(h) * p.D * 2;
     }
     for (int d = lane * 4; d < p.D; d += 128) {
@@ -164,7 +172,14 @@ __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitCombine
       uint2 raw;
       raw.x = pack16(acc.x, acc.y, p.out_dtype);
       raw.y = pack16(acc.z, acc.w, p.out_dtype);
-      *reinterpret_cast<uint2*>(orow + d * 2) = raw;
+      if (orow != nullptr) {
+        *reinterpret_cast<uint2*>(orow + d * 2) = raw;
+      } else {
+        for (int i = 0; i < p.n_dest; ++i)
+          *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.prefix_ptrs[i]) + b * p.prefix_batch_bytes +
+                                    s * p.prefix_row_bytes + p.prefix_head_bytes + static_cast<long long>(h) * p.D * 2 +
+                                    d * 2) = raw;
+      }
     }
     if (lane == 0 && p.lse != nullptr) p.lse[lidx] = mx + logf(wsum);
   }
@@ -304,6 +319,8 @@ __device__ __forceinline__ void qk_norm_rope_job(const NormRopeParams& p, float 
   }
   const int grp = h / p.heads_per_group;
   const long long out_h = (p.n_out_ptrs > 0 ? 0 : grp * p.os_g) + (h % p.heads_per_group) * p.os_h + d0;
+  // a null entry in out_ptrs drops that head group (replicated rows of which a rank keeps only its own heads)
+  const bool keep = p.n_out_ptrs == 0 || p.out_ptrs[active ? grp : 0] != nullptr;
   uint16_t* const out_base = static_cast<uint16_t*>(p.n_out_ptrs > 0 ? p.out_ptrs[grp] : p.out) + out_h;
   const int grid_tokens = p.gf * p.gh * p.gw;
   const int pos0 = static_cast<int>(p.pos_offset);
@@ -424,7 +441,7 @@ __device__ __forceinline__ void qk_norm_rope_job(const NormRopeParams& p, float 
         }
         rstd = rsqrtf(ss * inv_n + p.eps);
       }
-      if (active) {
+      if (active && keep) {
         float y[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {

@@ -668,6 +668,11 @@ def attn_fwd_exchange(
     softmax_scale: Optional[float] = None,
     n_splits: Optional[int] = None,
     workspace: Optional[torch.Tensor] = None,
+    prefix_rows: int = 0,
+    prefix_ptrs: Optional[Sequence[int]] = None,
+    prefix_batch_stride: int = 0,
+    prefix_row_stride: int = 0,
+    prefix_head_offset: int = 0,
 ) -> None:
     """:func:`attn_fwd_scatter` over exchange buffers guarded by arrival flags; see ``chitu_b200_attn_fwd_exchange``."""
     import ctypes
@@ -693,7 +698,9 @@ def attn_fwd_exchange(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr_array(out_ptrs), len(out_ptrs), int(rows_per_dest),
             int(dest_batch_stride), int(dest_row_stride), int(dest_head_offset), B, Sq, Sk, H, D,
             _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale,
-            _DTYPES[q.dtype], int(n_splits), ws_ptr, ws_bytes, int(rows_per_src), ctypes.byref(sync[0]),
+            _DTYPES[q.dtype], int(n_splits), ws_ptr, ws_bytes, int(rows_per_src), int(prefix_rows),
+            _lib.ptr_array(prefix_ptrs) if prefix_ptrs else None, int(prefix_batch_stride), int(prefix_row_stride),
+            int(prefix_head_offset), ctypes.byref(sync[0]),
             status_word(q.device).data_ptr(), _stream_ptr(q.device),
         )
     _lib.check(rc, "attn_fwd_exchange")

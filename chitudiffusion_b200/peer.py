@@ -47,7 +47,11 @@ class PeerUlysses:
     until the call after next (the reference hands back a fresh tensor; no copy is made here).
     """
 
-    def __init__(self, group: CommGroup, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device):
+    def __init__(self, group: CommGroup, B: int, s: int, H: int, D: int, dtype: torch.dtype, device: torch.device,
+                 prefix_rows: int = 0):
+        """``prefix_rows`` > 0: the replicated-text layout (Qwen-Image): the gathered tensors start with
+        ``prefix_rows`` rows that every rank produces itself (it keeps its own head group of them), the
+        exchanged rows follow, and the prefix rows of the result are stored to every rank (``txt_out``)."""
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _lib
@@ -60,10 +64,12 @@ class PeerUlysses:
         self.group, self.U, self.rank = group, U, group.rank_in_group
         self.B, self.s, self.H, self.D, self.hc = B, s, H, D, H // U
         self.dtype, self.device = dtype, device
+        self.T = T = int(prefix_rows)
         es = torch.empty((), dtype=dtype).element_size()
         self.es = es
-        tile = B * U * s * self.hc * D * es  # one of q / k / v in the gathered layout
-        out_bytes = _align(B * s * H * D * es)
+        tile = B * (T + U * s) * self.hc * D * es  # one of q / k / v in the gathered layout
+        out_bytes = _align(B * s * H * D * es) + _align(B * T * H * D * es)  # image rows, then the text rows
+        self._txt_out_off = _align(B * s * H * D * es)
         self.off_q = 0
         self.off_k = _align(tile)
         self.off_v = self.off_k + _align(tile)
@@ -84,20 +90,21 @@ class PeerUlysses:
                 n *= d
             return self.buf[off : off + n * es].view(dtype).view(shape)
 
-        gathered = (B, U * s, self.hc, D)
+        gathered = (B, T + U * s, self.hc, D)
         self.q, self.k, self.v = view(self.off_q, gathered), view(self.off_k, gathered), view(self.off_v, gathered)
         self.outs = [view(self.off_out + i * out_bytes, (B, s, H, D)) for i in range(2)]
+        self.txt_outs = [view(self.off_out + i * out_bytes + self._txt_out_off, (B, T, H, D)) for i in range(2)]
         self.out = self.outs[0]
         self._out_slot = 0
         self.flag_ptrs = [p + self.off_flags for p in self.ptrs]
         self.sync = _lib.peer_sync_desc(self.flag_ptrs, self.rank)
-        # element strides (b, s, -, h) of the gathered layout; this rank's rows start at rank * s
-        self.gather_strides = (U * s * self.hc * D, self.hc * D, 0, D)
+        # element strides (b, s, -, h) of the gathered layout; this rank's rows start at prefix + rank * s
+        self.gather_strides = ((T + U * s) * self.hc * D, self.hc * D, 0, D)
         self._row_bytes = self.hc * D * es
-        self._row0 = self.rank * s * self._row_bytes
+        self._row0 = (T + self.rank * s) * self._row_bytes
         # key-split scratch owned by this object: graphs captured over it keep a valid address
-        self.n_splits = ops.auto_key_splits(B, U * s, U * s, self.hc)
-        need = ops.splitkv_workspace_bytes(B, U * s, self.hc, D, self.n_splits)
+        self.n_splits = ops.auto_key_splits(B, T + U * s, T + U * s, self.hc)
+        need = ops.splitkv_workspace_bytes(B, T + U * s, self.hc, D, self.n_splits)
         self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=device) if self.n_splits > 1 else None
 
     def dest_ptrs(self, which: str, row_offset: int = 0):
@@ -143,6 +150,38 @@ class PeerUlysses:
                      out_ptrs=self.dest_ptrs(w)) for t, w in ((q, "q"), (k, "k"), (v, "v"))]
         ops.qk_norm_rope_batch(jobs, num_heads=self.H, eps=0.0, rope_table=None, out_strides=self.gather_strides,
                                heads_per_group=self.hc, out_dtype=self.dtype, sync=self.sync)
+
+    def scatter_prefix(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Replicated rows ``[B, T, H, D]`` (every rank holds the same ones): this rank's head group of them goes
+        to rows ``[0, T)`` of its OWN buffers; the other head groups are dropped.  No announcement (local rows)."""
+        jobs = []
+        for t, which in ((q, "q"), (k, "k"), (v, "v")):
+            off = {"q": self.off_q, "k": self.off_k, "v": self.off_v}[which]
+            ptrs = [0] * self.U
+            ptrs[self.rank] = self.ptrs[self.rank] + off
+            jobs.append(dict(x=t.reshape(self.B, self.T, self.H * self.D), norm_mode=2, rope_mode=0, out_ptrs=ptrs))
+        ops.qk_norm_rope_batch(jobs, num_heads=self.H, eps=0.0, rope_table=None, out_strides=self.gather_strides,
+                               heads_per_group=self.hc, out_dtype=self.dtype)
+
+    def attention_full_txt(self, n_valid: int, softmax_scale: Optional[float] = None):
+        """Attention over ``[text | gathered image rows]``; keys past ``n_valid`` image rows (the zero-padded tail of
+        the last shard) are never attended.  Returns ``(text result [B, T, H, D] for all heads, this rank's image
+        rows [B, s, H, D])``, both valid until the call after next."""
+        self._out_slot ^= 1
+        slot_off = self.off_out + self._out_slot * self._out_bytes
+        Sk = self.T + min(int(n_valid), self.U * self.s)
+        ops.attn_fwd_exchange(
+            self.q, self.k[:, :Sk], self.v[:, :Sk], [p + slot_off for p in self.ptrs], rows_per_dest=self.s,
+            dest_batch_stride=self.s * self.H * self.D, dest_row_stride=self.H * self.D,
+            dest_head_offset=self.rank * self.hc * self.D, rows_per_src=self.s, sync=self.sync,
+            softmax_scale=softmax_scale, n_splits=self.n_splits, workspace=self.workspace,
+            prefix_rows=self.T, prefix_ptrs=[p + slot_off + self._txt_out_off for p in self.ptrs],
+            prefix_batch_stride=self.T * self.H * self.D, prefix_row_stride=self.H * self.D,
+            prefix_head_offset=self.rank * self.hc * self.D,
+        )
+        ops.peer_wait_outputs(self.sync, self.device)
+        self.out = self.outs[self._out_slot]
+        return self.txt_outs[self._out_slot], self.out
 
     def attention(self, softmax_scale: Optional[float] = None) -> torch.Tensor:
         """Attention over the gathered q/k/v as their rows arrive, output rows stored to their owners, then the

@@ -354,6 +354,14 @@ int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* sta
  *   (bounded, status 5 on timeout) for rank s's flag before its first copy that touches them, and walks
  *   the key tiles starting with this rank's own rows.  When the last output row has been stored it writes
  *   the new epoch into every peer's "outputs of rank r have landed" flag.
+ *   Replicated prefix (the text tokens of the Qwen-Image layout, cp_attn_with_full_txt,
+ *   diffusion_attn_backend.py:839-984): rows [0, prefix_rows) of q, k and v are this rank's own copies - no
+ *   flag is waited for, the exchanged rows start at prefix_rows - and the output rows of the prefix, which
+ *   each rank computes for its own heads only, are stored to EVERY rank's prefix_ptrs[i] buffer at
+ *   batch*prefix_batch_stride + row*prefix_row_stride + prefix_head_offset + head*128 + d (the all-gather
+ *   of the text output over heads, :968-984).  prefix_rows = 0: none.  A null entry in the out_ptrs of
+ *   chitu_b200_qk_norm_rope_scatter / _batch drops that head group (a rank keeps only its own heads of the
+ *   replicated rows).
  * chitu_b200_peer_wait_outputs: one warp that waits (bounded) until every rank's output flag has reached
  *   the next epoch: after it, this rank's output buffer is complete, and - because a rank signals only
  *   when its whole attention grid has finished - its q / k / v buffers may be overwritten by the next layer.
@@ -373,8 +381,10 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
                                  int64_t dest_head_offset, int B, int Sq, int Sk, int H, int D,
                                  const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                                  float softmax_scale, int dtype, int n_splits, void* workspace,
-                                 int64_t workspace_bytes, int rows_per_src, const chitu_b200_peer_sync* sync,
-                                 int* status, void* stream);
+                                 int64_t workspace_bytes, int rows_per_src, int prefix_rows,
+                                 void* const* prefix_ptrs, int64_t prefix_batch_stride, int64_t prefix_row_stride,
+                                 int64_t prefix_head_offset, const chitu_b200_peer_sync* sync, int* status,
+                                 void* stream);
 int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, void* stream);
 
 /*

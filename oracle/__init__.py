@@ -46,3 +46,4 @@ from .layouts import (  # noqa: F401
 from .quantised import attention_q8  # noqa: F401,E402
 from .dit_block import layer_norm_fp32, wan_block  # noqa: F401,E402
 from .flux_block import flux_double_block, flux_single_block  # noqa: F401,E402
+from .qwen_block import qwen_attention, qwen_double_block, qwen_streams, slice_rotary_freqs, apply_rotary_complex  # noqa: F401,E402

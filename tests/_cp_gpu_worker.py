@@ -99,6 +99,21 @@ def main():
         t_out, i_out = core.attention(*(t.to(dev) for t in txt), ql, kl, vl)
         results[f"imagecp_{mode}"] = max(rel_err(t_out, full_it[:, :24]), rel_err(i_out, full_it[:, 24:][:, sl]))
     print(f"rank {rank}: imagecp done", flush=True)
+    # replicated text + sharded image with a zero-padded tail (the Qwen-Image layout), Ulysses over peer memory:
+    # text rows kept locally, image rows exchanged, padded keys never attended, text result stored to every rank
+    n_img = S - 5
+    iq, ik, iv = (t[:, :n_img] for t in (q, k, v))
+    full_pad = oracle.sdpa_fp32(torch.cat([txt[0], iq], 1), torch.cat([txt[1], ik], 1), torch.cat([txt[2], iv], 1))
+    shards = [oracle.split_sequence_padding(t, world, 1)[rank].contiguous().to(dev) for t in (iq, ik, iv)]
+    ls = shards[0].shape[1]
+    wrapper = B200ContextParallel(backend, world, cp_backend="ucp")
+    for rep in range(2):
+        t_out, i_out = wrapper.cp_attn_with_full_txt(*(t.to(dev) for t in txt), *shards, image_seq_len=n_img)
+    assert any(getattr(px, "T", 0) == 24 for px in wrapper._peer_cache.values()), "peer path not taken"
+    valid = max(0, min(ls, n_img - rank * ls))
+    results["fulltxt_peer"] = max(rel_err(t_out, full_pad[:, :24]),
+                                  rel_err(i_out[:, :valid], full_pad[:, 24 + rank * ls: 24 + rank * ls + valid]))
+    print(f"rank {rank}: fulltxt_peer done", flush=True)
 
     # peer-store exchange: norm + rotary pre-pass scattered to the owners, attention scattered back
     comm.destroy_diffusion_parallel_groups()

@@ -169,6 +169,53 @@ def main():
                 err = (got[key].float() - ref.float()).abs().max().item() if ref.numel() else 0.0
                 ok = ok and same_meta and err <= tol * max(1.0, ref.float().abs().max().item() if ref.numel() else 1.0)
                 print(f"rank {rank} {mode} {key} dtype {got[key].dtype} err {err:.2e} ok={ok}", flush=True)
+        elif mode == "qwen":
+            # the Qwen-Image processor mirror over the replicated-text layout: image tokens sharded with a zero-padded
+            # tail, rotary rows taken at this rank's image offset (zero past the end), text replicated
+            from chitudiffusion_b200.pre_attention import table_from_complex
+            from chitudiffusion_b200.qwen import B200QwenAttnProcessor, QwenDoubleBlock, QwenJointAttention
+
+            class HostProcessor(B200QwenAttnProcessor):
+                """Same control flow; the per-stream kernel launch is replaced by the oracle's arithmetic on host tensors."""
+
+                def _stream(self, x, proj_q, proj_k, proj_v, norm_q, norm_k, heads, table, outs=None, row_offset=0):
+                    Bx, Sx, _ = x.shape
+                    q = oracle.per_head_rms_norm(proj_q(x).view(Bx, Sx, heads, -1), norm_q.weight)
+                    k = oracle.per_head_rms_norm(proj_k(x).view(Bx, Sx, heads, -1), norm_k.weight)
+                    v = proj_v(x).view(Bx, Sx, heads, -1)
+                    if table is not None:
+                        cos, sin = table[..., 0].double(), table[..., 1].double()
+                        q, k = oracle.apply_rope_interleaved(q, cos, sin), oracle.apply_rope_interleaved(k, cos, sin)
+                    return q, k, v
+
+            Cq, Hq = 64, 4
+            n_img, n_txt = s * cp_size - 3, 5
+            pq = {}
+            for name, shape in QwenDoubleBlock.param_shapes(Cq, Hq).items():
+                if name.startswith("attn."):
+                    pq[name] = (1.0 + 0.1 * torch.randn(shape, generator=gen)) if "norm" in name else \
+                        0.2 * torch.randn(shape, generator=gen)
+            hi = torch.randn(1, n_img, Cq, generator=gen)
+            ht = torch.randn(1, n_txt, Cq, generator=gen)
+            half = Cq // Hq // 2
+            rotary = (torch.polar(torch.ones(n_img, half, dtype=torch.float64), torch.randn(n_img, half, generator=gen).double()),
+                      torch.polar(torch.ones(n_txt, half, dtype=torch.float64), torch.randn(n_txt, half, generator=gen).double()))
+            ref_img, ref_txt = oracle.qwen_attention(hi, ht, pq, Hq, rotary)
+            shard = oracle.split_sequence_padding(hi, cp_size, 1)[r]
+            ls = shard.shape[1]
+            proc = HostProcessor(wrapper)
+            assert proc.base_attn_backend is wrapper.attn
+            info = {"image_offset": r * ls, "image_seq_len": n_img}
+            img_o, txt_o = proc(QwenJointAttention(pq, Hq), shard, ht, None, None, rotary, info)
+            valid = max(0, min(ls, n_img - r * ls))
+            err_i = (img_o[:, :valid] - ref_img[:, r * ls:r * ls + valid]).abs().max().item() if valid else 0.0
+            err_t = (txt_o - ref_txt).abs().max().item()
+            ok = err_i < 1e-4 and err_t < 1e-4 and tuple(img_o.shape) == (1, ls, Cq)
+            # the table handed to the image stream: this rank's rows, zeros past the true image length
+            tab = proc._table(rotary[0], torch.device("cpu"), r * ls, ls)
+            full = table_from_complex(rotary[0])
+            ok = ok and torch.equal(tab[:valid], full[r * ls:r * ls + valid]) and not tab[valid:].any()
+            print(f"rank {rank} qwen err_img {err_i:.2e} err_txt {err_t:.2e} ok={ok}", flush=True)
         elif mode == "fused":
             S = s * cp_size
             q, k, v = (torch.randn(B, S, H, D, generator=gen) for _ in range(3))

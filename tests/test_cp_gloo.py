@@ -27,9 +27,9 @@ def _run(nproc, cfg_size, up, cp_backend, mode):
     (2, 1, 2, "ucp", "plain,fused,imagecp_ring,imagecp_agkv,golden:ulysses2,golden:ulysses2_bf16,golden:fulltxt_ulysses2"),
     (2, 1, 1, "ucp", "plain,golden:ring2,golden:ring2_bf16"),              # ring-2
     # all-gather-KV, also with the replicated-text layout
-    (2, 1, 2, "agcp", "plain,fulltxt,golden:agcp2,golden:agcp2_bf16,golden:fulltxt_agcp2"),
+    (2, 1, 2, "agcp", "plain,fulltxt,qwen,golden:agcp2,golden:agcp2_bf16,golden:fulltxt_agcp2"),
     # Ulysses-2 x ring-2; batch > 1 (unpack-copy path); Qwen layout with a padded tail; image-CP core, unified mode
-    (4, 1, 2, "ucp", "plain,batch2,fulltxt,imagecp_unified,golden:usp_u2r2,golden:usp_u2r2_batch2,"
+    (4, 1, 2, "ucp", "plain,batch2,fulltxt,qwen,imagecp_unified,golden:usp_u2r2,golden:usp_u2r2_batch2,"
                      "golden:usp_u2r2_bf16,golden:fulltxt_usp_u2r2"),
     (4, 1, 4, "ucp", "golden:ulysses4"),
     (4, 1, 1, "ucp", "golden:ring4,golden:fulltxt_ring4"),

@@ -209,3 +209,54 @@ def test_flux_single_block_against_oracle(cuda):
         out = b(x.to(cuda).clone(), temb.to(cuda), table.to(cuda), B200AttnBackend("b200"))
         err, cos_sim = _close(out, ref)
         assert err <= 3e-2 and cos_sim >= 0.999, (err, cos_sim)
+
+
+def _qwen_inputs(dim, n_txt, n_img, heads):
+    gen = torch.Generator().manual_seed(33)
+    img = torch.randn(2, n_img, dim, generator=gen).to(torch.bfloat16)
+    txt = torch.randn(2, n_txt, dim, generator=gen).to(torch.bfloat16)
+    temb = torch.randn(2, dim, generator=gen).to(torch.bfloat16)
+    half = dim // heads // 2
+    ang_i = torch.randn(n_img, half, generator=gen, dtype=torch.float64)
+    ang_t = torch.randn(n_txt, half, generator=gen, dtype=torch.float64)
+    rotary = (torch.polar(torch.ones_like(ang_i), ang_i), torch.polar(torch.ones_like(ang_t), ang_t))
+    return img, txt, temb, rotary
+
+
+def test_qwen_double_block_and_processor_against_oracle(cuda):
+    """The Qwen-Image MMDiT block (and the attention processor inside it) against the fp32 restatement; the block's
+    definition lives in the un-vendored diffusers, so this parity is unpinned - the processor's call contract is the
+    reference's own."""
+    from chitudiffusion_b200 import B200AttnBackend
+    from chitudiffusion_b200.qwen import B200QwenAttnProcessor, QwenDoubleBlock, slice_rotary_table
+    from chitudiffusion_b200.pre_attention import table_from_complex
+
+    dim, heads = 256, 2
+    img, txt, temb, rotary = _qwen_inputs(dim, 20, 150, heads)
+    blk = QwenDoubleBlock.random_init(dim, heads, cuda, seed=12, std=0.05)
+    gen = torch.Generator().manual_seed(6)
+    for name, t in blk.p.items():
+        if name.endswith(".bias"):
+            t.copy_((0.05 * torch.randn(t.shape, generator=gen)).to(t.dtype))
+        elif "norm" in name:
+            t.copy_(1.0 + 0.1 * torch.randn(t.shape, generator=gen))
+    p = {k: v.float().cpu() for k, v in blk.p.items()}
+    ref_txt, ref_img = oracle.qwen_double_block(img.float(), txt.float(), temb.float(), p, heads, rotary)
+    proc = B200QwenAttnProcessor(B200AttnBackend("b200"))
+    blk2 = QwenDoubleBlock.from_reference(p, heads, cuda)
+    rot_dev = tuple(r.to(cuda) for r in rotary)
+    for b in (blk, blk2):
+        o_txt, o_img = b(img.to(cuda).clone(), txt.to(cuda).clone(), temb.to(cuda), rot_dev, proc)
+        for out, ref in ((o_txt, ref_txt), (o_img, ref_img)):
+            err, cos_sim = _close(out, ref)
+            assert err <= 3e-2 and cos_sim >= 0.999, (err, cos_sim)
+    # rows of the image rotary table taken at an offset, zero past the end (what a rank with a padded shard gets)
+    t = table_from_complex(rotary[0])
+    got = slice_rotary_table(t, 140, 16)
+    assert torch.equal(got[:10], t[140:150]) and not got[10:].any()
+    want = oracle.slice_rotary_freqs(rotary[0], 140, 16)
+    assert torch.equal(got, table_from_complex(want))
+    with pytest.raises(ValueError):
+        proc(blk.attn, img.to(cuda), None)
+    with pytest.raises(NotImplementedError):
+        proc(blk.attn, img.to(cuda), txt.to(cuda), attention_mask=torch.ones(1))
