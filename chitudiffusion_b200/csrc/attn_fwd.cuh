@@ -251,12 +251,26 @@ __device__ __forceinline__ void transform_q_tile(uint8_t* tile, int warp_in_tile
 }
 
 template <bool kFp16>
+#ifdef CHITU_ATTN_TIMING
+#define CHITU_TRACE(i)                                                                                       \
+  do {                                                                                                       \
+    if (p.dbg != nullptr) {                                                                                  \
+      unsigned long long t_;                                                                                 \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                 \
+      p.dbg[64 + 8 * (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) + (i)] = (long long)t_; \
+    }                                                                                                        \
+  } while (0)
+#else
+#define CHITU_TRACE(i)
+#endif
+
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  if (threadIdx.x == 0) CHITU_TRACE(0);
 
   const uint32_t q_smem = smem_base;                          // 2 tiles
   const uint32_t kv_smem = smem_base + kQTiles * kTileBytes;  // kStages tiles
@@ -344,6 +358,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if ((src_ready >> src) & 1u) continue;
         if (!wait_flag(p.in_flags + src, flag_epoch, p.flag_timeout, p.status)) *abort_flag = 1;
         src_ready |= 1u << src;
+        CHITU_TRACE(1);
         // the rows were written by a peer's ordinary stores and are about to be read by the copy engine
         #if CHITU_FLAG_VARIANT != 3
           asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -377,6 +392,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       __syncwarp();
     }
+    if (lane == 0) CHITU_TRACE(2);
     if (*abort_flag && lane == 0) {
       // A role gave up: make sure no bulk copy of ours is still landing in this
       // CTA's shared memory before the CTA retires (bounded polls): the Q tiles, then the last
@@ -641,6 +657,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #endif
 
       // epilogue: O / l -> 16-bit, row-contiguous 256-byte stores; LSE in natural log
+      if (t == 0 && row_in_tile == 0) CHITU_TRACE(3);
       mbar_wait(bar_o_final + 8 * t, 0, abort_flag, p.status, kDevTimeoutEpilogue);
       tc_fence_after_sync();
       const int row = q0 + t * kTileM + row_in_tile;
@@ -680,12 +697,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           p.part_lse[((static_cast<size_t>(split) * p.B + batch) * p.H + head) * p.Sq + row] =
               (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
       } else {
+        // Rows go out through this query tile's shared memory (its last reader, the final QK^T, has completed):
+        // each thread parks its 256-byte row there, then the warp stores its own 32 rows two at a time, 512
+        // contiguous bytes per instruction.  A row per thread straight to global memory would leave the SM as
+        // 16-byte pieces, which peer stores over NVLink carry at a fraction of the link rate.
+        uint8_t* stage = smem_gen + t * kTileBytes;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tmem_ld32(t_o + c * 32, o);
-        tmem_wait_ld();
-        if (row < p.Sq) {
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_o + c * 32, o);
+          tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v;
@@ -693,16 +714,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             v.y = pack2<kFp16>(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
             v.z = pack2<kFp16>(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
             v.w = pack2<kFp16>(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-            dst[c * 4 + (i >> 3)] = v;
-            if (in_prefix) {  // the same row for the other ranks
-              const long long off = reinterpret_cast<uint8_t*>(dst) - static_cast<uint8_t*>(p.prefix_ptrs[0]);
+            const int chunk = c * 4 + (i >> 3);
+            *reinterpret_cast<uint4*>(stage + row_in_tile * 256 + ((chunk ^ (row_in_tile & 7)) << 4)) = v;
+          }
+        }
+        __syncwarp();
+        const unsigned long long my_dst = row < p.Sq ? reinterpret_cast<unsigned long long>(dst) : 0ull;
+        const int chunk = lane & 15;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int owner = 2 * i + (lane >> 4);  // the lane whose row this half-warp stores
+          const unsigned long long base = __shfl_sync(0xffffffffu, my_dst, owner);
+          const int to_all = __shfl_sync(0xffffffffu, static_cast<int>(in_prefix), owner);
+          const int r = quad * 32 + owner;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((chunk ^ (r & 7)) << 4));
+          if (base != 0ull) {
+            reinterpret_cast<uint4*>(base)[chunk] = v;
+            if (to_all) {  // a replicated row: the same bytes for the other ranks
+              const long long off = static_cast<long long>(base - reinterpret_cast<unsigned long long>(p.prefix_ptrs[0]));
               for (int d = 1; d < p.n_dest; ++d)
-                reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.prefix_ptrs[d]) + off)[c * 4 + (i >> 3)] = v;
+                reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.prefix_ptrs[d]) + off)[chunk] = v;
             }
           }
         }
       }
-      }
+      if (t == 0 && row_in_tile == 0) CHITU_TRACE(4);
       if (p.n_splits == 1 && p.lse != nullptr && row < p.Sq) {
         p.lse[(static_cast<size_t>(batch) * p.H + head) * p.Sq + row] =
             (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
@@ -712,12 +748,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) CHITU_TRACE(5);
   if (warp == 8) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
   if (p.signal_out && threadIdx.x == 0)
     publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, gridDim.x * gridDim.y * gridDim.z);
+  if (threadIdx.x == 0) CHITU_TRACE(6);
 }
 
 }  // namespace chitu
