@@ -31,6 +31,9 @@ EXPORTS = (
     "chitu_b200_set_flag_wait_cycles",
     "chitu_b200_qk_norm_rope_batch_signal",
     "chitu_b200_attn_fwd_exchange",
+    "chitu_b200_attn_fwd_exchange_push",
+    "chitu_b200_qk_norm_rope_batch_stage",
+    "chitu_b200_push_ctas",
     "chitu_b200_attn_fwd_qpre",
     "chitu_b200_peer_wait_outputs",
     "chitu_b200_attn_splitkv_workspace_bytes",
@@ -64,6 +67,13 @@ class NormRopeJob(ctypes.Structure):
         ("norm_mode", ctypes.c_int), ("rope_mode", ctypes.c_int), ("out", ctypes.c_void_p),
         ("out_ptrs", ctypes.POINTER(ctypes.c_void_p)), ("n_out_ptrs", ctypes.c_int), ("rstd_out", ctypes.c_void_p),
     ]
+
+
+class PushDesc(ctypes.Structure):
+    """Mirror of ``chitu_b200_push``."""
+
+    _fields_ = [("stage", ctypes.c_void_p * 3), ("dest", ctypes.POINTER(ctypes.c_void_p) * 3),
+                ("block_bytes", ctypes.c_int64)]
 
 
 class PeerSyncDesc(ctypes.Structure):
@@ -186,6 +196,17 @@ def load() -> ctypes.CDLL:
         _i64p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
         ctypes.POINTER(PeerSyncDesc), _vp,
     ]
+    lib.chitu_b200_qk_norm_rope_batch_stage.restype = ctypes.c_int
+    lib.chitu_b200_qk_norm_rope_batch_stage.argtypes = list(lib.chitu_b200_qk_norm_rope_batch_signal.argtypes)
+    lib.chitu_b200_push_ctas.restype = ctypes.c_int
+    lib.chitu_b200_push_ctas.argtypes = [ctypes.c_int] * 4
+    lib.chitu_b200_attn_fwd_exchange_push.restype = ctypes.c_int
+    lib.chitu_b200_attn_fwd_exchange_push.argtypes = [
+        _vp, _vp, _vp, _vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+        _i64p, _i64p, _i64p, ctypes.c_float, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int64, ctypes.c_int,
+        ctypes.POINTER(PushDesc), ctypes.POINTER(PeerSyncDesc), _vp, _vp,
+    ]
     lib.chitu_b200_attn_fwd_exchange.restype = ctypes.c_int
     lib.chitu_b200_attn_fwd_exchange.argtypes = [
         _vp, _vp, _vp, _vpp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
@@ -209,6 +230,18 @@ def load() -> ctypes.CDLL:
     lib.chitu_b200_peer_barrier.argtypes = [_vpp, ctypes.c_int, ctypes.c_int, _vp, _vp]
     _lib = lib
     return lib
+
+
+def push_desc(stage_ptrs: Sequence[int], dest_ptrs: Sequence[Sequence[int]], block_bytes: int):
+    """``(descriptor, keep-alive)`` of ``chitu_b200_push``: staging areas of q, k, v and, per tensor, where this
+    rank's block starts in every rank's gathered buffer."""
+    arrs = [(ctypes.c_void_p * len(d))(*[int(x) for x in d]) for d in dest_ptrs]
+    desc = PushDesc()
+    for t in range(3):
+        desc.stage[t] = int(stage_ptrs[t])
+        desc.dest[t] = ctypes.cast(arrs[t], ctypes.POINTER(ctypes.c_void_p))
+    desc.block_bytes = int(block_bytes)
+    return desc, arrs
 
 
 def peer_sync_desc(block_ptrs: Sequence[int], rank: int):

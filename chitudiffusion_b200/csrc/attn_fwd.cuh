@@ -77,6 +77,20 @@ struct AttnParams {
   long long flag_timeout;
   PeerSync sync;
   int signal_out;
+  // Push mode (push_x > 0): the rows this rank owes its peers are staged in local memory, and the CTAs with
+  // blockIdx.x >= gridDim.x - push_x do no attention: they copy the staged rows into the peers' buffers
+  // while the attention CTAs of the same launch already work - the query rows for every peer first, where
+  // the staging launch has not delivered them itself (push_src[0] != nullptr; announced in q_flags), then
+  // key and value rows in push_order, the order in which the receivers walk their keys: the first
+  // push_first peers, then the others (announced in in_flags).  The rank's own rows are already in place (the
+  // staging launch wrote them) and have no flag.  The host only chooses this mode when the whole grid is
+  // resident at once, so a waiting attention CTA never keeps a copy CTA off the machine.
+  int push_x, push_rounds, push_first, rot_other;
+  int push_order[8];
+  const uint4* push_src[3];  // staged q, k, v: block d (push_vecs 16-byte vectors) holds the rows for rank d
+  uint4* push_dst[3][8];     // where this rank's block starts in rank d's gathered q, k, v
+  long long push_vecs;
+  const int* q_flags;
   // Replicated prefix (the text tokens of the Qwen-Image layout): rows [0, prefix_rows) of q, k and v
   // are this rank's own copies (no arrival flag to wait for; the exchanged rows start at prefix_rows),
   // and the output rows of the prefix are stored to EVERY rank's prefix_ptrs buffer - each rank computes
@@ -250,7 +264,83 @@ __device__ __forceinline__ void transform_q_tile(uint8_t* tile, int warp_in_tile
   }
 }
 
-template <bool kFp16>
+// The copy CTAs of push mode (see AttnParams): `id` of `n` CTAs, blockDim.x threads each.
+// One stage is a list of equally long segments (a tensor's block for one peer each); the threads walk the
+// concatenation with a fixed stride and keep eight 16-byte loads in flight each - the copy is latency
+// bound, and a segment alone (two vectors per thread on eight GPUs) would leave the pipeline empty.
+template <typename SegFn>
+__device__ __forceinline__ void push_segments(int n_seg, long long vecs, long long first, long long stride,
+                                              SegFn seg_fn) {
+  int seg = 0;
+  long long i = first;
+  while (i >= vecs) {
+    i -= vecs;
+    ++seg;
+  }
+  while (seg < n_seg) {
+    uint4 t[8];
+    uint4* d[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      d[u] = nullptr;
+      if (seg < n_seg) {
+        const uint4* src;
+        uint4* dst;
+        seg_fn(seg, src, dst);
+        t[u] = __ldg(src + i);
+        d[u] = dst + i;
+        i += stride;
+        while (i >= vecs) {
+          i -= vecs;
+          ++seg;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (d[u] != nullptr) *d[u] = t[u];
+  }
+}
+
+__device__ __forceinline__ void push_rows(const AttnParams& p, int id, int n) {
+  const int epoch = *reinterpret_cast<const volatile int*>(p.in_epoch);
+  const long long stride = static_cast<long long>(n) * blockDim.x;
+  const long long first = static_cast<long long>(id) * blockDim.x + threadIdx.x;
+  if (p.push_src[0] != nullptr) {  // query rows too (a staging launch that left them to this one)
+    push_segments(p.push_rounds, p.push_vecs, first, stride, [&](int seg, const uint4*& src, uint4*& dst) {
+      const int dest = p.push_order[seg];
+      src = p.push_src[0] + dest * p.push_vecs;
+      dst = p.push_dst[0][dest];
+    });
+    // (the CTA holds its next stores back until the fence of this stage has completed: a fence that has to
+    // outwait stores still being issued around it delayed the announcement by a whole stage)
+    __syncthreads();
+    if (threadIdx.x == 0) push_phase_done(p.sync, 0, n, kSyncQFlag, 0xffu, epoch);
+    __syncthreads();
+  }
+  // key and value rows in two stages (the peers that need them first, then the rest): a stage ends with
+  // one fence, and a fence costs a round trip to the peers, so there are few of them
+  int r = 0;
+  for (int stage = 0; stage < 2; ++stage) {
+    const int r_end = stage == 0 ? p.push_first : p.push_rounds;
+    if (r_end <= r) continue;
+    push_segments(2 * (r_end - r), p.push_vecs, first, stride, [&](int seg, const uint4*& src, uint4*& dst) {
+      const int dest = p.push_order[r + (seg >> 1)];
+      const int t = 1 + (seg & 1);
+      src = p.push_src[t] + dest * p.push_vecs;
+      dst = p.push_dst[t][dest];
+    });
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned dests = 0;
+      for (int i = r; i < r_end; ++i) dests |= 1u << p.push_order[i];
+      push_phase_done(p.sync, 1 + stage, n, kSyncInFlag, dests, epoch);
+    }
+    __syncthreads();
+    r = r_end;
+  }
+}
+
 #ifdef CHITU_ATTN_TIMING
 #define CHITU_TRACE(i)                                                                                       \
   do {                                                                                                       \
@@ -264,6 +354,7 @@ template <bool kFp16>
 #define CHITU_TRACE(i)
 #endif
 
+template <bool kFp16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -271,6 +362,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   if (threadIdx.x == 0) CHITU_TRACE(0);
+  const int n_qblocks = gridDim.x - p.push_x;
+  if (static_cast<int>(blockIdx.x) >= n_qblocks) {  // a copy CTA of push mode: no tensor memory, no barriers
+    push_rows(p, (blockIdx.x - n_qblocks) + p.push_x * (blockIdx.y + gridDim.y * blockIdx.z),
+              p.push_x * gridDim.y * gridDim.z);
+    if (threadIdx.x == 0) CHITU_TRACE(6);
+    return;
+  }
 
   const uint32_t q_smem = smem_base;                          // 2 tiles
   const uint32_t kv_smem = smem_base + kQTiles * kTileBytes;  // kStages tiles
@@ -307,6 +405,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (first_local >= kv0 && first_local < kv0 + n_kv &&
         (first_local + 1) * kTileN <= p.prefix_rows + (p.local_src + 1) * p.rows_per_src)
       rot = first_local - kv0;
+    else if (p.rot_other < n_kv)
+      rot = p.rot_other;
   }
 
   if (threadIdx.x == 0) {
@@ -348,16 +448,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     // arrival flags of the fused exchange: lane 0 remembers which source ranks it has already seen
-    uint32_t src_ready = 0;
+    // (push mode: the rank's own rows were put in place by the staging launch and have no flag; query rows
+    // and key / value rows are announced separately)
+    uint32_t src_ready = p.push_x > 0 ? 1u << p.local_src : 0u;
+    uint32_t q_ready = src_ready;
     const int flag_epoch = (p.in_flags != nullptr && lane == 0) ? *reinterpret_cast<const volatile int*>(p.in_epoch) : 0;
-    auto wait_rows = [&](int row_lo, int row_hi, int rows_total) {  // rows [row_lo, row_hi) of a gathered tensor
-      if (p.in_flags == nullptr) return;
+    auto wait_rows = [&](const int* flags, uint32_t& ready, int row_lo, int row_hi, int rows_total) {
+      // rows [row_lo, row_hi) of a gathered tensor
+      if (flags == nullptr) return;
       const int last = min(row_hi, rows_total) - 1 - p.prefix_rows;  // rows of the prefix are local
       if (last < 0) return;
       for (int src = max(row_lo - p.prefix_rows, 0) / p.rows_per_src; src <= last / p.rows_per_src; ++src) {
-        if ((src_ready >> src) & 1u) continue;
-        if (!wait_flag(p.in_flags + src, flag_epoch, p.flag_timeout, p.status)) *abort_flag = 1;
-        src_ready |= 1u << src;
+        if ((ready >> src) & 1u) continue;
+        if (!wait_flag(flags + src, flag_epoch, p.flag_timeout, p.status)) *abort_flag = 1;
+        ready |= 1u << src;
         CHITU_TRACE(1);
         // the rows were written by a peer's ordinary stores and are about to be read by the copy engine
         #if CHITU_FLAG_VARIANT != 3
@@ -366,7 +470,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     };
     if (lane == 0) {
-      wait_rows(q0, q0 + n_qt * kTileM, p.Sq);
+      wait_rows(p.push_x > 0 ? p.q_flags : p.in_flags, q_ready, q0, q0 + n_qt * kTileM, p.Sq);
+      CHITU_TRACE(7);
       for (int t = 0; t < n_qt; ++t) {
         mbar_arrive_expect_tx(bar_q_full + 8 * t, kTileBytes);
         tma_load_4d(q_smem + t * kTileBytes, &tm_q, bar_q_full + 8 * t, 0, head, q0 + t * kTileM, batch);
@@ -383,7 +488,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
         const int rel = (i >> 1) + rot;  // tile of this item relative to kv0, wrapped without a division
         const int row = (kv0 + (rel >= n_kv ? rel - n_kv : rel)) * kTileN;
-        wait_rows(row, row + kTileN, p.Sk);
+        wait_rows(p.in_flags, src_ready, row, row + kTileN, p.Sk);
         const uint32_t dst = kv_smem + slot * kTileBytes;
         const uint32_t bar = bar_kv_full + 8 * slot;
         mbar_arrive_expect_tx(bar, kTileBytes);
@@ -754,7 +859,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_dealloc(tmem_base, 512);
   }
   if (p.signal_out && threadIdx.x == 0)
-    publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, gridDim.x * gridDim.y * gridDim.z);
+    publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, n_qblocks * gridDim.y * gridDim.z);
   if (threadIdx.x == 0) CHITU_TRACE(6);
 }
 

@@ -166,7 +166,25 @@ struct Exchange {
   int prefix_rows = 0;
   void* const* prefix_ptrs = nullptr;
   int64_t prefix_batch_stride = 0, prefix_row_stride = 0, prefix_head_offset = 0;  // elements
+  const chitu_b200_push* push = nullptr;  // copy CTAs inside the attention launch
 };
+
+// Copy CTAs of push mode: extra blocks along x (each one adds H * B * n_splits CTAs) so that attention
+// and copy CTAs together are resident at once - one CTA per SM - and there are at least 8 and at most
+// 48 copy CTAs.  0: the shape does not qualify.
+int plan_push_x(int B, int Sq, int H, int n_splits) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return 0;
+  const long long per_x = static_cast<long long>(H) * B * n_splits;
+  const long long qblocks = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
+  const long long free_sms = sms - qblocks * per_x;
+  if (per_x <= 0 || free_sms < 8) return 0;
+  long long x = free_sms / per_x;
+  if (x * per_x > 48) x = 48 / per_x;
+  return x * per_x >= 8 ? static_cast<int>(x) : 0;
+}
 
 int fill_peer_sync(chitu::PeerSync* ps, const chitu_b200_peer_sync* sync, const char* what) {
   if (!sync || !sync->blocks || sync->world < 1 || sync->world > 8 || sync->rank < 0 || sync->rank >= sync->world)
@@ -330,6 +348,64 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     p.local_src = p.sync.rank;
     p.signal_out = n_splits == 1;
   }
+  p.push_x = p.push_rounds = p.push_first = p.rot_other = 0;
+  p.push_vecs = 0;
+  p.q_flags = nullptr;
+  for (int t = 0; t < 3; ++t) {
+    p.push_src[t] = nullptr;
+    for (int i = 0; i < 8; ++i) p.push_dst[t][i] = nullptr;
+  }
+  for (int i = 0; i < 8; ++i) p.push_order[i] = 0;
+  if (ex.push != nullptr) {
+    const int world = p.sync.world, me = p.sync.rank;
+    if (ex.sync == nullptr || world < 2) return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: needs a sync descriptor");
+    if (ex.prefix_rows != 0 || qpre != nullptr)
+      return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: no replicated prefix, no in-kernel q transform");
+    if (ex.push->block_bytes <= 0 || (ex.push->block_bytes & 15))
+      return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: block_bytes must be a positive multiple of 16");
+    p.push_x = plan_push_x(B, Sq, H, n_splits);
+    if (p.push_x == 0)
+      return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: the grid leaves no room for resident copy CTAs");
+    for (int t = 0; t < 3; ++t) {
+      if (t == 0 && !ex.push->stage[0]) continue;  // query rows were delivered by the staging launch
+      if (!ex.push->stage[t] || (reinterpret_cast<uintptr_t>(ex.push->stage[t]) & 15) || !ex.push->dest[t])
+        return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: staging area %d null or misaligned", t);
+      p.push_src[t] = static_cast<const uint4*>(ex.push->stage[t]);
+      for (int i = 0; i < world; ++i) {
+        if (i == me) continue;
+        if (!ex.push->dest[t][i] || (reinterpret_cast<uintptr_t>(ex.push->dest[t][i]) & 15))
+          return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: destination %d of tensor %d null or misaligned", i, t);
+        p.push_dst[t][i] = static_cast<uint4*>(ex.push->dest[t][i]);
+      }
+    }
+    p.push_vecs = ex.push->block_bytes / 16;
+    p.q_flags = p.sync.blocks[me] + chitu::kSyncQFlag;
+    // Serve the peers in the order in which they will ask for this rank's rows: receiver d walks the source
+    // ranks of a key range upwards, starting at itself where the range holds it, at the range's first
+    // source otherwise.
+    const int ranges = (world % n_splits == 0) ? n_splits : 1;
+    const int len = world / ranges;
+    int pos[8], n = 0;
+    for (int d = 0; d < world; ++d) {
+      if (d == me) continue;
+      const int lo = me / len * len;
+      pos[d] = (d / len == me / len) ? (me - d + len) % len : (me - lo - d % len + len) % len;
+      p.push_order[n++] = d;
+    }
+    for (int i = 1; i < n; ++i)  // insertion sort by (position in the receiver's walk, distance)
+      for (int j = i; j > 0; --j) {
+        const int a = p.push_order[j - 1], b = p.push_order[j];
+        const int da = (me - a + world) % world, db = (me - b + world) % world;
+        if (pos[a] < pos[b] || (pos[a] == pos[b] && da <= db)) break;
+        p.push_order[j - 1] = b;
+        p.push_order[j] = a;
+      }
+    p.push_rounds = n;
+    p.push_first = (n + 1) / 2;
+    // a CTA whose key range holds none of this rank's own rows starts its walk at a source that depends on
+    // the rank, so that the receivers do not all ask the same source first
+    p.rot_other = static_cast<int>((static_cast<long long>(me % len) * ex.rows_per_src) / chitu::kTileN);
+  }
 #ifdef CHITU_ATTN_TIMING
   p.dbg = g_dbg;
 #endif
@@ -341,7 +417,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
                 : ensure_dynamic_smem(chitu::attn_fwd_kernel<false>, chitu::kAttnSmemBytes, attr_done[0], attr_mu);
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
 
-  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B * n_splits);
+  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM) + p.push_x, H, B * n_splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p.is_fp16)
     chitu::attn_fwd_kernel<true><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
@@ -465,6 +541,39 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
                        dtype, status, stream, ks, ex);
 }
 
+int chitu_b200_push_ctas(int B, int Sq, int H, int n_splits) {
+  if (B <= 0 || Sq <= 0 || H <= 0 || n_splits < 1) return 0;
+  return plan_push_x(B, Sq, H, n_splits) * H * B * n_splits;
+}
+
+int chitu_b200_attn_fwd_exchange_push(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
+                                      int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
+                                      int64_t dest_head_offset, int B, int Sq, int Sk, int H, int D,
+                                      const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                      float softmax_scale, int dtype, int n_splits, void* workspace,
+                                      int64_t workspace_bytes, int rows_per_src, const chitu_b200_push* push,
+                                      const chitu_b200_peer_sync* sync, int* status, void* stream) {
+  KeySplit ks;
+  ks.n_splits = n_splits;
+  ks.workspace = workspace;
+  ks.workspace_bytes = workspace_bytes;
+  OutScatter sc;
+  sc.ptrs = out_ptrs;
+  sc.n_dest = n_dest;
+  sc.rows_per_dest = rows_per_dest;
+  sc.batch_stride = dest_batch_stride;
+  sc.row_stride = dest_row_stride;
+  sc.head_offset = dest_head_offset;
+  if (n_dest <= 0) return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: n_dest must be positive");
+  if (!sync || !push) return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: sync or push descriptor missing");
+  Exchange ex;
+  ex.sync = sync;
+  ex.rows_per_src = rows_per_src;
+  ex.push = push;
+  return attn_fwd_impl(q, k, v, nullptr, sc, nullptr, B, Sq, Sk, H, D, q_strides, k_strides, v_strides, softmax_scale,
+                       dtype, status, stream, ks, ex);
+}
+
 int chitu_b200_attn_fwd_qpre(const void* q_raw, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
                              int H, int D, const int64_t* q_strides, const int64_t* k_strides,
                              const int64_t* v_strides, float softmax_scale, int dtype, const chitu_b200_q_pre* q_pre,
@@ -524,7 +633,7 @@ struct NormRopeShared {
 };
 
 int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, const NormRopeShared& sh, void* stream,
-                            const chitu_b200_peer_sync* sync = nullptr) {
+                            const chitu_b200_peer_sync* sync = nullptr, bool stage_only = false) {
   if (!jobs || n_jobs < 1 || n_jobs > 3) return fail(CHITU_E_INVALID, "qk_norm_rope: 1..3 jobs per launch");
   if (!sh.out_strides) return fail(CHITU_E_INVALID, "qk_norm_rope: null pointer");
   const int B = sh.B, S = sh.S, H = sh.H, D = sh.D;
@@ -554,7 +663,7 @@ int qk_norm_rope_batch_impl(const chitu_b200_norm_rope_job* jobs, int n_jobs, co
   if (sync != nullptr) {
     const int rc = fill_peer_sync(&batch.sync, sync, "qk_norm_rope_batch_signal");
     if (rc != CHITU_OK) return rc;
-    batch.signal = 1;
+    batch.signal = stage_only ? 2 : 1;
   }
   for (int j = 0; j < n_jobs; ++j) {
     const chitu_b200_norm_rope_job& jb = jobs[j];
@@ -740,6 +849,17 @@ int chitu_b200_qk_norm_rope_batch_signal(const chitu_b200_norm_rope_job* jobs, i
   NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
                     out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
   return qk_norm_rope_batch_impl(jobs, n_jobs, sh, stream, sync);
+}
+
+int chitu_b200_qk_norm_rope_batch_stage(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
+                                        float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                                        const int* axis_split, int64_t pos_offset, int out_dtype,
+                                        const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                                        int round_mid, const chitu_b200_peer_sync* sync, void* stream) {
+  if (!sync) return fail(CHITU_E_INVALID, "qk_norm_rope_batch_stage: sync descriptor missing");
+  NormRopeShared sh{in_dtype, w_dtype,  eps,         rope_table,      table_rows, gf, gh, gw, axis_split, pos_offset,
+                    out_dtype, out_strides, heads_per_group, B, S, H, D, round_mid};
+  return qk_norm_rope_batch_impl(jobs, n_jobs, sh, stream, sync, /*stage_only=*/true);
 }
 
 int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* status, void* stream) {

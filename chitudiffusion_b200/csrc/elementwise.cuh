@@ -531,8 +531,13 @@ __device__ __forceinline__ void qk_norm_rope_body(const NormRopeBatch& batch) {
   qk_norm_rope_dispatch<kInDtype, kNormModeT, kRopeModeT>(batch, red);
   if (batch.signal) {
     __syncthreads();
-    if (threadIdx.x == 0)
-      publish_when_last(batch.sync, kSyncScatterDone, kSyncInEpoch, kSyncInFlag, gridDim.x * gridDim.y);
+    if (threadIdx.x == 0) {
+      if (batch.signal == 2)  // push mode: query rows went straight to the peers and are announced here; key and
+                              // value rows were staged locally, the attention launch's copy CTAs announce those
+        publish_when_last(batch.sync, kSyncScatterDone, kSyncInEpoch, kSyncQFlag, gridDim.x * gridDim.y);
+      else
+        publish_when_last(batch.sync, kSyncScatterDone, kSyncInEpoch, kSyncInFlag, gridDim.x * gridDim.y);
+    }
   }
 }
 

@@ -408,11 +408,14 @@ def qk_norm_rope_batch(
     out_dtype: torch.dtype = torch.bfloat16,
     round_mid: bool = True,
     sync=None,
+    stage_only: bool = False,
 ):
     """Up to three pre-attention jobs (q, k, v) in one launch; see ``chitu_b200_qk_norm_rope_batch``.
 
     With ``sync`` (a ``_lib.peer_sync_desc`` pair) the launch ends by announcing this rank's rows to its
-    peers (``chitu_b200_qk_norm_rope_batch_signal``).
+    peers (``chitu_b200_qk_norm_rope_batch_signal``); with ``stage_only`` as well it only advances the layer
+    epoch - its destinations are local, the attention launch's copy CTAs deliver and announce the rows
+    (``chitu_b200_qk_norm_rope_batch_stage``).
 
     Each job is a dict with ``x [B,S,H*D]``, optional ``weight``, ``norm_mode``, ``rope_mode`` and
     either ``out`` (tensor), ``out_ptrs`` (list of device addresses) or neither (a contiguous
@@ -483,7 +486,8 @@ def qk_norm_rope_batch(
         if sync is not None:
             import ctypes as _ct
 
-            rc = lib.chitu_b200_qk_norm_rope_batch_signal(*args, _ct.byref(sync[0]), _stream_ptr(x0.device))
+            fn = lib.chitu_b200_qk_norm_rope_batch_stage if stage_only else lib.chitu_b200_qk_norm_rope_batch_signal
+            rc = fn(*args, _ct.byref(sync[0]), _stream_ptr(x0.device))
         else:
             rc = lib.chitu_b200_qk_norm_rope_batch(*args, _stream_ptr(x0.device))
     _lib.check(rc, "qk_norm_rope_batch")
@@ -673,8 +677,11 @@ def attn_fwd_exchange(
     prefix_batch_stride: int = 0,
     prefix_row_stride: int = 0,
     prefix_head_offset: int = 0,
+    push=None,
 ) -> None:
-    """:func:`attn_fwd_scatter` over exchange buffers guarded by arrival flags; see ``chitu_b200_attn_fwd_exchange``."""
+    """:func:`attn_fwd_scatter` over exchange buffers guarded by arrival flags; see ``chitu_b200_attn_fwd_exchange``.
+    With ``push`` (a ``_lib.push_desc`` pair) the launch also delivers the staged rows to the peers
+    (``chitu_b200_attn_fwd_exchange_push``)."""
     import ctypes
 
     _require_cuda(q, k, v)
@@ -693,6 +700,20 @@ def attn_fwd_exchange(
         if ws.numel() * ws.element_size() < need or ws.device != q.device:
             raise ValueError(f"attn_fwd_exchange: workspace must hold {need} bytes on {q.device}")
         ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+    if push is not None:
+        if prefix_rows:
+            raise NotImplementedError("push mode has no replicated prefix")
+        with torch.cuda.device(q.device):
+            rc = lib.chitu_b200_attn_fwd_exchange_push(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr_array(out_ptrs), len(out_ptrs),
+                int(rows_per_dest), int(dest_batch_stride), int(dest_row_stride), int(dest_head_offset), B, Sq, Sk, H,
+                D, _lib.i64_array(q.stride()), _lib.i64_array(k.stride()), _lib.i64_array(v.stride()), scale,
+                _DTYPES[q.dtype], int(n_splits), ws_ptr, ws_bytes, int(rows_per_src), ctypes.byref(push[0]),
+                ctypes.byref(sync[0]), status_word(q.device).data_ptr(), _stream_ptr(q.device),
+            )
+        _lib.check(rc, "attn_fwd_exchange_push")
+        _launched(2 if n_splits > 1 and Sk > 128 else 1)
+        return
     with torch.cuda.device(q.device):
         rc = lib.chitu_b200_attn_fwd_exchange(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr_array(out_ptrs), len(out_ptrs), int(rows_per_dest),
@@ -705,6 +726,11 @@ def attn_fwd_exchange(
         )
     _lib.check(rc, "attn_fwd_exchange")
     _launched(2 if n_splits > 1 and Sk > 128 else 1)
+
+
+def push_ctas(B: int, Sq: int, H: int, n_splits: int) -> int:
+    """Copy CTAs that push mode would add to an attention launch of this shape on the current device (0: none)."""
+    return int(_lib.load().chitu_b200_push_ctas(int(B), int(Sq), int(H), int(n_splits)))
 
 
 def peer_wait_outputs(sync, device: torch.device) -> None:

@@ -106,11 +106,34 @@ class PeerUlysses:
         self.n_splits = ops.auto_key_splits(B, T + U * s, T + U * s, self.hc)
         need = ops.splitkv_workspace_bytes(B, T + U * s, self.hc, D, self.n_splits)
         self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=device) if self.n_splits > 1 else None
+        # Push mode: where the attention grid leaves SMs idle, only the query rows are stored straight to the
+        # peers; key and value rows for the peers are staged locally and copy CTAs inside the attention launch
+        # deliver them while the attention already runs
+        # (``chitu_b200_attn_fwd_exchange_push``).  One batch entry only: a staged block is the contiguous
+        # image of this rank's rows in a peer's buffer.
+        self.push = None
+        import os
 
-    def dest_ptrs(self, which: str, row_offset: int = 0):
-        """Per-destination base addresses for this rank's rows (from local row ``row_offset`` on) of q / k / v."""
+        if (B == 1 and T == 0 and os.environ.get("CHITU_B200_PUSH", "1") != "0"
+                and ops.push_ctas(B, U * s, self.hc, self.n_splits) > 0):
+            block = s * self._row_bytes
+            self._stage = torch.empty(3 * U * block, dtype=torch.uint8, device=device)
+            self._stage_ptrs = [self._stage.data_ptr() + t * U * block for t in range(3)]
+            self._block_bytes = block
+            dests = [[p + off + self._row0 for p in self.ptrs] for off in (self.off_q, self.off_k, self.off_v)]
+            self.push = _lib.push_desc([0] + self._stage_ptrs[1:], dests, block)
+
+    def dest_ptrs(self, which: str, row_offset: int = 0, direct: bool = False):
+        """Per-destination base addresses for this rank's rows (from local row ``row_offset`` on) of q / k / v.
+        In push mode (unless ``direct``) the peers' entries point into the local staging area."""
         off = {"q": self.off_q, "k": self.off_k, "v": self.off_v}[which]
-        return [p + off + self._row0 + row_offset * self._row_bytes for p in self.ptrs]
+        ptrs = [p + off + self._row0 + row_offset * self._row_bytes for p in self.ptrs]
+        if self.push is not None and not direct and which != "q":  # query rows go straight to the peers
+            t = ("q", "k", "v").index(which)
+            for d in range(self.U):
+                if d != self.rank:
+                    ptrs[d] = self._stage_ptrs[t] + d * self._block_bytes + row_offset * self._row_bytes
+        return ptrs
 
     def barrier(self) -> None:
         ops.peer_barrier(self.flag_ptrs, self.rank, self.U, self.device)
@@ -119,7 +142,7 @@ class PeerUlysses:
         """``x [B, s, H*D]`` (or ``[B,s,H,D]``) 16-bit: copy each head group to its owner (no announcement)."""
         flat = x.reshape(self.B, self.s, self.H * self.D)
         ops.qk_norm_rope(flat, self.H, None, 0.0, norm_mode=2, rope_mode=0, rope_table=None,
-                         out_ptrs=self.dest_ptrs(which), out_strides=self.gather_strides,
+                         out_ptrs=self.dest_ptrs(which, direct=True), out_strides=self.gather_strides,
                          heads_per_group=self.hc, out_dtype=self.dtype)
 
     def scatter_qkv(self, jobs, v: torch.Tensor, row_offset: int = 0, last: bool = True, **batch_args) -> None:
@@ -142,14 +165,15 @@ class PeerUlysses:
         for j, which in zip(jobs, ("q", "k", "v")):
             j["out_ptrs"] = self.dest_ptrs(which, row_offset)
         ops.qk_norm_rope_batch(jobs, out_strides=self.gather_strides, heads_per_group=self.hc, out_dtype=self.dtype,
-                               sync=self.sync if last else None, **batch_args)
+                               sync=self.sync if last else None, stage_only=self.push is not None, **batch_args)
 
     def scatter_ready(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         """q, k, v ``[B, s, H, D]`` that are already normalised and rotated: one launch of three plain jobs."""
         jobs = [dict(x=t.reshape(self.B, self.s, self.H * self.D), norm_mode=2, rope_mode=0,
                      out_ptrs=self.dest_ptrs(w)) for t, w in ((q, "q"), (k, "k"), (v, "v"))]
         ops.qk_norm_rope_batch(jobs, num_heads=self.H, eps=0.0, rope_table=None, out_strides=self.gather_strides,
-                               heads_per_group=self.hc, out_dtype=self.dtype, sync=self.sync)
+                               heads_per_group=self.hc, out_dtype=self.dtype, sync=self.sync,
+                               stage_only=self.push is not None)
 
     def scatter_prefix(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         """Replicated rows ``[B, T, H, D]`` (every rank holds the same ones): this rank's head group of them goes
@@ -192,7 +216,7 @@ class PeerUlysses:
             self.q, self.k, self.v, [p + slot_off for p in self.ptrs], rows_per_dest=self.s,
             dest_batch_stride=self.s * self.H * self.D, dest_row_stride=self.H * self.D,
             dest_head_offset=self.rank * self.hc * self.D, rows_per_src=self.s, sync=self.sync,
-            softmax_scale=softmax_scale, n_splits=self.n_splits, workspace=self.workspace,
+            softmax_scale=softmax_scale, n_splits=self.n_splits, workspace=self.workspace, push=self.push,
         )
         ops.peer_wait_outputs(self.sync, self.device)
         self.out = self.outs[self._out_slot]

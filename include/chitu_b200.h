@@ -388,6 +388,45 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
 int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, void* stream);
 
 /*
+ * Push mode: the same exchange with the transfer overlapped with the attention itself, for grids that
+ * leave SMs idle (a few hundred query rows per rank: Flux on 4 or 8 GPUs).  (Same reference lines; what it
+ * replaces in addition is the overlap the reference gets from its side-stream all-to-all in
+ * attention_fused, diffusion_attn_backend.py:638-737.)
+ *
+ * chitu_b200_qk_norm_rope_batch_stage: chitu_b200_qk_norm_rope_batch_signal that announces QUERY rows only
+ *   (a flag of their own): point the q job's out_ptrs at the peers' gathered buffers as before, and the k and
+ *   v jobs' at LOCAL memory - this rank's own head group in its own gathered buffers, the other groups in a
+ *   staging area, block d (block_bytes) holding the rows for rank d in the layout they will have there.
+ * chitu_b200_attn_fwd_exchange_push: chitu_b200_attn_fwd_exchange whose grid is extended by copy CTAs
+ *   that move the staged blocks into the peers' buffers while the attention CTAs already run: key and
+ *   value rows in the order in which the receivers walk their keys, in two stages announced by flags
+ *   (stage[0] non-null: the query rows as well, first, for a staging launch that kept them local).  The attention CTAs wait per source rank for the
+ *   query rows of their block and for each key / value block as they reach it; this rank's own rows are
+ *   already in place.  Refused (CHITU_E_UNSUPPORTED) unless the whole grid - attention CTAs and copy CTAs -
+ *   is resident at once; chitu_b200_push_ctas says how many copy CTAs a shape gets (0: use
+ *   chitu_b200_attn_fwd_exchange).  dest[t][d] is where this rank's block starts in rank d's gathered
+ *   q (t = 0), k (1), v (2); entry `rank` is ignored.
+ */
+typedef struct {
+  const void* stage[3];
+  void* const* dest[3];
+  int64_t block_bytes; /* multiple of 16 */
+} chitu_b200_push;
+int chitu_b200_push_ctas(int B, int Sq, int H, int n_splits);
+int chitu_b200_qk_norm_rope_batch_stage(const chitu_b200_norm_rope_job* jobs, int n_jobs, int in_dtype, int w_dtype,
+                                        float eps, const float* rope_table, int table_rows, int gf, int gh, int gw,
+                                        const int* axis_split, int64_t pos_offset, int out_dtype,
+                                        const int64_t* out_strides, int heads_per_group, int B, int S, int H, int D,
+                                        int round_mid, const chitu_b200_peer_sync* sync, void* stream);
+int chitu_b200_attn_fwd_exchange_push(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,
+                                      int rows_per_dest, int64_t dest_batch_stride, int64_t dest_row_stride,
+                                      int64_t dest_head_offset, int B, int Sq, int Sk, int H, int D,
+                                      const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                      float softmax_scale, int dtype, int n_splits, void* workspace,
+                                      int64_t workspace_bytes, int rows_per_src, const chitu_b200_push* push,
+                                      const chitu_b200_peer_sync* sync, int* status, void* stream);
+
+/*
  * Clock budget (GPU cycles) of the flag waits in chitu_b200_peer_barrier and in the arrival-flag
  * polls of the fused exchange; applies to launches made after the call, process-wide.  Returns the
  * previous budget; a non-positive argument only queries.  The default, 2^31 cycles, is about a second -

@@ -137,6 +137,16 @@ def main():
             px.scatter_qkv(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
         out = px.attention()
         results[f"peer{rep}"] = rel_err(out, ref2[:, sl])
+    # this small grid leaves SMs idle, so the object above delivered its rows with copy CTAs inside the attention
+    # launch; the same layer with that mode switched off: stores straight to the peers, one flag per rank
+    assert px.push is not None, "push mode was expected for this shape"
+    os.environ["CHITU_B200_PUSH"] = "0"
+    px_direct = PeerUlysses(comm.get_up_group(world), 1, s, H, D, torch.bfloat16, dev)
+    os.environ.pop("CHITU_B200_PUSH")
+    assert px_direct.push is None
+    for rep in range(2):
+        px_direct.scatter_qkv(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
+        results[f"direct{rep}"] = rel_err(px_direct.attention(), ref2[:, sl])
     # the same through the wrapper's projections-in entry, whole and in two row pieces (as Flux's two streams arrive)
     wrapper = B200ContextParallel(backend, world, cp_backend="ucp")
     lq, lk, lv = (t[:, sl].contiguous().to(dev) for t in (xq, xk, xv))
