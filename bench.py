@@ -616,6 +616,119 @@ def measure_flux_dit(rank, world, device, exchange, sync, dist, steps=3):
             "weights": "random-init N(0, 0.02^2) bf16, bf16 residual streams; GEMMs are library calls"}
 
 
+def measure_qwen_dit(rank, world, device, sync, dist, blocks=12, steps=2):
+    """Latency of random-init Qwen-Image MMDiT blocks (hidden 3072, 24 heads; 256 text tokens replicated, 83 x 83
+    image tokens sharded and zero-padded over the ranks) through the processor mirror: ``blocks`` of the model's 60
+    are built and timed, the 60-block figure is the multiple (all blocks are alike)."""
+    from chitudiffusion_b200 import B200AttnBackend, comm
+    from chitudiffusion_b200.context_parallel import B200ContextParallel
+    from chitudiffusion_b200.dispatch import SequencePadder
+    from chitudiffusion_b200.qwen import QwenDiTStack
+
+    H, D, n_img, n_txt = 24, 128, 83 * 83, 256
+    C = H * D
+    backend = B200AttnBackend("b200")
+    attn, parallelism, info = backend, "single", None
+    gen = torch.Generator().manual_seed(77)  # every rank builds the same full tensors
+    img_full = torch.randn(1, n_img, C, generator=gen).to(torch.bfloat16)
+    txt = torch.randn(1, n_txt, C, generator=gen).to(torch.bfloat16).to(device)
+    temb = torch.randn(1, C, generator=gen).to(torch.bfloat16).to(device)
+    ang_i = torch.rand(n_img, D // 2, generator=gen, dtype=torch.float64) * 6.0
+    ang_t = torch.rand(n_txt, D // 2, generator=gen, dtype=torch.float64) * 6.0
+    rotary = (torch.polar(torch.ones_like(ang_i), ang_i).to(device), torch.polar(torch.ones_like(ang_t), ang_t).to(device))
+    img = img_full.to(device)
+    if world > 1:
+        comm.destroy_diffusion_parallel_groups()
+        comm.initialize_diffusion_parallel_groups(1, world, world)
+        attn = B200ContextParallel(backend, world, cp_backend="ucp")
+        img = SequencePadder.split_sequence_padding(img_full, world, 1)[rank].contiguous().to(device)
+        info = {"image_offset": rank * img.shape[1], "image_seq_len": n_img}
+        parallelism = f"ulysses{world} (replicated text, peer stores)"
+    stack = QwenDiTStack(blocks, C, H, device, attn, seed=5)
+    holder = {}
+
+    def run():
+        holder["out"] = stack(img, txt, temb, rotary, info)
+
+    run()
+    sync()
+    graph = torch.cuda.CUDAGraph()  # no NCCL call on this path: the pass replays from a graph on any number of GPUs
+    with torch.cuda.graph(graph):
+        run()
+    graph.replay()
+    sync()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        graph.replay()
+    t1.record()
+    sync()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        comm.destroy_diffusion_parallel_groups()
+    ms_block = float(ms.item()) / (steps * blocks)
+    S = n_img + n_txt
+    # per token and block, both streams alike: qkv 3C^2 + out C^2 + MLP 8C^2 multiply-adds
+    flops = 4.0 * S * S * D * H + 2.0 * S * 12 * C * C
+    return {"workload": "qwen-image-1328-dit-step", "blocks_timed": blocks, "blocks_in_model": 60, "seq_len": S, "hidden": C,
+            "ms_per_block": round(ms_block, 3), "step_ms_60_blocks": round(60 * ms_block, 2),
+            "tflops": round(flops / (ms_block * 1e-3) / 1e12, 1),
+            "attention_share_of_flops": round(4.0 * S * S * D * H / flops, 3), "parallelism": parallelism,
+            "cuda_graph": True, "finite": bool(all(torch.isfinite(o.float()).all().item() for o in holder["out"])),
+            "weights": "random-init N(0, 0.02^2) bf16, bf16 residual streams; GEMMs are library calls"}
+
+
+def measure_layer_timeline(pipe, dev_sets, sync, dist):
+    """Per-launch timeline of one layer on the peer-store Ulysses path: the step is captured in a graph with
+    timer stamps between the launches of every layer (``chitu_b200_stamp``), replayed, and the medians over the
+    layers are reported: the staging / scatter launch, the attention launch(es) - which in push mode also
+    deliver the key and value rows - the wait for every rank's outputs, and the gap to the next layer."""
+    from chitudiffusion_b200 import ops
+
+    qp = dev_sets[0][0]
+    px = pipe.attn.peer_exchange(qp.shape[0], qp.shape[1], pipe.H, pipe.D, torch.bfloat16, pipe.device)
+    blocks = pipe.w["blocks"]
+    slots = torch.zeros(blocks * 4, dtype=torch.int64, device=pipe.device)
+    layer = [0]
+
+    def trace(point):
+        ops.stamp(slots, 4 * layer[0] + point)
+        if point == 3:
+            layer[0] += 1
+
+    px.trace = trace
+    try:
+        sync()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph):
+            pipe.step(dev_sets)
+        per_layer = (ops.launch_count - before) / blocks
+    finally:
+        px.trace = None
+    for _ in range(3):
+        graph.replay()
+    sync()
+    t = slots.cpu().view(blocks, 4).double() / 1e3
+    skip = min(5, blocks // 2)
+
+    def med(x):
+        return round(float(x[skip:].median().item()), 1)
+
+    res = {"launches_per_layer": per_layer, "stage_or_scatter_us": med(t[:, 1] - t[:, 0]),
+           "attention_us": med(t[:, 2] - t[:, 1]), "wait_outputs_us": med(t[:, 3] - t[:, 2]),
+           "gap_us": med(t[1:, 0] - t[:-1, 3]) if blocks > 1 else 0.0,
+           "layer_us": round(float((t[-1, 3] - t[skip, 0]).item() / (blocks - skip)), 1),
+           "mode": "push (copy CTAs inside the attention launch)" if px.push is not None else "direct peer stores",
+           "key_splits": px.n_splits, "rank": pipe.rank,
+           "note": "timer stamps add one tiny launch between the kernels; compare with ms_per_step / blocks"}
+    gathered = [None] * pipe.world
+    dist.all_gather_object(gathered, res["layer_us"])
+    res["layer_us_max_over_ranks"] = max(gathered)
+    return res
+
+
 def measure_library_sdpa(pipe, dev_sets, w, sync):
     """torch's scaled_dot_product_attention (whatever fused backend it picks, and cuDNN's when it can be
     forced) on the same post-transform q/k/v, cycled over the same input sets, timed the same way.  Context
@@ -830,6 +943,9 @@ def run_ours(args):
 
     library = None
     pre_modes = None
+    timeline = None
+    if world > 1 and use_graph and not args.profile and pipe.parallelism.endswith("-peer-stores"):
+        timeline = measure_layer_timeline(pipe, dev_sets, sync, dist)
     if world == 1 and not args.profile and args.attn == "b200":
         library = measure_library_sdpa(pipe, dev_sets, w, sync)
         # the two placements of q's norm + rotary transform, same step, same inputs: inside the attention
@@ -878,6 +994,9 @@ def run_ours(args):
         for n in [x.strip() for x in args.dit.split(",") if x.strip()]:
             if n.startswith("flux"):
                 dit.append(measure_flux_dit(rank, world, device, args.exchange, sync, dist))
+            elif n.startswith("qwen"):
+                if args.exchange == "peer":
+                    dit.append(measure_qwen_dit(rank, world, device, sync, dist))
             else:
                 dit.append(measure_dit(n, rank, world, device, args.exchange, sync, dist))
 
@@ -946,6 +1065,8 @@ def run_ours(args):
         line["library_sdpa"] = library
     if pre_modes is not None:
         line["pre_attention_placement"] = pre_modes
+    if timeline is not None:
+        line["layer_timeline"] = timeline
     if dit:
         line["dit_step"] = dit
     if nvlink:
@@ -1049,7 +1170,7 @@ def main():
                     help="N > 1: context-parallel layout (auto = the widest Ulysses degree the head count allows)")
     ap.add_argument("--extra-layouts", default="ring,agkv,usp",
                     help="N > 1: comma-separated layouts (ring, agkv, usp) timed on the Wan2.1-14B 720p layer besides Ulysses")
-    ap.add_argument("--dit", default="flux1-dev-1024,wan1.3b-480p-81f",
+    ap.add_argument("--dit", default="flux1-dev-1024,wan1.3b-480p-81f,qwen-image-1328",
                     help="comma-separated workloads (flux1-dev-1024 or a Wan workload) whose full DiT pass latency "
                          "is reported too ('' = none)")
     ap.add_argument("--no-extra", action="store_true", help="skip the second (Wan2.1-14B 720p) workload")

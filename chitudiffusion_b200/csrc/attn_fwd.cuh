@@ -77,14 +77,14 @@ struct AttnParams {
   long long flag_timeout;
   PeerSync sync;
   int signal_out;
-  // Push mode (push_x > 0): the rows this rank owes its peers are staged in local memory, and the CTAs with
-  // blockIdx.x >= gridDim.x - push_x do no attention: they copy the staged rows into the peers' buffers
-  // while the attention CTAs of the same launch already work - the query rows for every peer first, where
-  // the staging launch has not delivered them itself (push_src[0] != nullptr; announced in q_flags), then
-  // key and value rows in push_order, the order in which the receivers walk their keys: the first
-  // push_first peers, then the others (announced in in_flags).  The rank's own rows are already in place (the
-  // staging launch wrote them) and have no flag.  The host only chooses this mode when the whole grid is
-  // resident at once, so a waiting attention CTA never keeps a copy CTA off the machine.
+  // Push mode (push_x > 0): key and value rows this rank owes its peers are staged in local memory, and the
+  // CTAs with blockIdx.x < push_x (the first to be given an SM) do no attention: they copy the staged rows
+  // into the peers' buffers while the attention CTAs of the same launch already work - in push_order, the
+  // order in which the receivers walk their keys: the first push_first peers, then the others (announced
+  // in in_flags).  Query rows are normally delivered and announced (q_flags) by the staging launch itself;
+  // push_src[0] != nullptr makes the copy CTAs send them too, first.  The rank's own rows are already in
+  // place and have no flag.  Copy CTAs never wait for anything, and the host only chooses this mode when
+  // the whole grid is resident at once, so a waiting attention CTA never keeps a copy CTA off the machine.
   int push_x, push_rounds, push_first, rot_other;
   int push_order[8];
   const uint4* push_src[3];  // staged q, k, v: block d (push_vecs 16-byte vectors) holds the rows for rank d
@@ -363,8 +363,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   if (threadIdx.x == 0) CHITU_TRACE(0);
   const int n_qblocks = gridDim.x - p.push_x;
-  if (static_cast<int>(blockIdx.x) >= n_qblocks) {  // a copy CTA of push mode: no tensor memory, no barriers
-    push_rows(p, (blockIdx.x - n_qblocks) + p.push_x * (blockIdx.y + gridDim.y * blockIdx.z),
+  if (static_cast<int>(blockIdx.x) < p.push_x) {  // a copy CTA of push mode: no tensor memory, no barriers
+    push_rows(p, blockIdx.x + p.push_x * (blockIdx.y + gridDim.y * blockIdx.z),
               p.push_x * gridDim.y * gridDim.z);
     if (threadIdx.x == 0) CHITU_TRACE(6);
     return;
@@ -389,7 +389,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * (kQTiles * kTileM);
+  const int q0 = (static_cast<int>(blockIdx.x) - p.push_x) * (kQTiles * kTileM);
   const int head = blockIdx.y;
   const int batch = blockIdx.z / p.n_splits;
   const int split = blockIdx.z - batch * p.n_splits;
@@ -631,7 +631,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #endif
           mbar_wait(bar_q_full + 8 * t, 0, abort_flag, p.status, kDevTimeoutSoftmax);
 #ifdef CHITU_ATTN_TIMING
-          if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+          if (p.dbg != nullptr && static_cast<int>(blockIdx.x) == p.push_x && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
             p.dbg[24] = qt1 - qt0;
             p.dbg[25] = clock64() - qt1;
             qt1 = clock64();
@@ -641,7 +641,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         fence_proxy_async_smem();  // the rewritten tile is read by the tensor core through the async proxy
         mbar_arrive(bar_q_ready + 8 * t);
 #ifdef CHITU_ATTN_TIMING
-        if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0)
+        if (p.dbg != nullptr && static_cast<int>(blockIdx.x) == p.push_x && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0)
           p.dbg[26] = clock64() - qt1;
 #endif
       }
@@ -756,7 +756,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         l_sum += (la.x + la.y) + (lb.x + lb.y);
       }
 #ifdef CHITU_ATTN_TIMING
-      if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
+      if (p.dbg != nullptr && static_cast<int>(blockIdx.x) == p.push_x && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
         p.dbg[t * 4 + 0] = tw; p.dbg[t * 4 + 1] = tl; p.dbg[t * 4 + 2] = tm; p.dbg[t * 4 + 3] = ts;
       }
 #endif

@@ -879,6 +879,14 @@ int chitu_b200_peer_barrier(int* const* flag_ptrs, int rank, int world, int* sta
   return CHITU_OK;
 }
 
+int chitu_b200_stamp(unsigned long long* slot, void* stream) {
+  if (!slot || (reinterpret_cast<uintptr_t>(slot) & 7)) return fail(CHITU_E_INVALID, "stamp: slot null or misaligned");
+  chitu::stamp_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(slot);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "stamp: launch");
+  return CHITU_OK;
+}
+
 long long chitu_b200_set_flag_wait_cycles(long long cycles) {
   const long long old = g_flag_wait_cycles;
   if (cycles > 0) g_flag_wait_cycles = cycles;

@@ -122,6 +122,13 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long long 
   return true;
 }
 
+// Measurement aid: the GPU's nanosecond timer at the moment this launch ran.
+__global__ void stamp_kernel(unsigned long long* slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *slot = t;
+}
+
 // One warp: lane i waits for peer i's output flag of the next layer, then the epoch advances.
 __global__ void peer_wait_outputs_kernel(const PeerSync ps, int* status) {
   int* mine = ps.blocks[ps.rank];

@@ -728,6 +728,18 @@ def attn_fwd_exchange(
     _launched(2 if n_splits > 1 and Sk > 128 else 1)
 
 
+def stamp(slots: torch.Tensor, index: int) -> None:
+    """Enqueue a launch that writes the GPU's nanosecond timer into ``slots[index]`` (int64 tensor on the GPU);
+    works inside a captured graph.  Not counted as a launch of the hot path."""
+    if slots.dtype != torch.int64 or not slots.is_cuda or not slots.is_contiguous():
+        raise ValueError("stamp: slots must be a contiguous int64 CUDA tensor")
+    if not 0 <= index < slots.numel():
+        raise IndexError("stamp: index out of range")
+    with torch.cuda.device(slots.device):
+        rc = _lib.load().chitu_b200_stamp(slots.data_ptr() + 8 * int(index), _stream_ptr(slots.device))
+    _lib.check(rc, "stamp")
+
+
 def push_ctas(B: int, Sq: int, H: int, n_splits: int) -> int:
     """Copy CTAs that push mode would add to an attention launch of this shape on the current device (0: none)."""
     return int(_lib.load().chitu_b200_push_ctas(int(B), int(Sq), int(H), int(n_splits)))

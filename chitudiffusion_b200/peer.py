@@ -112,6 +112,9 @@ class PeerUlysses:
         # (``chitu_b200_attn_fwd_exchange_push``).  One batch entry only: a staged block is the contiguous
         # image of this rank's rows in a peer's buffer.
         self.push = None
+        self.trace = None  # optional callable(point): 0 before the first launch of a layer, 1 after the last
+        #                    staging / scatter launch, 2 after the attention launch(es), 3 after the wait
+        self._layer_open = False
         import os
 
         if (B == 1 and T == 0 and os.environ.get("CHITU_B200_PUSH", "1") != "0"
@@ -154,6 +157,9 @@ class PeerUlysses:
         """
         jobs = [dict(j) for j in jobs]
         batch_args.pop("out_dtype", None)  # the exchange buffers fix the store type
+        if self.trace is not None and not self._layer_open:
+            self.trace(0)
+        self._layer_open = not last
         rows = jobs[0]["x"].shape[1]
         if v.dtype == jobs[0]["x"].dtype:
             jobs.append(dict(x=v.reshape(self.B, rows, self.H * self.D), norm_mode=2, rope_mode=0))
@@ -166,6 +172,8 @@ class PeerUlysses:
             j["out_ptrs"] = self.dest_ptrs(which, row_offset)
         ops.qk_norm_rope_batch(jobs, out_strides=self.gather_strides, heads_per_group=self.hc, out_dtype=self.dtype,
                                sync=self.sync if last else None, stage_only=self.push is not None, **batch_args)
+        if self.trace is not None and last:
+            self.trace(1)
 
     def scatter_ready(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         """q, k, v ``[B, s, H, D]`` that are already normalised and rotated: one launch of three plain jobs."""
@@ -218,7 +226,11 @@ class PeerUlysses:
             dest_head_offset=self.rank * self.hc * self.D, rows_per_src=self.s, sync=self.sync,
             softmax_scale=softmax_scale, n_splits=self.n_splits, workspace=self.workspace, push=self.push,
         )
+        if self.trace is not None:
+            self.trace(2)
         ops.peer_wait_outputs(self.sync, self.device)
+        if self.trace is not None:
+            self.trace(3)
         self.out = self.outs[self._out_slot]
         return self.out
 

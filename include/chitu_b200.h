@@ -436,6 +436,13 @@ int chitu_b200_attn_fwd_exchange_push(const void* q, const void* k, const void* 
  */
 long long chitu_b200_set_flag_wait_cycles(long long cycles);
 
+/*
+ * Measurement aid, no reference counterpart: a one-thread kernel that writes the GPU's nanosecond timer
+ * (%globaltimer) into *slot.  Enqueued between the launches of a layer - also inside a captured graph,
+ * where events cannot be read back - it gives the per-launch timeline that bench.py reports.
+ */
+int chitu_b200_stamp(unsigned long long* slot, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
