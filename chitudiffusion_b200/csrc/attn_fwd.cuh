@@ -58,10 +58,16 @@ struct AttnParams {
   int rows_per_dest;
   long long dest_batch_bytes, dest_row_bytes, dest_head_bytes;
   // Split over keys (under-filled grids): blockIdx.z = batch * n_splits + split; split s takes
-  // key tiles [s * tiles_per_split, (s+1) * tiles_per_split).  With n_splits > 1 each CTA writes a
-  // normalised fp32 partial result and its log-sum-exp to scratch memory for the combine kernel:
-  //   part_o [n_splits][B][Sq][H][128] fp32,  part_lse [n_splits][B][H][Sq] fp32 (natural log)
+  // key tiles [s * tiles_per_split, (s+1) * tiles_per_split).  With n_splits > 1 each CTA parks the
+  // normalised fp32 rows of its key range and their log-sum-exps in scratch memory and bumps the
+  // counter of its (batch, head, query block); the CTA that completes the count - the last of the
+  // n_splits to finish - merges all ranges and writes the result, so no second launch is needed:
+  //   split_count [batch][head][query block] int32, zero between calls (the merging CTA resets it)
+  //   part_o   [n_splits][tile][32 chunks][128 rows] float4  (tile = ((batch * H + head) * query blocks
+  //            + block) * 2 + t; chunk-major so that a warp's 32 rows are 512 contiguous bytes)
+  //   part_lse [n_splits][tile][128 rows] fp32 (natural log)
   int n_splits, tiles_per_split;
+  int* split_count;
   float* part_o;
   float* part_lse;
   // Fused exchange (in_flags != nullptr): the rows of q / k / v were stored into this GPU's buffers by
@@ -384,12 +390,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
   const uint32_t bar_drain = smem_u32(tail + 16);  // only used when a wait has run out (see the MMA warp's exit)
+  volatile int* merge_flag = reinterpret_cast<volatile int*>(tail + 40);  // this CTA merges the key ranges
   const uint32_t bar_q_ready = smem_u32(tail + 24);  // [2] a query tile has been transformed in place (128 arrivals)
   const bool q_fuse = p.q_norm_mode != 2 || p.q_rope_mode != 0;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q0 = (static_cast<int>(blockIdx.x) - p.push_x) * (kQTiles * kTileM);
+  const int qblock = static_cast<int>(blockIdx.x) - p.push_x;
+  const int q0 = qblock * (kQTiles * kTileM);
   const int head = blockIdx.y;
   const int batch = blockIdx.z / p.n_splits;
   const int split = blockIdx.z - batch * p.n_splits;
@@ -782,47 +790,102 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_ptrs[dest]) + batch * p.dest_batch_bytes +
                                        local_row * p.dest_row_bytes + p.dest_head_bytes + head * (kHeadDim * 2));
       }
-      if (p.n_splits > 1) {
-        // partial result of this key range: normalised fp32 rows + log-sum-exp for the combine kernel
-        float4* pdst = reinterpret_cast<float4*>(
-            p.part_o + (((static_cast<size_t>(split) * p.B + batch) * p.Sq + row) * p.H + head) * kHeadDim);
+      uint8_t* stage = smem_gen + t * kTileBytes;
+      // a 32-column piece of the final row, packed and parked in this query tile's shared memory
+      auto park = [&](int c, const float (&f)[32]) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = pack2<kFp16>(f[i], f[i + 1]);
+          v.y = pack2<kFp16>(f[i + 2], f[i + 3]);
+          v.z = pack2<kFp16>(f[i + 4], f[i + 5]);
+          v.w = pack2<kFp16>(f[i + 6], f[i + 7]);
+          const int chunk = c * 4 + (i >> 3);
+          *reinterpret_cast<uint4*>(stage + row_in_tile * 256 + ((chunk ^ (row_in_tile & 7)) << 4)) = v;
+        }
+      };
+      float lse_row = (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
+      bool write_out = true;
+      if (p.n_splits == 1) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
           tmem_ld32(t_o + c * 32, o);
           tmem_wait_ld();
-          if (row < p.Sq) {
+          float f[32];
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              pdst[c * 8 + (i >> 2)] = make_float4(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l,
-                                                   __uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * inv_l;
+          park(c, f);
+        }
+      } else {
+        // (1) this key range's normalised rows and log-sum-exp go to scratch
+        const size_t tiles_total = static_cast<size_t>(p.B) * p.H * n_qblocks * 2;
+        const size_t tile_id = ((static_cast<size_t>(batch) * p.H + head) * n_qblocks + qblock) * 2 + t;
+        float4* mine = reinterpret_cast<float4*>(p.part_o) + (split * tiles_total + tile_id) * (32 * kTileM) + row_in_tile;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(t_o + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            mine[(c * 8 + (i >> 2)) * kTileM] =
+                make_float4(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l,
+                            __uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+        }
+        p.part_lse[(split * tiles_total + tile_id) * kTileM + row_in_tile] = lse_row;
+        // (2) the CTA's softmax threads meet; one of them counts the CTA in and learns whether it is the
+        //     last of the n_splits that share this query block
+        asm volatile("bar.sync 1, %0;" ::"r"(n_qt * kTileM) : "memory");
+        if (threadIdx.x == 0) {
+          __threadfence();
+          int* counter = p.split_count + (static_cast<size_t>(batch) * p.H + head) * n_qblocks + qblock;
+          const int prev = atomicAdd(counter, 1);
+          const int last = prev + 1 == p.n_splits;
+          if (last) *counter = 0;
+          __threadfence();
+          *merge_flag = last;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(n_qt * kTileM) : "memory");
+        write_out = *merge_flag != 0;
+        if (write_out) {
+          // (3) merge: out = sum_i exp(lse_i - lse) * part_i, lse = log sum_i exp(lse_i)
+          const float* lses = p.part_lse + tile_id * kTileM + row_in_tile;
+          const size_t lse_stride = tiles_total * kTileM;
+          float mx = -INFINITY;
+          for (int i = 0; i < p.n_splits; ++i) mx = fmaxf(mx, __ldcg(lses + i * lse_stride));
+          float wsum = 0.f;
+          for (int i = 0; i < p.n_splits; ++i) wsum += expf(__ldcg(lses + i * lse_stride) - mx);
+          const float inv_w = 1.0f / wsum;
+          lse_row = mx + logf(wsum);
+          const float4* parts = reinterpret_cast<const float4*>(p.part_o) + tile_id * (32 * kTileM) + row_in_tile;
+          const size_t part_stride = tiles_total * (32 * kTileM);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = 0.f;
+            for (int s_i = 0; s_i < p.n_splits; ++s_i) {
+              const float w = expf(__ldcg(lses + s_i * lse_stride) - mx) * inv_w;
+              const float4* src = parts + s_i * part_stride + (c * 8) * kTileM;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 v = __ldcg(src + j * kTileM);
+                f[4 * j] = fmaf(w, v.x, f[4 * j]);
+                f[4 * j + 1] = fmaf(w, v.y, f[4 * j + 1]);
+                f[4 * j + 2] = fmaf(w, v.z, f[4 * j + 2]);
+                f[4 * j + 3] = fmaf(w, v.w, f[4 * j + 3]);
+              }
+            }
+            park(c, f);
           }
         }
-        if (row < p.Sq)
-          p.part_lse[((static_cast<size_t>(split) * p.B + batch) * p.H + head) * p.Sq + row] =
-              (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
-      } else {
+      }
+      if (write_out) {
         // Rows go out through this query tile's shared memory (its last reader, the final QK^T, has completed):
-        // each thread parks its 256-byte row there, then the warp stores its own 32 rows two at a time, 512
+        // each thread has parked its 256-byte row there, now the warp stores its own 32 rows two at a time, 512
         // contiguous bytes per instruction.  A row per thread straight to global memory would leave the SM as
         // 16-byte pieces, which peer stores over NVLink carry at a fraction of the link rate.
-        uint8_t* stage = smem_gen + t * kTileBytes;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(t_o + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            v.x = pack2<kFp16>(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-            v.y = pack2<kFp16>(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-            v.z = pack2<kFp16>(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-            v.w = pack2<kFp16>(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-            const int chunk = c * 4 + (i >> 3);
-            *reinterpret_cast<uint4*>(stage + row_in_tile * 256 + ((chunk ^ (row_in_tile & 7)) << 4)) = v;
-          }
-        }
         __syncwarp();
         const unsigned long long my_dst = row < p.Sq ? reinterpret_cast<unsigned long long>(dst) : 0ull;
         const int chunk = lane & 15;
@@ -844,10 +907,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       if (t == 0 && row_in_tile == 0) CHITU_TRACE(4);
-      if (p.n_splits == 1 && p.lse != nullptr && row < p.Sq) {
-        p.lse[(static_cast<size_t>(batch) * p.H + head) * p.Sq + row] =
-            (m_used * sl2 + log2f(l_sum)) * 0.6931471805599453f;
-      }
+      if (write_out && p.lse != nullptr && row < p.Sq)
+        p.lse[(static_cast<size_t>(batch) * p.H + head) * p.Sq + row] = lse_row;
     }
   }
 

@@ -199,10 +199,14 @@ int fill_peer_sync(chitu::PeerSync* ps, const chitu_b200_peer_sync* sync, const 
   return CHITU_OK;
 }
 
+// Key-split scratch: a fixed header of per-query-block counters (zero between calls), then the partial
+// rows and their log-sum-exps, whole 128-row tiles (see AttnParams).
+constexpr int64_t kSplitHeaderBytes = CHITU_SPLITKV_HEADER_BYTES;
 int64_t splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits) {
   if (n_splits <= 1) return 0;
-  const int64_t rows = static_cast<int64_t>(B) * Sq * H;
-  return static_cast<int64_t>(n_splits) * rows * (static_cast<int64_t>(D) + 1) * 4;  // fp32 rows + one LSE each
+  const int64_t qblocks = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
+  const int64_t rows = static_cast<int64_t>(B) * H * qblocks * chitu::kQTiles * chitu::kTileM;
+  return kSplitHeaderBytes + static_cast<int64_t>(n_splits) * rows * (static_cast<int64_t>(D) + 1) * 4;
 }
 
 int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const OutScatter& sc, float* lse, int B,
@@ -242,6 +246,10 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
       return fail(CHITU_E_INVALID, "attn_fwd: workspace too small (%lld bytes needed)",
                   (long long)splitkv_workspace_bytes(B, Sq, H, D, n_splits));
     if (static_cast<int64_t>(B) * n_splits > 65535) return fail(CHITU_E_UNSUPPORTED, "attn_fwd: B * n_splits too large");
+    const int64_t qblocks = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
+    if (static_cast<int64_t>(B) * H * qblocks * 4 > kSplitHeaderBytes)
+      return fail(CHITU_E_UNSUPPORTED, "attn_fwd: a split over keys serves at most %lld query blocks x heads x batch",
+                  (long long)(kSplitHeaderBytes / 4));
   }
 
   CUtensorMap tq, tk, tv;
@@ -268,8 +276,14 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
   for (int i = 0; i < 8; ++i) p.out_ptrs[i] = i < sc.n_dest ? sc.ptrs[i] : nullptr;
   p.n_splits = n_splits;
   p.tiles_per_split = tiles_per_split;
-  p.part_o = static_cast<float*>(ks.workspace);
-  p.part_lse = p.part_o ? p.part_o + static_cast<size_t>(n_splits) * B * Sq * H * D : nullptr;
+  p.split_count = static_cast<int*>(ks.workspace);
+  p.part_o = p.part_lse = nullptr;
+  if (n_splits > 1) {
+    const int64_t qblocks = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
+    const size_t rows = static_cast<size_t>(B) * H * qblocks * chitu::kQTiles * chitu::kTileM;
+    p.part_o = reinterpret_cast<float*>(static_cast<uint8_t*>(ks.workspace) + kSplitHeaderBytes);
+    p.part_lse = p.part_o + static_cast<size_t>(n_splits) * rows * D;
+  }
   p.q_norm_mode = 2;
   p.q_rope_mode = 0;
   p.q_round_mid = 0;
@@ -346,7 +360,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     p.in_epoch = p.sync.blocks[p.sync.rank] + chitu::kSyncInEpoch;
     p.rows_per_src = ex.rows_per_src;
     p.local_src = p.sync.rank;
-    p.signal_out = n_splits == 1;
+    p.signal_out = 1;
   }
   p.push_x = p.push_rounds = p.push_first = p.rot_other = 0;
   p.push_vecs = 0;
@@ -425,36 +439,6 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     chitu::attn_fwd_kernel<false><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attn_fwd: launch");
-  if (n_splits > 1) {
-    chitu::SplitCombineParams c;
-    c.part_o = p.part_o;
-    c.part_lse = p.part_lse;
-    c.out = out;
-    c.lse = lse;
-    c.n = n_splits;
-    c.B = B;
-    c.S = Sq;
-    c.H = H;
-    c.D = D;
-    c.out_dtype = dtype;
-    c.n_dest = sc.n_dest;
-    c.rows_per_dest = sc.rows_per_dest;
-    c.dest_batch_bytes = p.dest_batch_bytes;
-    c.dest_row_bytes = p.dest_row_bytes;
-    c.dest_head_bytes = p.dest_head_bytes;
-    for (int i = 0; i < 8; ++i) c.out_ptrs[i] = p.out_ptrs[i];
-    c.sync = p.sync;
-    c.signal_out = ex.sync != nullptr;
-    c.prefix_rows = p.prefix_rows;
-    for (int i = 0; i < 8; ++i) c.prefix_ptrs[i] = p.prefix_ptrs[i];
-    c.prefix_batch_bytes = p.prefix_batch_bytes;
-    c.prefix_row_bytes = p.prefix_row_bytes;
-    c.prefix_head_bytes = p.prefix_head_bytes;
-    const long long rows = static_cast<long long>(B) * Sq * H;
-    chitu::splitkv_combine_kernel<<<grid_for(rows, 8, 148 * 16), 256, 0, st>>>(c);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "attn_fwd: combine launch");
-  }
   return CHITU_OK;
 }
 

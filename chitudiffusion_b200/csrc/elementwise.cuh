@@ -105,91 +105,6 @@ lse_combine_kernel(float* __restrict__ acc_out, float* __restrict__ acc_lse, con
 }
 
 // ----------------------------------------------------------------------------
-// Merge of the key-range partials of one attention call: one warp per (b, s, h) row.
-//   out = sum_i exp(lse_i - lse) * part_o_i,  lse = log sum_i exp(lse_i)
-// part_o [n][B][S][H][D] fp32, part_lse [n][B][H][S] fp32, out 16-bit, lse [B][H][S] optional.
-// Row r goes to out, or (n_dest > 0) to out_ptrs[r / rows_per_dest] like the attention epilogue.
-// ----------------------------------------------------------------------------
-struct SplitCombineParams {
-  const float* part_o;
-  const float* part_lse;
-  void* out;
-  float* lse;
-  int n, B, S, H, D, out_dtype;
-  void* out_ptrs[8];
-  int n_dest, rows_per_dest;
-  long long dest_batch_bytes, dest_row_bytes, dest_head_bytes;
-  // when signal_out is set, the last CTA tells every peer that this rank's output rows have landed
-  PeerSync sync;
-  int signal_out;
-  // replicated prefix (see AttnParams): rows [0, prefix_rows) go to EVERY rank's prefix_ptrs buffer
-  int prefix_rows;
-  void* prefix_ptrs[8];
-  long long prefix_batch_bytes, prefix_row_bytes, prefix_head_bytes;
-};
-
-__global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitCombineParams p) {
-  const int lane = threadIdx.x & 31;
-  const long long warps_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  const long long rows = static_cast<long long>(p.B) * p.S * p.H;
-  const size_t part_stride = static_cast<size_t>(rows) * p.D;
-  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += warps_total) {
-    const int h = static_cast<int>(row % p.H);
-    const long long bs = row / p.H;
-    const int s = static_cast<int>(bs % p.S);
-    const int b = static_cast<int>(bs / p.S);
-    const size_t lidx = (static_cast<size_t>(b) * p.H + h) * p.S + s;
-    const size_t lstride = static_cast<size_t>(p.B) * p.H * p.S;
-    float mx = -INFINITY;
-    for (int i = 0; i < p.n; ++i) mx = fmaxf(mx, p.part_lse[i * lstride + lidx]);
-    float wsum = 0.f;
-    for (int i = 0; i < p.n; ++i) wsum += expf(p.part_lse[i * lstride + lidx] - mx);
-    const float inv = 1.0f / wsum;
-    uint8_t* orow;
-    const bool in_prefix = s < p.prefix_rows;
-    if (p.n_dest == 0) {
-      orow = static_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.D * 2;
-    } else if (in_prefix) {
-      orow = nullptr;  // stored to every rank below
-    } else {
-      const int si = s - p.prefix_rows;
-      const int dest = min(si / p.rows_per_dest, p.n_dest - 1);
-      orow = static_cast<uint8_t*>(p.out_ptrs[dest]) + b * p.dest_batch_bytes +
-             (si - static_cast<long long>(dest) * p.rows_per_dest) * p.dest_row_bytes + p.dest_head_bytes +
-             static_cast<long long>(h) * p.D * 2;
-    }
-    for (int d = lane * 4; d < p.D; d += 128) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int i = 0; i < p.n; ++i) {
-        const float w = expf(p.part_lse[i * lstride + lidx] - mx) * inv;
-        const float4 v = *reinterpret_cast<const float4*>(p.part_o + i * part_stride + static_cast<size_t>(row) * p.D + d);
-        acc.x = fmaf(w, v.x, acc.x);
-        acc.y = fmaf(w, v.y, acc.y);
-        acc.z = fmaf(w, v.z, acc.z);
-        acc.w = fmaf(w, v.w, acc.w);
-      }
-      uint2 raw;
-      raw.x = pack16(acc.x, acc.y, p.out_dtype);
-      raw.y = pack16(acc.z, acc.w, p.out_dtype);
-      if (orow != nullptr) {
-        *reinterpret_cast<uint2*>(orow + d * 2) = raw;
-      } else {
-        for (int i = 0; i < p.n_dest; ++i)
-          *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.prefix_ptrs[i]) + b * p.prefix_batch_bytes +
-                                    s * p.prefix_row_bytes + p.prefix_head_bytes + static_cast<long long>(h) * p.D * 2 +
-                                    d * 2) = raw;
-      }
-    }
-    if (lane == 0 && p.lse != nullptr) p.lse[lidx] = mx + logf(wsum);
-  }
-  if (p.signal_out) {
-    __syncthreads();
-    if (threadIdx.x == 0) publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, gridDim.x);
-  }
-}
-
-// ----------------------------------------------------------------------------
 // RMSNorm + rotary + cast: one CTA per token, 8-element vectors in registers.
 // ----------------------------------------------------------------------------
 struct NormRopeParams {

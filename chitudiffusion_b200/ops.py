@@ -124,7 +124,8 @@ def auto_key_splits(B: int, Sq: int, Sk: int, H: int) -> int:
 
 
 def splitkv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Scratch for key-split partials, one buffer per (device, stream), grown on demand.
+    """Scratch for key-split partials, one buffer per (device, stream), grown on demand, zero-filled when
+    created (the library keeps per-query-block counters in its first 64 KiB and leaves them zero after each call).
 
     A buffer that has been handed out may be baked into a captured CUDA graph, so a superseded buffer
     is never freed: it is parked for the life of the process and the larger replacement serves later
@@ -139,7 +140,7 @@ def splitkv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     if ws is None or ws.numel() < nbytes:
         if ws is not None:
             _retired_workspaces.append(ws)
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)  # the counters at its head start at zero
         _workspaces[key] = ws
     return ws
 
@@ -220,7 +221,7 @@ def attn_fwd(
                 scale, _DTYPES[q.dtype], ctypes.byref(desc), int(n_splits), ws_ptr, ws_bytes,
                 status_word(q.device).data_ptr(), _stream_ptr(q.device))
         _lib.check(rc, "attn_fwd_qpre")
-        _launched(2 if n_splits > 1 and Sk > 128 else 1)
+        _launched(1)
         return out, lse
     with torch.cuda.device(q.device):
         if n_splits > 1:
@@ -242,7 +243,7 @@ def attn_fwd(
                 status_word(q.device).data_ptr(), _stream_ptr(q.device),
             )
     _lib.check(rc, "attn_fwd")
-    _launched(2 if n_splits > 1 and Sk > 128 else 1)
+    _launched(1)
     return out, lse
 
 
@@ -645,7 +646,7 @@ def attn_fwd_scatter(
             _stream_ptr(q.device),
         )
     _lib.check(rc, "attn_fwd_scatter")
-    _launched(2 if n_splits > 1 and Sk > 128 else 1)
+    _launched(1)
 
 
 def peer_barrier(flag_ptrs: Sequence[int], rank: int, world: int, device: torch.device) -> None:
@@ -712,7 +713,7 @@ def attn_fwd_exchange(
                 ctypes.byref(sync[0]), status_word(q.device).data_ptr(), _stream_ptr(q.device),
             )
         _lib.check(rc, "attn_fwd_exchange_push")
-        _launched(2 if n_splits > 1 and Sk > 128 else 1)
+        _launched(1)
         return
     with torch.cuda.device(q.device):
         rc = lib.chitu_b200_attn_fwd_exchange(
@@ -725,7 +726,7 @@ def attn_fwd_exchange(
             status_word(q.device).data_ptr(), _stream_ptr(q.device),
         )
     _lib.check(rc, "attn_fwd_exchange")
-    _launched(2 if n_splits > 1 and Sk > 128 else 1)
+    _launched(1)
 
 
 def stamp(slots: torch.Tensor, index: int) -> None:

@@ -105,7 +105,7 @@ class PeerUlysses:
         # key-split scratch owned by this object: graphs captured over it keep a valid address
         self.n_splits = ops.auto_key_splits(B, T + U * s, T + U * s, self.hc)
         need = ops.splitkv_workspace_bytes(B, T + U * s, self.hc, D, self.n_splits)
-        self.workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=device) if self.n_splits > 1 else None
+        self.workspace = torch.zeros(max(need, 16), dtype=torch.uint8, device=device) if self.n_splits > 1 else None
         # Push mode: where the attention grid leaves SMs idle, only the query rows are stored straight to the
         # peers; key and value rows for the peers are staged locally and copy CTAs inside the attention launch
         # deliver them while the attention already runs

@@ -66,14 +66,20 @@ int chitu_b200_attn_fwd(const void* q, const void* k, const void* v, void* out, 
 
 /*
  * The same attention with the keys split into n_splits ranges that run as separate CTAs (for grids
- * that would leave most of the 148 SMs idle: few query rows or few heads per GPU); a second kernel
- * merges the partial results.  Same reference call sites as chitu_b200_attn_fwd.  The split count is
- * clamped to the number of 128-key tiles; with one split no workspace is touched.
+ * that would leave most of the 148 SMs idle: few query rows or few heads per GPU).  Each CTA parks its
+ * partial rows in the workspace; the last of the n_splits CTAs of a query block to finish merges them
+ * and writes the result - one launch.  Same reference call sites as chitu_b200_attn_fwd.  The split count
+ * is clamped to the number of 128-key tiles; with one split no workspace is touched.
  *
  *   workspace        device scratch of at least chitu_b200_attn_splitkv_workspace_bytes(...) bytes,
- *                    16-byte aligned: fp32 partial rows [n_splits][B][Sq][H][D] then their
- *                    log-sum-exps [n_splits][B][H][Sq].  Contents need no initialisation.
+ *                    16-byte aligned.  Its first CHITU_SPLITKV_HEADER_BYTES hold one counter per
+ *                    (batch, head, 256-row query block) - at most CHITU_SPLITKV_HEADER_BYTES / 4 of them,
+ *                    more is CHITU_E_UNSUPPORTED - and must be ZERO before the first call; every call
+ *                    that completes leaves them zero again (a call that ended with a non-zero status
+ *                    word may not: clear the header before reusing the workspace).  The rest - fp32
+ *                    partial rows and their log-sum-exps, in whole 128-row tiles - needs no initialisation.
  */
+#define CHITU_SPLITKV_HEADER_BYTES 65536
 int64_t chitu_b200_attn_splitkv_workspace_bytes(int B, int Sq, int H, int D, int n_splits);
 int chitu_b200_attn_fwd_splitkv(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq,
                                 int Sk, int H, int D, const int64_t* q_strides, const int64_t* k_strides,
@@ -103,7 +109,8 @@ int chitu_b200_attn_fwd_splitkv(const void* q, const void* k, const void* v, voi
  *     afterwards nothing more is taken.  cudaDeviceReset() destroys the array and invalidates the
  *     cached address: a process that resets a device must not call this entry point on it again.
  *   - One array per GPU, shared by every call: it keeps the previous call's partial results and nothing
- *     in it needs clearing, because each call overwrites every row it later reads.  Two calls that run
+ *     in it needs clearing, because each call overwrites every row it later reads and returns the counters
+ *     at its head (zero when the library is loaded) to zero.  Two calls that run
  *     at the same time on one GPU (different streams, or different threads) race on it; serialise them.
  */
 int chitu_b200_attn_fwd_splitkv_static(const void* q, const void* k, const void* v, void* out, float* lse, int B,

@@ -52,7 +52,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
         k = torch.randn(B, Sk, H, 128, generator=gen).to(torch.bfloat16).to(dev)
         v = torch.randn(B, Sk, H, 128, generator=gen).to(torch.bfloat16).to(dev)
         need = int(lib.chitu_b200_attn_splitkv_workspace_bytes(B, Sq, H, 128, n_splits))
-        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev)  # the counters at its head must start at zero
         rc_ref, out_ref, lse_ref = _call(lib, "chitu_b200_attn_fwd_splitkv", q, k, v, n_splits, ws)
         assert rc_ref == 0, lib.chitu_b200_last_error()
         rc, out, lse = _call(lib, "chitu_b200_attn_fwd_splitkv_static", q, k, v, n_splits)
