@@ -169,9 +169,10 @@ struct Exchange {
   const chitu_b200_push* push = nullptr;  // copy CTAs inside the attention launch
 };
 
-// Copy CTAs of push mode: extra blocks along x (each one adds H * B * n_splits CTAs) so that attention
-// and copy CTAs together are resident at once - one CTA per SM - and there are at least 8 and at most
-// 48 copy CTAs.  0: the shape does not qualify.
+// Copy CTAs of push mode: extra blocks along x (each one adds H * B * n_splits CTAs), about 40 and between 8
+// and 48.  They come first in the grid and never wait for anything, so they hold an SM before any attention
+// CTA does; where the attention CTAs alone leave SMs idle, the count is cut to what fits beside them, so the
+// whole grid is resident at once.  0: the shape does not qualify.
 int plan_push_x(int B, int Sq, int H, int n_splits) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -179,10 +180,12 @@ int plan_push_x(int B, int Sq, int H, int n_splits) {
     return 0;
   const long long per_x = static_cast<long long>(H) * B * n_splits;
   const long long qblocks = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
-  const long long free_sms = sms - qblocks * per_x;
-  if (per_x <= 0 || free_sms < 8) return 0;
-  long long x = free_sms / per_x;
+  if (per_x <= 0 || per_x > 48) return 0;
+  long long x = (40 + per_x / 2) / per_x;
+  if (x < 1) x = 1;
   if (x * per_x > 48) x = 48 / per_x;
+  const long long free_sms = sms - qblocks * per_x;
+  if (free_sms > 0 && free_sms < x * per_x && free_sms / per_x * per_x >= 8) x = free_sms / per_x;
   return x * per_x >= 8 ? static_cast<int>(x) : 0;
 }
 
@@ -379,7 +382,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
       return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: block_bytes must be a positive multiple of 16");
     p.push_x = plan_push_x(B, Sq, H, n_splits);
     if (p.push_x == 0)
-      return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: the grid leaves no room for resident copy CTAs");
+      return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: no copy-CTA count between 8 and 48 for this grid");
     for (int t = 0; t < 3; ++t) {
       if (t == 0 && !ex.push->stage[0]) continue;  // query rows were delivered by the staging launch
       if (!ex.push->stage[t] || (reinterpret_cast<uintptr_t>(ex.push->stage[t]) & 15) || !ex.push->dest[t])

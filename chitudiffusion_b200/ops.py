@@ -116,11 +116,34 @@ NUM_SMS = 148
 
 
 def auto_key_splits(B: int, Sq: int, Sk: int, H: int) -> int:
-    """How many key ranges to run as separate CTAs so that a small grid still covers the SMs."""
+    """How many key ranges to run as separate CTAs.  A CTA serves 256 query rows of one head; the grid runs in
+    waves of one CTA per SM, so the cost of a call is (waves) x (key tiles per CTA, plus about 1.5 tile steps
+    for parking the partial rows) plus about one tile step per range for the merge.  The split that minimises
+    it is taken when it saves at least 8 %: it fills small grids (54 CTAs -> 2 ranges) and evens out badly
+    quantised ones (216 CTAs, 1.46 waves -> 2 ranges, 2.92 waves).
+    ``CHITU_B200_KEY_SPLITS`` overrides."""
+    import os
+
+    forced = os.environ.get("CHITU_B200_KEY_SPLITS")
+    tiles = -(-Sk // 128)
+    if forced:
+        return max(1, min(int(forced), tiles, 64))
     ctas = -(-Sq // 256) * H * B
-    if ctas * 10 >= NUM_SMS * 7:  # already at least 0.7 of a wave
-        return 1
-    return max(1, min(-(-Sk // 128), NUM_SMS // ctas, 16))
+
+    def cost(n):
+        per = -(-tiles // n)
+        n_eff = -(-tiles // per)
+        waves = -(-ctas * n_eff // NUM_SMS)
+        return waves * per if n_eff == 1 else waves * (per + 1.5) + 1.0 * n_eff
+
+    best, best_cost = 1, cost(1)
+    for n in range(2, min(tiles, 16) + 1):
+        if ctas * n > 512:  # the parked rows (128 KiB per CTA) should stay in L2 until they are merged
+            break
+        c = cost(n)
+        if c < best_cost * 0.92 and c < cost(best):
+            best, best_cost = n, c
+    return best
 
 
 def splitkv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:

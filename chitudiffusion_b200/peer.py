@@ -117,8 +117,10 @@ class PeerUlysses:
         self._layer_open = False
         import os
 
-        if (B == 1 and T == 0 and os.environ.get("CHITU_B200_PUSH", "1") != "0"
-                and ops.push_ctas(B, U * s, self.hc, self.n_splits) > 0):
+        mode = os.environ.get("CHITU_B200_PUSH", "1")  # "0": never; "1": where the whole grid is resident; "force"
+        n_push = ops.push_ctas(B, U * s, self.hc, self.n_splits) if (B == 1 and T == 0 and mode != "0") else 0
+        resident = -(-(U * s) // 256) * self.hc * B * self.n_splits + n_push <= ops.NUM_SMS
+        if n_push > 0 and (resident or mode == "force"):
             block = s * self._row_bytes
             self._stage = torch.empty(3 * U * block, dtype=torch.uint8, device=device)
             self._stage_ptrs = [self._stage.data_ptr() + t * U * block for t in range(3)]

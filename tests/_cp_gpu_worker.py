@@ -147,6 +147,19 @@ def main():
     for rep in range(2):
         px_direct.scatter_qkv(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
         results[f"direct{rep}"] = rel_err(px_direct.attention(), ref2[:, sl])
+    # both modes again with the keys of every query block split over two CTAs (the CTA that finishes last
+    # merges the ranges, stores the rows to their owners and takes part in the announcement)
+    os.environ["CHITU_B200_KEY_SPLITS"] = "2"
+    px_split = PeerUlysses(comm.get_up_group(world), 1, s, H, D, torch.bfloat16, dev)
+    os.environ["CHITU_B200_PUSH"] = "0"
+    px_split_direct = PeerUlysses(comm.get_up_group(world), 1, s, H, D, torch.bfloat16, dev)
+    os.environ.pop("CHITU_B200_PUSH")
+    os.environ.pop("CHITU_B200_KEY_SPLITS")
+    assert px_split.n_splits == 2 and px_split.push is not None and px_split_direct.push is None
+    for name, obj in (("split_push", px_split), ("split_direct", px_split_direct)):
+        for rep in range(2):
+            obj.scatter_qkv(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
+            results[f"{name}{rep}"] = rel_err(obj.attention(), ref2[:, sl])
     # the same through the wrapper's projections-in entry, whole and in two row pieces (as Flux's two streams arrive)
     wrapper = B200ContextParallel(backend, world, cp_backend="ucp")
     lq, lk, lv = (t[:, sl].contiguous().to(dev) for t in (xq, xk, xv))
