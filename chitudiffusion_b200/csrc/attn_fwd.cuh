@@ -83,15 +83,17 @@ struct AttnParams {
   long long flag_timeout;
   PeerSync sync;
   int signal_out;
-  // Push mode (push_x > 0): key and value rows this rank owes its peers are staged in local memory, and the
-  // CTAs with blockIdx.x < push_x (the first to be given an SM) do no attention: they copy the staged rows
+  // Push mode (push_ctas > 0): key and value rows this rank owes its peers are staged in local memory, and
+  // the launch is one-dimensional: its first push_ctas CTAs do no attention, they copy the staged rows
   // into the peers' buffers while the attention CTAs of the same launch already work - in push_order, the
   // order in which the receivers walk their keys: the first push_first peers, then the others (announced
-  // in in_flags).  Query rows are normally delivered and announced (q_flags) by the staging launch itself;
-  // push_src[0] != nullptr makes the copy CTAs send them too, first.  The rank's own rows are already in
-  // place and have no flag.  Copy CTAs never wait for anything, and the host only chooses this mode when
-  // the whole grid is resident at once, so a waiting attention CTA never keeps a copy CTA off the machine.
-  int push_x, push_rounds, push_first, rot_other;
+  // in in_flags).  The attention CTAs follow, (query block, head, batch x split) in that order of
+  // significance, grid_q x grid_h x grid_z of them.  Query rows are normally delivered and announced
+  // (q_flags) by the staging launch itself; push_src[0] != nullptr makes the copy CTAs send them too,
+  // first.  The rank's own rows are already in place and have no flag.  Copy CTAs never wait for anything
+  // and are the first CTAs of the grid, so they are on the machine before an attention CTA can wait for
+  // a peer's: the GPUs cannot starve one another of copy CTAs.
+  int push_ctas, grid_q, grid_h, grid_z, push_rounds, push_first, rot_other;
   int push_order[8];
   const uint4* push_src[3];  // staged q, k, v: block d (push_vecs 16-byte vectors) holds the rows for rank d
   uint4* push_dst[3][8];     // where this rank's block starts in rank d's gathered q, k, v
@@ -360,6 +362,26 @@ __device__ __forceinline__ void push_rows(const AttnParams& p, int id, int n) {
 #define CHITU_TRACE(i)
 #endif
 
+// (query block, head, batch x split) of an attention CTA.  Read afresh from the special registers each time
+// (the asm is volatile), so that the epilogue can ask again instead of keeping four values in registers
+// through the whole key loop.
+__device__ __forceinline__ void attn_cta_coords(const AttnParams& p, int& qblock, int& head, int& bz) {
+  unsigned x, y, z;
+  asm volatile("mov.u32 %0, %%ctaid.x;" : "=r"(x));
+  asm volatile("mov.u32 %0, %%ctaid.y;" : "=r"(y));
+  asm volatile("mov.u32 %0, %%ctaid.z;" : "=r"(z));
+  qblock = static_cast<int>(x);
+  head = static_cast<int>(y);
+  bz = static_cast<int>(z);
+  if (p.push_ctas > 0) {
+    const int lin = qblock - p.push_ctas;
+    const int rest = lin / p.grid_q;
+    qblock = lin - rest * p.grid_q;
+    bz = rest / p.grid_h;
+    head = rest - bz * p.grid_h;
+  }
+}
+
 template <bool kFp16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -368,13 +390,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   if (threadIdx.x == 0) CHITU_TRACE(0);
-  const int n_qblocks = gridDim.x - p.push_x;
-  if (static_cast<int>(blockIdx.x) < p.push_x) {  // a copy CTA of push mode: no tensor memory, no barriers
-    push_rows(p, blockIdx.x + p.push_x * (blockIdx.y + gridDim.y * blockIdx.z),
-              p.push_x * gridDim.y * gridDim.z);
+  if (p.push_ctas > 0 && static_cast<int>(blockIdx.x) < p.push_ctas) {  // a copy CTA: no tensor memory, no barriers
+    push_rows(p, blockIdx.x, p.push_ctas);
     if (threadIdx.x == 0) CHITU_TRACE(6);
     return;
   }
+  int bx, by, bz;
+  attn_cta_coords(p, bx, by, bz);
 
   const uint32_t q_smem = smem_base;                          // 2 tiles
   const uint32_t kv_smem = smem_base + kQTiles * kTileBytes;  // kStages tiles
@@ -396,11 +418,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int qblock = static_cast<int>(blockIdx.x) - p.push_x;
+  const int qblock = bx;
   const int q0 = qblock * (kQTiles * kTileM);
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z / p.n_splits;
-  const int split = blockIdx.z - batch * p.n_splits;
+  const int head = by;
+  const int batch = bz / p.n_splits;
+  const int split = bz - batch * p.n_splits;
   const int n_kv_total = (p.Sk + kTileN - 1) / kTileN;
   const int kv0 = split * p.tiles_per_split;                      // first key tile of this CTA
   const int n_kv = min(p.tiles_per_split, n_kv_total - kv0);      // >= 1 (the host sizes the splits)
@@ -458,7 +480,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // arrival flags of the fused exchange: lane 0 remembers which source ranks it has already seen
     // (push mode: the rank's own rows were put in place by the staging launch and have no flag; query rows
     // and key / value rows are announced separately)
-    uint32_t src_ready = p.push_x > 0 ? 1u << p.local_src : 0u;
+    uint32_t src_ready = p.push_ctas > 0 ? 1u << p.local_src : 0u;
     uint32_t q_ready = src_ready;
     const int flag_epoch = (p.in_flags != nullptr && lane == 0) ? *reinterpret_cast<const volatile int*>(p.in_epoch) : 0;
     auto wait_rows = [&](const int* flags, uint32_t& ready, int row_lo, int row_hi, int rows_total) {
@@ -478,7 +500,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     };
     if (lane == 0) {
-      wait_rows(p.push_x > 0 ? p.q_flags : p.in_flags, q_ready, q0, q0 + n_qt * kTileM, p.Sq);
+      wait_rows(p.push_ctas > 0 ? p.q_flags : p.in_flags, q_ready, q0, q0 + n_qt * kTileM, p.Sq);
       CHITU_TRACE(7);
       for (int t = 0; t < n_qt; ++t) {
         mbar_arrive_expect_tx(bar_q_full + 8 * t, kTileBytes);
@@ -639,7 +661,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #endif
           mbar_wait(bar_q_full + 8 * t, 0, abort_flag, p.status, kDevTimeoutSoftmax);
 #ifdef CHITU_ATTN_TIMING
-          if (p.dbg != nullptr && static_cast<int>(blockIdx.x) == p.push_x && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+          if (p.dbg != nullptr && bx == 0 && by == 0 && bz == 0 && threadIdx.x == 0) {
             p.dbg[24] = qt1 - qt0;
             p.dbg[25] = clock64() - qt1;
             qt1 = clock64();
@@ -649,7 +671,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         fence_proxy_async_smem();  // the rewritten tile is read by the tensor core through the async proxy
         mbar_arrive(bar_q_ready + 8 * t);
 #ifdef CHITU_ATTN_TIMING
-        if (p.dbg != nullptr && static_cast<int>(blockIdx.x) == p.push_x && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0)
+        if (p.dbg != nullptr && bx == 0 && by == 0 && bz == 0 && threadIdx.x == 0)
           p.dbg[26] = clock64() - qt1;
 #endif
       }
@@ -764,7 +786,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         l_sum += (la.x + la.y) + (lb.x + lb.y);
       }
 #ifdef CHITU_ATTN_TIMING
-      if (p.dbg != nullptr && static_cast<int>(blockIdx.x) == p.push_x && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0) {
+      if (p.dbg != nullptr && bx == 0 && by == 0 && bz == 0 && lane == 0 && (warp & 3) == 0) {
         p.dbg[t * 4 + 0] = tw; p.dbg[t * 4 + 1] = tl; p.dbg[t * 4 + 2] = tm; p.dbg[t * 4 + 3] = ts;
       }
 #endif
@@ -773,7 +795,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (t == 0 && row_in_tile == 0) CHITU_TRACE(3);
       mbar_wait(bar_o_final + 8 * t, 0, abort_flag, p.status, kDevTimeoutEpilogue);
       tc_fence_after_sync();
-      const int row = q0 + t * kTileM + row_in_tile;
+      int qblock, head, ez;
+      attn_cta_coords(p, qblock, head, ez);
+      const int batch = ez / p.n_splits;
+      const int split = ez - batch * p.n_splits;
+      const int row = qblock * (kQTiles * kTileM) + t * kTileM + row_in_tile;
       const float inv_l = 1.0f / l_sum;
       uint4* dst;
       const bool in_prefix = p.n_dest != 0 && row < p.prefix_rows;
@@ -819,6 +845,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       } else {
         // (1) this key range's normalised rows and log-sum-exp go to scratch
+        const int n_qblocks = p.push_ctas > 0 ? p.grid_q : static_cast<int>(gridDim.x);
         const size_t tiles_total = static_cast<size_t>(p.B) * p.H * n_qblocks * 2;
         const size_t tile_id = ((static_cast<size_t>(batch) * p.H + head) * n_qblocks + qblock) * 2 + t;
         float4* mine = reinterpret_cast<float4*>(p.part_o) + (split * tiles_total + tile_id) * (32 * kTileM) + row_in_tile;
@@ -920,7 +947,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_dealloc(tmem_base, 512);
   }
   if (p.signal_out && threadIdx.x == 0)
-    publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, n_qblocks * gridDim.y * gridDim.z);
+    publish_when_last(p.sync, kSyncAttnDone, kSyncOutEpoch, kSyncOutFlag, p.push_ctas > 0 ? p.grid_q * p.grid_h * p.grid_z : gridDim.x * gridDim.y * gridDim.z);
   if (threadIdx.x == 0) CHITU_TRACE(6);
 }
 

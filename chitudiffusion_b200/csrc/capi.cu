@@ -169,24 +169,18 @@ struct Exchange {
   const chitu_b200_push* push = nullptr;  // copy CTAs inside the attention launch
 };
 
-// Copy CTAs of push mode: extra blocks along x (each one adds H * B * n_splits CTAs), about 40 and between 8
-// and 48.  They come first in the grid and never wait for anything, so they hold an SM before any attention
-// CTA does; where the attention CTAs alone leave SMs idle, the count is cut to what fits beside them, so the
-// whole grid is resident at once.  0: the shape does not qualify.
-int plan_push_x(int B, int Sq, int H, int n_splits) {
+// Copy CTAs of push mode: 40, or - where the attention CTAs alone leave SMs idle - what fits beside them
+// (8 to 48), so that the whole grid is resident at once.  They are the first CTAs of a one-dimensional
+// grid and never wait for anything.
+int plan_push_ctas(int B, int Sq, int H, int n_splits) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return 0;
-  const long long per_x = static_cast<long long>(H) * B * n_splits;
   const long long qblocks = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
-  if (per_x <= 0 || per_x > 48) return 0;
-  long long x = (40 + per_x / 2) / per_x;
-  if (x < 1) x = 1;
-  if (x * per_x > 48) x = 48 / per_x;
-  const long long free_sms = sms - qblocks * per_x;
-  if (free_sms > 0 && free_sms < x * per_x && free_sms / per_x * per_x >= 8) x = free_sms / per_x;
-  return x * per_x >= 8 ? static_cast<int>(x) : 0;
+  const long long free_sms = sms - qblocks * H * B * n_splits;
+  if (free_sms >= 8) return static_cast<int>(free_sms < 48 ? free_sms : 48);
+  return sms >= 80 ? 40 : 0;
 }
 
 int fill_peer_sync(chitu::PeerSync* ps, const chitu_b200_peer_sync* sync, const char* what) {
@@ -365,7 +359,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     p.local_src = p.sync.rank;
     p.signal_out = 1;
   }
-  p.push_x = p.push_rounds = p.push_first = p.rot_other = 0;
+  p.push_ctas = p.grid_q = p.grid_h = p.grid_z = p.push_rounds = p.push_first = p.rot_other = 0;
   p.push_vecs = 0;
   p.q_flags = nullptr;
   for (int t = 0; t < 3; ++t) {
@@ -380,9 +374,13 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
       return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: no replicated prefix, no in-kernel q transform");
     if (ex.push->block_bytes <= 0 || (ex.push->block_bytes & 15))
       return fail(CHITU_E_INVALID, "attn_fwd_exchange_push: block_bytes must be a positive multiple of 16");
-    p.push_x = plan_push_x(B, Sq, H, n_splits);
-    if (p.push_x == 0)
-      return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: no copy-CTA count between 8 and 48 for this grid");
+    p.push_ctas = plan_push_ctas(B, Sq, H, n_splits);
+    if (p.push_ctas == 0) return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: this device has too few SMs");
+    p.grid_q = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
+    p.grid_h = H;
+    p.grid_z = B * n_splits;
+    if (static_cast<int64_t>(p.grid_q) * H * B * n_splits + p.push_ctas >= (1LL << 31))
+      return fail(CHITU_E_UNSUPPORTED, "attn_fwd_exchange_push: grid too large");
     for (int t = 0; t < 3; ++t) {
       if (t == 0 && !ex.push->stage[0]) continue;  // query rows were delivered by the staging launch
       if (!ex.push->stage[t] || (reinterpret_cast<uintptr_t>(ex.push->stage[t]) & 15) || !ex.push->dest[t])
@@ -434,7 +432,8 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
                 : ensure_dynamic_smem(chitu::attn_fwd_kernel<false>, chitu::kAttnSmemBytes, attr_done[0], attr_mu);
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
 
-  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM) + p.push_x, H, B * n_splits);
+  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B * n_splits);
+  if (p.push_ctas > 0) grid = dim3(p.push_ctas + p.grid_q * p.grid_h * p.grid_z, 1, 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p.is_fp16)
     chitu::attn_fwd_kernel<true><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
@@ -530,7 +529,7 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
 
 int chitu_b200_push_ctas(int B, int Sq, int H, int n_splits) {
   if (B <= 0 || Sq <= 0 || H <= 0 || n_splits < 1) return 0;
-  return plan_push_x(B, Sq, H, n_splits) * H * B * n_splits;
+  return plan_push_ctas(B, Sq, H, n_splits);
 }
 
 int chitu_b200_attn_fwd_exchange_push(const void* q, const void* k, const void* v, void* const* out_ptrs, int n_dest,

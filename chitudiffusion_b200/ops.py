@@ -117,10 +117,10 @@ NUM_SMS = 148
 
 def auto_key_splits(B: int, Sq: int, Sk: int, H: int) -> int:
     """How many key ranges to run as separate CTAs.  A CTA serves 256 query rows of one head; the grid runs in
-    waves of one CTA per SM, so the cost of a call is (waves) x (key tiles per CTA, plus about 1.5 tile steps
-    for parking the partial rows) plus about one tile step per range for the merge.  The split that minimises
-    it is taken when it saves at least 8 %: it fills small grids (54 CTAs -> 2 ranges) and evens out badly
-    quantised ones (216 CTAs, 1.46 waves -> 2 ranges, 2.92 waves).
+    waves of one CTA per SM, so the cost of a call is (waves) x (key tiles per CTA, plus about 5 tile steps for
+    a CTA's prologue and for parking its partial rows: 216 CTAs x 36 tiles measured 138 us, 432 CTAs x 18 tiles
+    143 us) plus about one tile step per range for the merge.  The split that minimises it is taken when it
+    saves at least 8 %: it fills small grids (54 CTAs -> 2 ranges).
     ``CHITU_B200_KEY_SPLITS`` overrides."""
     import os
 
@@ -134,7 +134,7 @@ def auto_key_splits(B: int, Sq: int, Sk: int, H: int) -> int:
         per = -(-tiles // n)
         n_eff = -(-tiles // per)
         waves = -(-ctas * n_eff // NUM_SMS)
-        return waves * per if n_eff == 1 else waves * (per + 1.5) + 1.0 * n_eff
+        return waves * per if n_eff == 1 else waves * (per + 5.0) + 1.0 * n_eff
 
     best, best_cost = 1, cost(1)
     for n in range(2, min(tiles, 16) + 1):

@@ -106,21 +106,22 @@ class PeerUlysses:
         self.n_splits = ops.auto_key_splits(B, T + U * s, T + U * s, self.hc)
         need = ops.splitkv_workspace_bytes(B, T + U * s, self.hc, D, self.n_splits)
         self.workspace = torch.zeros(max(need, 16), dtype=torch.uint8, device=device) if self.n_splits > 1 else None
-        # Push mode: where the attention grid leaves SMs idle, only the query rows are stored straight to the
-        # peers; key and value rows for the peers are staged locally and copy CTAs inside the attention launch
-        # deliver them while the attention already runs
-        # (``chitu_b200_attn_fwd_exchange_push``).  One batch entry only: a staged block is the contiguous
-        # image of this rank's rows in a peer's buffer.
+        # Push mode: only the query rows are stored straight to the peers; key and value rows for the peers are
+        # staged locally, and copy CTAs inside the attention launch - the first CTAs of its grid - deliver them
+        # while the attention already runs (``chitu_b200_attn_fwd_exchange_push``).  One batch entry only: a
+        # staged block is the contiguous image of this rank's rows in a peer's buffer.
         self.push = None
         self.trace = None  # optional callable(point): 0 before the first launch of a layer, 1 after the last
         #                    staging / scatter launch, 2 after the attention launch(es), 3 after the wait
         self._layer_open = False
         import os
 
-        mode = os.environ.get("CHITU_B200_PUSH", "1")  # "0": never; "1": where the whole grid is resident; "force"
+        # CHITU_B200_PUSH: "0" never; "1" (default) for grids of at most four waves - beyond that the transfer
+        # is a small share of the call and the direct stores are kept; "force" always
+        mode = os.environ.get("CHITU_B200_PUSH", "1")
         n_push = ops.push_ctas(B, U * s, self.hc, self.n_splits) if (B == 1 and T == 0 and mode != "0") else 0
-        resident = -(-(U * s) // 256) * self.hc * B * self.n_splits + n_push <= ops.NUM_SMS
-        if n_push > 0 and (resident or mode == "force"):
+        small = -(-(U * s) // 256) * self.hc * B * self.n_splits <= 4 * ops.NUM_SMS
+        if n_push > 0 and (small or mode == "force"):
             block = s * self._row_bytes
             self._stage = torch.empty(3 * U * block, dtype=torch.uint8, device=device)
             self._stage_ptrs = [self._stage.data_ptr() + t * U * block for t in range(3)]

@@ -409,10 +409,10 @@ int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, 
  *   value rows in the order in which the receivers walk their keys, in two stages announced by flags
  *   (stage[0] non-null: the query rows as well, first, for a staging launch that kept them local).  The attention CTAs wait per source rank for the
  *   query rows of their block and for each key / value block as they reach it; this rank's own rows are
- *   already in place.  The copy CTAs come first in the grid and never wait, so they are on the machine
- *   before any attention CTA; chitu_b200_push_ctas says how many a shape gets (about 40; cut to the SMs
- *   the attention CTAs leave idle where that keeps the whole grid resident; 0: use
- *   chitu_b200_attn_fwd_exchange).  dest[t][d] is where this rank's block starts in rank d's gathered
+ *   already in place.  The copy CTAs are the first CTAs of the (one-dimensional) grid and never wait, so
+ *   they are on the machine before any attention CTA can wait for a peer's; chitu_b200_push_ctas says
+ *   how many a shape gets on the current device (40, or what fits beside the attention CTAs where those
+ *   leave 8 or more SMs idle).  dest[t][d] is where this rank's block starts in rank d's gathered
  *   q (t = 0), k (1), v (2); entry `rank` is ignored.
  */
 typedef struct {

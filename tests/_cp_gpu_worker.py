@@ -160,6 +160,33 @@ def main():
         for rep in range(2):
             obj.scatter_qkv(pre.jobs(lq, lk, wq.to(dev), wk.to(dev)), lv, **pre.batch_args(s, grid))
             results[f"{name}{rep}"] = rel_err(obj.attention(), ref2[:, sl])
+    # a grid of more CTAs than the GPU has SMs: the copy CTAs are the first of the launch, so the attention CTAs
+    # of the first wave find their peers' rows arriving; checked against the direct exchange and against one GPU
+    hc = H // world
+    s_big = 256 * (ops.NUM_SMS // hc + 2) // world
+    gen_big = torch.Generator(device=dev).manual_seed(100 + rank)
+    bq, bk, bv = ((torch.randn(1, s_big, H, D, generator=gen_big, device=dev) * 0.7).to(torch.bfloat16) for _ in range(3))
+    os.environ["CHITU_B200_PUSH"] = "force"
+    px_waves = PeerUlysses(comm.get_up_group(world), 1, s_big, H, D, torch.bfloat16, dev)
+    os.environ["CHITU_B200_PUSH"] = "0"
+    px_waves_direct = PeerUlysses(comm.get_up_group(world), 1, s_big, H, D, torch.bfloat16, dev)
+    os.environ.pop("CHITU_B200_PUSH")
+    assert px_waves.push is not None and px_waves_direct.push is None
+    assert -(-(world * s_big) // 256) * hc * px_waves.n_splits > ops.NUM_SMS
+    outs_big = []
+    for obj in (px_waves, px_waves_direct):
+        for rep in range(2):
+            obj.scatter_ready(bq, bk, bv)
+            got = obj.attention().clone()
+        outs_big.append(got)
+    gathered = []
+    for t in (bq, bk, bv):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        gathered.append(torch.cat(parts, 1))
+    single = backend(gathered[0][:, rank * s_big:(rank + 1) * s_big], gathered[1], gathered[2])[0]
+    results["waves_push_vs_direct"] = rel_err(outs_big[0], outs_big[1].float().cpu())
+    results["waves_push_vs_single"] = rel_err(outs_big[0], single.float().cpu())
     # the same through the wrapper's projections-in entry, whole and in two row pieces (as Flux's two streams arrive)
     wrapper = B200ContextParallel(backend, world, cp_backend="ucp")
     lq, lk, lv = (t[:, sl].contiguous().to(dev) for t in (xq, xk, xv))
