@@ -111,6 +111,67 @@ def main():
             ok = (err_t < 2e-6 and err_i < 2e-6 and torch.equal(packed[0], t_out) and torch.equal(packed[1], i_out)
                   and core.stats()["calls"] == 2)
             print(f"rank {rank} {mode} err_txt {err_t:.2e} err_img {err_i:.2e}", flush=True)
+            # producer-callback entries take the same path
+            fused = core.attention_fused(produce_img_q=lambda: iq[:, sl], produce_img_k=lambda: ik[:, sl],
+                                         produce_img_v=lambda: iv[:, sl], produce_txt_q=lambda: tq,
+                                         produce_txt_k=lambda: tk, produce_txt_v=lambda: tv, num_heads=H)
+            fused2 = core.cp_attn_with_full_txt_fused(
+                produce_txt_q=lambda: tq, produce_txt_k=lambda: tk, produce_txt_v=lambda: tv,
+                produce_img_q=lambda: iq[:, sl], produce_img_k=lambda: ik[:, sl], produce_img_v=lambda: iv[:, sl],
+                num_heads=H, image_seq_len=s * cp_size)
+            fused3 = core.attention_fused_packed(
+                img_len=s, produce_q=lambda: torch.cat([iq[:, sl], tq], 1), produce_k=lambda: torch.cat([ik[:, sl], tk], 1),
+                produce_v=lambda: torch.cat([iv[:, sl], tv], 1), num_heads=H)
+            for got in (fused, fused2, fused3):
+                ok = ok and torch.equal(got[0], t_out) and torch.equal(got[1], i_out)
+            if mode == "imagecp_agkv":
+                from chitudiffusion_b200.image_cp import dequantize_fp8, quantize_fp8_per_head
+
+                def local_view(tk_, tv_, ik_, iv_):  # fp32 attention of this rank's queries against given keys
+                    o = oracle.sdpa_fp32(torch.cat([iq[:, sl], tq], 1), torch.cat([ik_, tk_], 1), torch.cat([iv_, tv_], 1))
+                    return o[:, s:], o[:, :s]
+
+                # FP8 transfer: the other ranks' shards arrive quantised per head, the local one stays exact
+                os.environ["CHITU_CP_FP8_KV"] = "1"
+                core8 = B200ImageContextParallel(wrapper, mode="agkv")
+                os.environ.pop("CHITU_CP_FP8_KV")
+                core8.enable(wrapper.group)
+
+                def through_fp8(x):
+                    parts = []
+                    for j in range(cp_size):
+                        piece = x[:, j * s:(j + 1) * s]
+                        parts.append(piece if j == r else dequantize_fp8(*quantize_fp8_per_head(piece), x.dtype))
+                    return torch.cat(parts, 1)
+
+                want_t, want_i = local_view(tk, tv, through_fp8(ik), through_fp8(iv))
+                got_t, got_i = core8.attention(tq, tk, tv, iq[:, sl], ik[:, sl], iv[:, sl])
+                e8 = max((got_t - want_t).abs().max().item(), (got_i - want_i).abs().max().item())
+                coarse = (got_i.float() - full[:, txt_len + r * s: txt_len + (r + 1) * s]).abs().max().item()
+                ok = ok and e8 < 2e-6 and 0 < coarse < 0.2
+                # cross-step cache: fresh on steps 0 and 2, stale on step 1 (remote shards of step 0, local shard new)
+                os.environ.update(CHITU_CP_KV_CACHE="1", CHITU_CP_KV_CACHE_WARMUP="1", CHITU_CP_KV_CACHE_INTERVAL="2",
+                                  CHITU_CP_KV_CACHE_TAIL="1")
+                corec = B200ImageContextParallel(wrapper, mode="agkv")
+                for name in ("CHITU_CP_KV_CACHE", "CHITU_CP_KV_CACHE_WARMUP", "CHITU_CP_KV_CACHE_INTERVAL",
+                             "CHITU_CP_KV_CACHE_TAIL"):
+                    os.environ.pop(name)
+                corec.enable(wrapper.group)
+                ik1, iv1 = ik + 0.3 * torch.randn(ik.shape, generator=gen), iv + 0.3 * torch.randn(iv.shape, generator=gen)
+                errs = []
+                for step, (kk, vv) in enumerate(((ik, iv), (ik1, iv1), (ik1, iv1), (ik1, iv1), (ik1, iv1))):
+                    corec.begin_forward(step, 5, "cond")
+                    got_t, got_i = corec.attention(tq, tk, tv, iq[:, sl], kk[:, sl], vv[:, sl])
+                    if step == 1:  # stale: the other ranks' keys are those of step 0
+                        mix_k, mix_v = ik.clone(), iv.clone()
+                        mix_k[:, sl], mix_v[:, sl] = ik1[:, sl], iv1[:, sl]
+                        want_t, want_i = local_view(tk, tv, mix_k, mix_v)
+                    else:
+                        want_t, want_i = local_view(tk, tv, kk, vv)
+                    errs.append(max((got_t - want_t).abs().max().item(), (got_i - want_i).abs().max().item()))
+                fresh = [corec._kvcache_is_fresh() for corec._cur_step in range(5)]
+                ok = ok and max(errs) < 2e-6 and fresh == [True, False, True, False, True]
+                print(f"rank {rank} {mode} fp8 {e8:.2e} (vs exact {coarse:.2e}) cache {max(errs):.2e}", flush=True)
         elif mode == "dispatch":
             from chitudiffusion_b200.dispatch import CfgDispatcher, ContextParallelDispatcher, SequencePadder
             disp = ContextParallelDispatcher()
