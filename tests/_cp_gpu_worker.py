@@ -115,6 +115,16 @@ def main():
                                   rel_err(i_out[:, :valid], full_pad[:, 24 + rank * ls: 24 + rank * ls + valid]))
     print(f"rank {rank}: fulltxt_peer done", flush=True)
 
+    # ring attention that keeps the state of every source block: all fresh, then the odd source offsets reused
+    from chitudiffusion_b200.cached_ring import CachedRingAttention
+    comm.destroy_diffusion_parallel_groups()
+    comm.initialize_diffusion_parallel_groups(1, world, 1)
+    cached = CachedRingAttention(backend, comm.get_cp_group())
+    results["cached_ring_fresh"] = rel_err(cached(ql, kl, vl), full[:, sl])
+    results["cached_ring_reuse"] = rel_err(cached(ql, kl, vl, plan=[True] + [t % 2 == 0 for t in range(1, world)]),
+                                           full[:, sl])
+    assert cached.stats["reused_blocks"] == world // 2
+    print(f"rank {rank}: cached_ring done", flush=True)
     # peer-store exchange: norm + rotary pre-pass scattered to the owners, attention scattered back
     comm.destroy_diffusion_parallel_groups()
     comm.initialize_diffusion_parallel_groups(1, world, world)

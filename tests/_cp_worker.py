@@ -172,6 +172,37 @@ def main():
                 fresh = [corec._kvcache_is_fresh() for corec._cur_step in range(5)]
                 ok = ok and max(errs) < 2e-6 and fresh == [True, False, True, False, True]
                 print(f"rank {rank} {mode} fp8 {e8:.2e} (vs exact {coarse:.2e}) cache {max(errs):.2e}", flush=True)
+        elif mode == "cached_ring":
+            from chitudiffusion_b200.cached_ring import CachedRingAttention
+            ring = CachedRingAttention(OracleBackend(), group, layer_id=3, merger_factory=OracleMerger)
+            P = cp_size
+            qs, ks, vs = [[torch.randn(1, s * P, H, D, generator=gen) for _ in range(2)] for _ in range(3)]
+            sl = slice(r * s, (r + 1) * s)
+
+            def expect(versions):  # versions[t]: which step's (q, k, v) the state of source offset t was computed with
+                out = lse = None
+                for t in range(P):
+                    ver = versions[t]
+                    src = slice(((r + t) % P) * s, ((r + t) % P + 1) * s)
+                    o, l = oracle.sdpa_fp32(qs[ver][:, sl], ks[ver][:, src], vs[ver][:, src], return_lse=True)
+                    out, lse = oracle.update_out_and_lse(out, lse, o, l)
+                return out
+
+            got0 = ring(qs[0][:, sl], ks[0][:, sl], vs[0][:, sl])  # step 0: everything fresh = exact attention
+            full0 = oracle.sdpa_fp32(qs[0][:, sl], ks[0], vs[0])
+            plan = [True] + [t % 2 == 0 for t in range(1, P)]  # odd offsets reuse their state of step 0
+            got1 = ring(qs[1][:, sl], ks[1][:, sl], vs[1][:, sl], plan=plan)
+            want1 = expect([1 if plan[t] else 0 for t in range(P)])
+            got2 = ring(qs[1][:, sl], ks[1][:, sl], vs[1][:, sl], plan=[True] * P)  # all fresh again
+            full1 = oracle.sdpa_fp32(qs[1][:, sl], ks[1], vs[1])
+            errs = [(got0 - full0).abs().max().item(), (got1 - want1).abs().max().item(), (got2 - full1).abs().max().item()]
+            refused = False
+            try:
+                ring(qs[1][:, sl], ks[1][:, sl], vs[1][:, sl], plan=plan, tag="uncond")  # nothing kept under this tag
+            except RuntimeError:
+                refused = True
+            ok = max(errs) < 2e-6 and refused and ring.stats["reused_blocks"] == sum(1 for x in plan if not x)
+            print(f"rank {rank} cached_ring errs {errs}", flush=True)
         elif mode == "dispatch":
             from chitudiffusion_b200.dispatch import CfgDispatcher, ContextParallelDispatcher, SequencePadder
             disp = ContextParallelDispatcher()
