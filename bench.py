@@ -941,6 +941,7 @@ def run_ours(args):
         e2e_run(max(1, min(args.warmup, 3)))
         e2e_ms = e2e_timed(args.steps)
 
+    ops.check_status(device)  # the headline legs must be clean; side legs below report their own failures
     library = None
     pre_modes = None
     timeline = None
@@ -959,48 +960,62 @@ def run_ours(args):
         os.environ["CHITU_B200_Q_PRELOAD"] = "prepass"
         pre_modes["default"] = "q_in_pre_pass"
 
+    def guarded(label, fn, *a, **kw):
+        """A side leg that fails is reported in its own entry (``error``) and does not take the headline with it."""
+        try:
+            return fn(*a, **kw)
+        except Exception as exc:  # noqa: BLE001 - the message goes into the JSON line
+            print(f"[bench] leg {label} failed on rank {rank}: {exc!r}", file=sys.stderr, flush=True)
+            return {"workload": label, "error": repr(exc)[:400]}
+
     extra = None
     also = []
     if args.workload == DEFAULT_WORKLOAD and not args.profile and not args.no_extra:
         # the compute-bound Wan2.1-14B 720p layer in every context-parallel layout the configuration names
-        extra = measure_extra("wan14b-720p-81f", 4, rank, world, device, args.exchange, sync, dist)
+        extra = guarded("wan14b-720p-81f", measure_extra, "wan14b-720p-81f", 4, rank, world, device, args.exchange,
+                        sync, dist)
         also.append(extra)
         if world > 1:
             for lay in [x.strip() for x in args.extra_layouts.split(",") if x.strip()]:
                 if lay == "usp" and pick_ulysses(world, WORKLOADS["wan14b-720p-81f"]["H"], "usp") < 2:
                     continue
-                also.append(measure_extra("wan14b-720p-81f", 2, rank, world, device, args.exchange, sync, dist, layout=lay))
+                also.append(guarded(f"wan14b-720p-81f:{lay}", measure_extra, "wan14b-720p-81f", 2, rank, world, device,
+                                    args.exchange, sync, dist, layout=lay))
             if world == 8:  # Wan2.1-1.3B 480p: 12 heads do not divide by 8, Ulysses-4 x ring-2
-                also.append(measure_extra("wan1.3b-480p-81f", 4, rank, world, device, args.exchange, sync, dist,
-                                          layout="usp"))
+                also.append(guarded("wan1.3b-480p-81f:usp", measure_extra, "wan1.3b-480p-81f", 4, rank, world, device,
+                                    args.exchange, sync, dist, layout="usp"))
         for leg in also:
             if leg.get("parity"):
                 parity[f"{leg['workload']}:{leg['parallelism']}"] = leg["parity"]
         if world == 8:  # Qwen-Image under CFG parallel 2 x context parallel 4, bf16 and the 8-bit variant
             for name in ("b200", "b200_q8"):
-                leg = measure_qwen_cfg(rank, world, device, sync, dist, name)
+                leg = guarded(f"qwen-image-1328-joint-attn:{name}", measure_qwen_cfg, rank, world, device, sync, dist, name)
                 also.append(leg)
-                if name == "b200":  # the 8-bit variant is held to its own accuracy class, stated in its entry
+                if name == "b200" and "parity" in leg:  # the 8-bit variant is held to its own accuracy class, stated in its entry
                     parity[f"{leg['workload']}:{leg['parallelism']}"] = {
                         k: leg["parity"][k] for k in ("vs_single_gpu_kernel", "vs_fp32_oracle_2_heads", "rows_per_rank")}
 
     nvlink = None
     if world > 1 and args.exchange == "peer" and not args.profile and not args.no_extra:
-        nvlink = measure_nvlink(rank, world, device, sync, dist)
+        nvlink = guarded("nvlink", measure_nvlink, rank, world, device, sync, dist)
 
     dit = None
     if args.dit and not args.profile:
         dit = []
         for n in [x.strip() for x in args.dit.split(",") if x.strip()]:
             if n.startswith("flux"):
-                dit.append(measure_flux_dit(rank, world, device, args.exchange, sync, dist))
+                dit.append(guarded(n, measure_flux_dit, rank, world, device, args.exchange, sync, dist))
             elif n.startswith("qwen"):
                 if args.exchange == "peer":
-                    dit.append(measure_qwen_dit(rank, world, device, sync, dist))
+                    dit.append(guarded(n, measure_qwen_dit, rank, world, device, sync, dist))
             else:
-                dit.append(measure_dit(n, rank, world, device, args.exchange, sync, dist))
+                dit.append(guarded(n, measure_dit, n, rank, world, device, args.exchange, sync, dist))
 
-    ops.check_status(device)
+    try:
+        ops.check_status(device)
+    except Exception as exc:  # noqa: BLE001 - a bounded wait of a side leg ran out: say so, keep the headline
+        print(f"[bench] device status after the side legs on rank {rank}: {exc!r}", file=sys.stderr, flush=True)
+        also.append({"workload": "device-status", "error": repr(exc)[:400]})
     bad = {k: v for k, v in parity.items()
            if max(v["vs_single_gpu_kernel"], v["vs_fp32_oracle_2_heads"]) > PARITY_LIMIT}
 

@@ -113,6 +113,16 @@ def main():
     valid = max(0, min(ls, n_img - rank * ls))
     results["fulltxt_peer"] = max(rel_err(t_out, full_pad[:, :24]),
                                   rel_err(i_out[:, :valid], full_pad[:, 24 + rank * ls: 24 + rank * ls + valid]))
+    # the same with the keys of every query block split over two CTAs (the merging CTA also stores the text rows
+    # to every rank)
+    os.environ["CHITU_B200_KEY_SPLITS"] = "2"
+    wrapper2 = B200ContextParallel(backend, world, cp_backend="ucp")
+    for rep in range(2):
+        t_out, i_out = wrapper2.cp_attn_with_full_txt(*(t.to(dev) for t in txt), *shards, image_seq_len=n_img)
+    os.environ.pop("CHITU_B200_KEY_SPLITS")
+    assert any(getattr(px, "T", 0) == 24 and px.n_splits == 2 for px in wrapper2._peer_cache.values())
+    results["fulltxt_peer_split"] = max(rel_err(t_out, full_pad[:, :24]),
+                                        rel_err(i_out[:, :valid], full_pad[:, 24 + rank * ls: 24 + rank * ls + valid]))
     print(f"rank {rank}: fulltxt_peer done", flush=True)
 
     # ring attention that keeps the state of every source block: all fresh, then the odd source offsets reused
