@@ -486,6 +486,27 @@ def measure_qwen_cfg(rank, world, device, sync, dist, attn_name="b200", blocks=4
                        "rows_per_rank": rows, "limit": PARITY_LIMIT if attn_name == "b200" else 8e-2}}
 
 
+DIT_PARITY_LIMIT = 3e-2  # 16-bit GEMMs over different row counts either side, attention included
+
+
+def block_parity(local_outs, full_outs, dist, device):
+    """Worst relative max-abs error, over the ranks, between this rank's rows of a block run under context
+    parallelism and the same rows of the block run on one GPU over the gathered tokens."""
+    worst = 0.0
+    for got, ref in zip(local_outs, full_outs):
+        worst = max(worst, float(((got.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-12)).item()))
+    t = torch.tensor([worst], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    err = round(float(t.item()), 5)
+    return {"first_block_vs_single_gpu": err, "limit": DIT_PARITY_LIMIT, "ok": err <= DIT_PARITY_LIMIT}
+
+
+def gather_rows(t, dist, world):
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous())
+    return torch.cat(parts, 1)
+
+
 def dit_flops_per_layer(w):
     """Multiply-add FLOPs of one Wan block: self-attention, text cross-attention and the nine GEMMs."""
     S, C, T, F = seq_len(w), w["H"] * w["D"], w["text"], w["ffn"]
@@ -515,9 +536,19 @@ def measure_dit(name, rank, world, device, exchange, sync, dist, layers=None, fo
     stack = WanDiTStack(n_layers, C, w["ffn"], H, device, seed=3, cp_size=world, cp_rank=rank)
     s_local = seq_len(w) // world
     gen = torch.Generator(device=device).manual_seed(5 + rank)
+    shared = torch.Generator(device=device).manual_seed(5)  # modulation and text context: the same on every rank
     x0 = torch.randn(1, s_local, C, generator=gen, device=device)
-    e = 0.1 * torch.randn(1, 6, C, generator=gen, device=device)
-    ctx = torch.randn(1, w["text"], C, generator=gen, device=device).to(torch.bfloat16)
+    e = 0.1 * torch.randn(1, 6, C, generator=shared, device=device)
+    ctx = torch.randn(1, w["text"], C, generator=shared, device=device).to(torch.bfloat16)
+    parity = None
+    if world > 1:  # first block: this rank's rows under context parallelism against one GPU on the gathered tokens
+        from chitudiffusion_b200.pre_attention import WanPreAttention
+
+        local = stack.blocks[0].forward(x0.clone(), e, w["grid"], ctx, attn, stack.pre, backend)
+        full = stack.blocks[0].forward(gather_rows(x0, dist, world), e, w["grid"], ctx, backend,
+                                       WanPreAttention(H, w["D"], cp_size=1, cp_rank=0, device=device), backend)
+        parity = block_parity([local], [full[:, rank * s_local:(rank + 1) * s_local]], dist, device)
+        del full
     x = x0.clone()
     run = lambda: stack(x, e, w["grid"], ctx, attn, backend)  # noqa: E731
     run()
@@ -547,7 +578,7 @@ def measure_dit(name, rank, world, device, exchange, sync, dist, layers=None, fo
             "text_tokens": w["text"], "forward_ms": round(fwd_ms, 2), "step_ms_cond_plus_uncond": round(2 * fwd_ms, 2),
             "forwards_timed": forwards, "tflops": round(flops / (fwd_ms * 1e-3) / 1e12, 1),
             "attention_share_of_flops": round(flops_per_block(w) / dit_flops_per_layer(w), 3),
-            "parallelism": parallelism, "cuda_graph": graphed, "finite": finite,
+            "parallelism": parallelism, "cuda_graph": graphed, "finite": finite, "parity": parity,
             "weights": "random-init N(0, 0.02^2) bf16, fp32 residual stream; GEMMs are library calls"}
 
 
@@ -577,7 +608,14 @@ def measure_flux_dit(rank, world, device, exchange, sync, dist, steps=3):
     gen = torch.Generator(device=device).manual_seed(9 + rank)
     img0 = torch.randn(1, i_loc, C, generator=gen, device=device).to(torch.bfloat16)
     txt0 = torch.randn(1, t_loc, C, generator=gen, device=device).to(torch.bfloat16)
-    temb = torch.randn(1, C, generator=gen, device=device).to(torch.bfloat16)
+    temb = torch.randn(1, C, generator=torch.Generator(device=device).manual_seed(9), device=device).to(torch.bfloat16)
+    parity = None
+    if world > 1:  # first double block: this rank's rows under context parallelism against one GPU on all tokens
+        l_txt, l_img = stack.double[0](img0.clone(), txt0.clone(), temb, table, attn)
+        f_txt, f_img = stack.double[0](gather_rows(img0, dist, world), gather_rows(txt0, dist, world), temb,
+                                       full.contiguous().to(device), backend)
+        parity = block_parity([l_txt, l_img], [f_txt[:, rank * t_loc:(rank + 1) * t_loc],
+                                               f_img[:, rank * i_loc:(rank + 1) * i_loc]], dist, device)
     img, txt = img0.clone(), txt0.clone()
     holder = {}
 
@@ -612,7 +650,7 @@ def measure_flux_dit(rank, world, device, exchange, sync, dist, steps=3):
     return {"workload": "flux1-dev-1024-dit-step", "double_blocks": 19, "single_blocks": 38, "seq_len": S, "hidden": C,
             "step_ms": round(step_ms, 2), "steps_timed": steps, "tflops": round(flops / (step_ms * 1e-3) / 1e12, 1),
             "attention_share_of_flops": round(57 * flops_per_block(w) / flops, 3), "parallelism": parallelism,
-            "cuda_graph": graphed, "finite": bool(torch.isfinite(holder["out"].float()).all().item()),
+            "cuda_graph": graphed, "finite": bool(torch.isfinite(holder["out"].float()).all().item()), "parity": parity,
             "weights": "random-init N(0, 0.02^2) bf16, bf16 residual streams; GEMMs are library calls"}
 
 
@@ -645,6 +683,15 @@ def measure_qwen_dit(rank, world, device, sync, dist, blocks=12, steps=2):
         info = {"image_offset": rank * img.shape[1], "image_seq_len": n_img}
         parallelism = f"ulysses{world} (replicated text, peer stores)"
     stack = QwenDiTStack(blocks, C, H, device, attn, seed=5)
+    parity = None
+    if world > 1:  # first block: this rank's valid rows and the text rows against one GPU on the whole image
+        from chitudiffusion_b200.qwen import B200QwenAttnProcessor
+
+        l_txt, l_img = stack.blocks[0](img.clone(), txt.clone(), temb, rotary, stack.processor, info)
+        f_txt, f_img = stack.blocks[0](img_full.to(device), txt.clone(), temb, rotary, B200QwenAttnProcessor(backend), None)
+        ls = img.shape[1]
+        valid = max(1, min(ls, n_img - rank * ls))
+        parity = block_parity([l_txt, l_img[:, :valid]], [f_txt, f_img[:, rank * ls:rank * ls + valid]], dist, device)
     holder = {}
 
     def run():
@@ -676,6 +723,7 @@ def measure_qwen_dit(rank, world, device, sync, dist, blocks=12, steps=2):
             "tflops": round(flops / (ms_block * 1e-3) / 1e12, 1),
             "attention_share_of_flops": round(4.0 * S * S * D * H / flops, 3), "parallelism": parallelism,
             "cuda_graph": True, "finite": bool(all(torch.isfinite(o.float()).all().item() for o in holder["out"])),
+            "parity": parity,
             "weights": "random-init N(0, 0.02^2) bf16, bf16 residual streams; GEMMs are library calls"}
 
 
