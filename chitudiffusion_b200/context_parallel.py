@@ -47,6 +47,17 @@ class _KernelMerger:
             self.lse = torch.empty((B, S, H, 1), dtype=torch.float32, device=block_out.device)
         ops.lse_combine(self.out, self.lse, block_out, block_lse, first=first)
 
+    def add_final(self, block_out: torch.Tensor, block_lse: torch.Tensor, final_out: torch.Tensor) -> None:
+        """The last block of a call: the merged rows are also written to ``final_out`` in its (16-bit) dtype."""
+        from . import ops
+
+        first = self.out is None
+        if first:
+            self.out = torch.empty(block_out.shape, dtype=torch.float32, device=block_out.device)
+            B, S, H, _ = block_out.shape
+            self.lse = torch.empty((B, S, H, 1), dtype=torch.float32, device=block_out.device)
+        ops.lse_combine(self.out, self.lse, block_out, block_lse, first=first, final_out=final_out)
+
     def result(self) -> torch.Tensor:
         return self.out
 

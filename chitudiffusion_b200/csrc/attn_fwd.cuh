@@ -87,8 +87,8 @@ struct AttnParams {
   // the launch is one-dimensional: its first push_ctas CTAs do no attention, they copy the staged rows
   // into the peers' buffers while the attention CTAs of the same launch already work - in push_order, the
   // order in which the receivers walk their keys: the first push_first peers, then the others (announced
-  // in in_flags).  The attention CTAs follow, (query block, head, batch x split) in that order of
-  // significance, grid_q x grid_h x grid_z of them.  Query rows are normally delivered and announced
+  // in in_flags).  The attention CTAs follow, (query block, batch x split, head) in that order of
+  // significance, grid_q x grid_z x grid_h of them.  Query rows are normally delivered and announced
   // (q_flags) by the staging launch itself; push_src[0] != nullptr makes the copy CTAs send them too,
   // first.  The rank's own rows are already in place and have no flag.  Copy CTAs never wait for anything
   // and are the first CTAs of the grid, so they are on the machine before an attention CTA can wait for
@@ -362,7 +362,9 @@ __device__ __forceinline__ void push_rows(const AttnParams& p, int id, int n) {
 #define CHITU_TRACE(i)
 #endif
 
-// (query block, head, batch x split) of an attention CTA.  Read afresh from the special registers each time
+// (query block, head, batch x split) of an attention CTA.  The grid is (query blocks, batch x splits, heads):
+// CTAs that follow one another in launch order share a head - all the key ranges of a query block included -
+// so the CTAs resident at one time stream few heads' keys and values through L2.  Read afresh from the special registers each time
 // (the asm is volatile), so that the epilogue can ask again instead of keeping four values in registers
 // through the whole key loop.
 __device__ __forceinline__ void attn_cta_coords(const AttnParams& p, int& qblock, int& head, int& bz) {
@@ -371,14 +373,14 @@ __device__ __forceinline__ void attn_cta_coords(const AttnParams& p, int& qblock
   asm volatile("mov.u32 %0, %%ctaid.y;" : "=r"(y));
   asm volatile("mov.u32 %0, %%ctaid.z;" : "=r"(z));
   qblock = static_cast<int>(x);
-  head = static_cast<int>(y);
-  bz = static_cast<int>(z);
+  bz = static_cast<int>(y);
+  head = static_cast<int>(z);
   if (p.push_ctas > 0) {
     const int lin = qblock - p.push_ctas;
     const int rest = lin / p.grid_q;
     qblock = lin - rest * p.grid_q;
-    bz = rest / p.grid_h;
-    head = rest - bz * p.grid_h;
+    head = rest / p.grid_z;
+    bz = rest - head * p.grid_z;
   }
 }
 

@@ -432,7 +432,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
                 : ensure_dynamic_smem(chitu::attn_fwd_kernel<false>, chitu::kAttnSmemBytes, attr_done[0], attr_mu);
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
 
-  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), H, B * n_splits);
+  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), B * n_splits, H);
   if (p.push_ctas > 0) grid = dim3(p.push_ctas + p.grid_q * p.grid_h * p.grid_z, 1, 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p.is_fp16)
