@@ -187,7 +187,8 @@ def attn_fwd(
     """``softmax(scale * q k^T) v`` for ``[B,S,H,128]`` bf16/fp16 tensors of any (16-byte aligned) strides.
 
     Returns ``(out [B,Sq,H,D] contiguous, lse [B,H,Sq] fp32 | None)``.  ``workspace`` is an optional
-    caller-owned uint8 scratch for the key-split partials (see :func:`splitkv_workspace`).  With ``q_pre``
+    caller-owned uint8 scratch for the key-split partials (see :func:`splitkv_workspace`); its first 64 KiB
+    hold counters that must be zero before the first use (``torch.zeros``) and are left zero by every call.  With ``q_pre``
     (keys ``norm_mode, rope_mode, weight, rstd, eps, rope_table, grid, axis_split, pos_offset, round_mid``)
     ``q`` is the raw projection and its pre-attention transform runs inside the kernel
     (``chitu_b200_attn_fwd_qpre``).
