@@ -496,9 +496,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ready |= 1u << src;
         CHITU_TRACE(1);
         // the rows were written by a peer's ordinary stores and are about to be read by the copy engine
-        #if CHITU_FLAG_VARIANT != 3
-          asm volatile("fence.proxy.async.global;" ::: "memory");
-#endif
+        asm volatile("fence.proxy.async.global;" ::: "memory");
       }
     };
     if (lane == 0) {

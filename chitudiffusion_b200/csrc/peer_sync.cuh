@@ -46,9 +46,6 @@ struct PeerSync {
   long long timeout_cycles;
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
   asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -91,28 +88,13 @@ __device__ __forceinline__ void push_phase_done(const PeerSync& ps, int phase, u
   }
 }
 
-// Bounded wait until `*flag` has reached `epoch` (wrap-safe).  Returns false on timeout after
-// recording status 5.
-__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
-  int v;
-  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Polls are relaxed loads with a short back-off (many CTAs may be polling the same word while a
-// peer is still writing rows into this GPU's memory); one acquire fence follows the successful poll.
-#ifndef CHITU_FLAG_VARIANT
-#define CHITU_FLAG_VARIANT 1
-#endif
+// Bounded wait until `*flag` has reached `epoch` (wrap-safe): system-scope acquire polls.  Returns false on
+// timeout after recording status 5.
 __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long long timeout_cycles, int* status) {
-#if CHITU_FLAG_VARIANT == 1
-#define CHITU_FLAG_LD ld_acquire_sys
-#else
-#define CHITU_FLAG_LD ld_relaxed_sys
-#endif
-  if (CHITU_FLAG_LD(flag) - epoch < 0) {
+  if (ld_acquire_sys(flag) - epoch < 0) {
     const long long t0 = clock64();
     unsigned spins = 0;
-    while (CHITU_FLAG_LD(flag) - epoch < 0) {
+    while (ld_acquire_sys(flag) - epoch < 0) {
       if ((++spins & 0x3f) == 0 && clock64() - t0 > timeout_cycles) {
         if (status) atomicCAS(status, 0, 5);
         return false;
