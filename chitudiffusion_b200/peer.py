@@ -4,13 +4,15 @@ Replaces, for the pure-Ulysses layout, the three all-to-all calls before the att
 the one after it (chitu_diffusion/modules/attention/diffusion_attn_backend.py:778-781,825-828)
 together with their pack/unpack copies (chitu_diffusion/core/distributed/comm_group.py:350-384):
 
-* the pre-attention kernel stores q and k (and a plain scatter stores v) straight into every
-  rank's ``[B, U*s, H/U, D]`` buffer - rank r's rows land at ``[r*s, (r+1)*s)`` of each peer;
-* one bounded barrier kernel;
-* the attention kernel's epilogue stores each output row into its owner's ``[B, s, H, D]`` buffer
-  (head columns ``[r*H/U, (r+1)*H/U)``);
-* a second barrier, after which every rank's output is complete and the exchange buffers may be
-  reused.
+* one pre-attention launch stores q, k and v (norm + rotary + cast fused) straight into every rank's
+  ``[B, U*s, H/U, D]`` buffer - rank r's rows land at ``[r*s, (r+1)*s)`` of each peer - and announces them
+  with an arrival flag per source rank; in push mode only q goes out that way, k and v for the peers are
+  staged locally and delivered by copy CTAs inside the attention launch;
+* the attention kernel waits per source rank for the rows it is about to read, its own rows first, and its
+  epilogue stores each output row into its owner's ``[B, s, H, D]`` buffer (head columns
+  ``[r*H/U, (r+1)*H/U)``); its last CTA announces the outputs;
+* a one-warp launch waits for every rank's output flag, after which this rank's output is complete and the
+  exchange buffers may be reused.  No barrier launch.
 
 Buffers come from ``torch.distributed._symmetric_memory`` (device memory mapped into every process
 of the group); the data path is plain peer stores from this library's kernels - no NCCL call, no
@@ -258,9 +260,10 @@ class PeerRing:
     receive from ``(r+U) % P``), ring step ``t`` here PULLS the block of rank ``(r + t*U) % P`` - the
     block that rotation delivers at step ``t`` - into local memory with the copy engines on a side
     stream while the attention kernel works on block ``t-1``; partial results merge with the
-    log-sum-exp combine kernel.  ``mode="agkv"`` pulls every block into one ``[B, P*s, H, D]`` buffer
-    and runs a single attention call (the AGCP branch, :581-597).  No NCCL call is on the data path,
-    so the whole call can be captured in a CUDA graph.
+    log-sum-exp combine kernel.  ``mode="agkv"`` (the AGCP branch, :581-597) pulls every block into one
+    ``[B, P*s, H, D]`` buffer, owners walked upwards from this rank, in three stages whose pulls run under
+    the previous stage's attention call; stage results merge by log-sum-exp and the result is handed back in
+    the backend's dtype.  No NCCL call is on the data path, so the whole call can be captured in a CUDA graph.
     """
 
     def __init__(self, group: CommGroup, ulysses: int, B: int, s: int, H: int, D: int, dtype: torch.dtype,

@@ -323,7 +323,7 @@ int chitu_b200_scatter_rows(const void* src, void* const* dst_ptrs, int n_dest, 
  * chitu_b200_attn_fwd_scatter: as chitu_b200_attn_fwd, but query row r is written to
  *   out_ptrs[r / rows_per_dest] at element offset
  *   batch*dest_batch_stride + (r % rows_per_dest)*dest_row_stride + dest_head_offset + head*128 + d;
- *   n_splits / workspace as in chitu_b200_attn_fwd_splitkv (the merge kernel then does the scattered store).
+ *   n_splits / workspace as in chitu_b200_attn_fwd_splitkv (the CTA that merges the ranges does the scattered store).
  * chitu_b200_peer_barrier: every rank enqueues it the same number of times; flag_ptrs[i] is rank i's
  *   array of `world + 1` int32 (zero-initialised: one flag per peer, then the local epoch counter)
  *   mapped into this process.  The epoch is kept on the device, so the call can be replayed from a
