@@ -35,6 +35,7 @@ EXPORTS = (
     "chitu_b200_qk_norm_rope_batch_stage",
     "chitu_b200_push_ctas",
     "chitu_b200_stamp",
+    "chitu_b200_set_cluster_merge",
     "chitu_b200_attn_fwd_qpre",
     "chitu_b200_peer_wait_outputs",
     "chitu_b200_attn_splitkv_workspace_bytes",
@@ -199,6 +200,10 @@ def load() -> ctypes.CDLL:
     ]
     lib.chitu_b200_qk_norm_rope_batch_stage.restype = ctypes.c_int
     lib.chitu_b200_qk_norm_rope_batch_stage.argtypes = list(lib.chitu_b200_qk_norm_rope_batch_signal.argtypes)
+    lib.chitu_b200_set_cluster_merge.restype = ctypes.c_int
+    lib.chitu_b200_set_cluster_merge.argtypes = [ctypes.c_int]
+    if os.environ.get("CHITU_B200_CLUSTER_MERGE", "1") == "0":
+        lib.chitu_b200_set_cluster_merge(0)
     lib.chitu_b200_stamp.restype = ctypes.c_int
     lib.chitu_b200_stamp.argtypes = [_vp, _vp]
     lib.chitu_b200_push_ctas.restype = ctypes.c_int

@@ -67,6 +67,10 @@ struct AttnParams {
   //            + block) * 2 + t; chunk-major so that a warp's 32 rows are 512 contiguous bytes)
   //   part_lse [n_splits][tile][128 rows] fp32 (natural log)
   int n_splits, tiles_per_split;
+  // cluster_merge (two key ranges only): the two CTAs of a query block are launched as a thread-block cluster;
+  // the CTA of the second range writes its rows into the first one's shared memory (the K/V ring, idle by
+  // then) and the first merges them with its own - no scratch memory, no counter.
+  int cluster_merge;
   int* split_count;
   float* part_o;
   float* part_lse;
@@ -362,6 +366,22 @@ __device__ __forceinline__ void push_rows(const AttnParams& p, int id, int n) {
 #define CHITU_TRACE(i)
 #endif
 
+// Thread-block cluster helpers (cluster_merge).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f1(uint32_t addr, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+}
+
 // (query block, head, batch x split) of an attention CTA.  The grid is (query blocks, batch x splits, heads):
 // CTAs that follow one another in launch order share a head - all the key ranges of a query block included -
 // so the CTAs resident at one time stream few heads' keys and values through L2.  Read afresh from the special registers each time
@@ -376,11 +396,18 @@ __device__ __forceinline__ void attn_cta_coords(const AttnParams& p, int& qblock
   bz = static_cast<int>(y);
   head = static_cast<int>(z);
   if (p.push_ctas > 0) {
-    const int lin = qblock - p.push_ctas;
+    int lin = qblock - p.push_ctas;
+    int low = 0;
+    if (p.cluster_merge) {  // the two key ranges of a query block are neighbours: they form the cluster
+      low = lin & 1;
+      lin >>= 1;
+    }
     const int rest = lin / p.grid_q;
     qblock = lin - rest * p.grid_q;
-    head = rest / p.grid_z;
-    bz = rest - head * p.grid_z;
+    const int gz = p.cluster_merge ? p.grid_z >> 1 : p.grid_z;
+    head = rest / gz;
+    bz = rest - head * gz;
+    if (p.cluster_merge) bz = bz * 2 + low;
   }
 }
 
@@ -640,10 +667,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
   }
+  if (p.cluster_merge) {  // the two cluster barriers of the epilogue (every thread of both CTAs takes part)
+    cluster_sync_all();
+    cluster_sync_all();
+  }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int t = warp >> 2;
+    if (t >= n_qt && p.cluster_merge) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
     if (t < n_qt) {
       const int quad = warp & 3;
       const int row_in_tile = quad * 32 + lane;
@@ -842,6 +877,61 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * inv_l;
           park(c, f);
+        }
+      } else if (p.cluster_merge) {
+        // Two key ranges, two CTAs of one cluster.  After the first barrier both K/V rings are idle; the CTA of
+        // the second range writes its normalised rows (chunk-major: a warp's 32 rows are 512 contiguous bytes)
+        // and log-sum-exps into the first CTA's ring; after the second barrier the first CTA merges them with
+        // the rows it still holds in tensor memory.
+        constexpr uint32_t kPartTile = 32 * kTileM * 16;  // one query tile of fp32 rows: 64 KiB
+        const uint32_t slot = kv_smem + t * kPartTile + row_in_tile * 16;
+        const uint32_t lse_slot = kv_smem + 2 * kPartTile + (t * kTileM + row_in_tile) * 4;
+        cluster_sync_all();
+        if (split == 1) {
+          const uint32_t remote = mapa_shared(slot, 0);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_o + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              st_cluster_f4(remote + (c * 8 + (i >> 2)) * (kTileM * 16), __uint_as_float(o[i]) * inv_l,
+                            __uint_as_float(o[i + 1]) * inv_l, __uint_as_float(o[i + 2]) * inv_l,
+                            __uint_as_float(o[i + 3]) * inv_l);
+          }
+          st_cluster_f1(mapa_shared(lse_slot, 0), lse_row);
+          write_out = false;
+        }
+        cluster_sync_all();
+        if (split == 0) {
+          float other_lse;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other_lse) : "r"(lse_slot));
+          const float mx = fmaxf(lse_row, other_lse);
+          float w_self = expf(lse_row - mx), w_other = expf(other_lse - mx);
+          const float wsum = w_self + w_other;
+          lse_row = mx + logf(wsum);
+          w_self *= inv_l / wsum;
+          w_other /= wsum;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_o + c * 32, o);
+            tmem_wait_ld();
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                           : "r"(slot + (c * 8 + j) * (kTileM * 16)));
+              f[4 * j] = fmaf(w_other, v.x, __uint_as_float(o[4 * j]) * w_self);
+              f[4 * j + 1] = fmaf(w_other, v.y, __uint_as_float(o[4 * j + 1]) * w_self);
+              f[4 * j + 2] = fmaf(w_other, v.z, __uint_as_float(o[4 * j + 2]) * w_self);
+              f[4 * j + 3] = fmaf(w_other, v.w, __uint_as_float(o[4 * j + 3]) * w_self);
+            }
+            park(c, f);
+          }
         }
       } else {
         // (1) this key range's normalised rows and log-sum-exp go to scratch

@@ -122,6 +122,9 @@ SplitPlan plan_key_splits(int Sk, int requested) {
 // Clock budget of the flag waits (peer barrier, arrival flags); about a second by default.
 long long g_flag_wait_cycles = 1ll << 31;
 
+// Two key ranges merge through a thread-block cluster's shared memory instead of scratch memory.
+int g_cluster_merge = 1;
+
 }  // namespace
 
 #ifdef CHITU_ATTN_TIMING
@@ -359,6 +362,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     p.local_src = p.sync.rank;
     p.signal_out = 1;
   }
+  p.cluster_merge = (n_splits == 2 && g_cluster_merge) ? 1 : 0;
   p.push_ctas = p.grid_q = p.grid_h = p.grid_z = p.push_rounds = p.push_first = p.rot_other = 0;
   p.push_vecs = 0;
   p.q_flags = nullptr;
@@ -432,13 +436,52 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
                 : ensure_dynamic_smem(chitu::attn_fwd_kernel<false>, chitu::kAttnSmemBytes, attr_done[0], attr_mu);
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "attn_fwd: cudaFuncSetAttribute");
 
-  dim3 grid((Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM), B * n_splits, H);
-  if (p.push_ctas > 0) grid = dim3(p.push_ctas + p.grid_q * p.grid_h * p.grid_z, 1, 1);
+  const unsigned qblocks_x = (Sq + chitu::kQTiles * chitu::kTileM - 1) / (chitu::kQTiles * chitu::kTileM);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p.is_fp16)
-    chitu::attn_fwd_kernel<true><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
-  else
-    chitu::attn_fwd_kernel<false><<<grid, chitu::kAttnThreads, chitu::kAttnSmemBytes, st>>>(tq, tk, tv, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(chitu::kAttnThreads);
+  cfg.dynamicSmemBytes = chitu::kAttnSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute cluster_attr[1];
+  auto set_grid = [&]() {
+    cfg.gridDim = dim3(qblocks_x, B * n_splits, H);
+    if (p.push_ctas > 0) cfg.gridDim = dim3(p.push_ctas + p.grid_q * p.grid_h * p.grid_z, 1, 1);
+    cfg.numAttrs = 0;
+    cfg.attrs = nullptr;
+    if (p.cluster_merge) {  // the two key ranges of a query block: neighbours along y, or along x in the 1-d grid
+      cluster_attr[0].id = cudaLaunchAttributeClusterDimension;
+      cluster_attr[0].val.clusterDim.x = p.push_ctas > 0 ? 2 : 1;
+      cluster_attr[0].val.clusterDim.y = p.push_ctas > 0 ? 1 : 2;
+      cluster_attr[0].val.clusterDim.z = 1;
+      cfg.attrs = cluster_attr;
+      cfg.numAttrs = 1;
+    }
+  };
+  if (p.cluster_merge && p.push_ctas > 0) {
+    // Copy CTAs pair up like everything else in a clustered grid, and the grid should stay resident at once
+    // where it was going to be: ask how many clusters fit and give the copy CTAs what the attention leaves.
+    p.push_ctas &= ~1;
+    set_grid();
+    int max_clusters = 0;
+    const cudaError_t oe = p.is_fp16
+        ? cudaOccupancyMaxActiveClusters(&max_clusters, chitu::attn_fwd_kernel<true>, &cfg)
+        : cudaOccupancyMaxActiveClusters(&max_clusters, chitu::attn_fwd_kernel<false>, &cfg);
+    const long long attn_ctas = static_cast<long long>(p.grid_q) * p.grid_h * p.grid_z;
+    if (oe != cudaSuccess || max_clusters <= 0) {
+      (void)cudaGetLastError();
+      p.cluster_merge = 0;
+    } else if (attn_ctas + p.push_ctas > 2LL * max_clusters && attn_ctas < 2LL * max_clusters) {
+      const long long room = 2LL * max_clusters - attn_ctas;
+      if (room >= 8) p.push_ctas = static_cast<int>(room < 48 ? room : 48) & ~1;
+      else p.cluster_merge = 0;
+    }
+  }
+  set_grid();
+  {
+    const cudaError_t le = p.is_fp16 ? cudaLaunchKernelEx(&cfg, chitu::attn_fwd_kernel<true>, tq, tk, tv, p)
+                                     : cudaLaunchKernelEx(&cfg, chitu::attn_fwd_kernel<false>, tq, tk, tv, p);
+    if (le != cudaSuccess) return cuda_fail(le, "attn_fwd: launch");
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attn_fwd: launch");
   return CHITU_OK;
@@ -871,6 +914,12 @@ int chitu_b200_stamp(unsigned long long* slot, void* stream) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "stamp: launch");
   return CHITU_OK;
+}
+
+int chitu_b200_set_cluster_merge(int enable) {
+  const int old = g_cluster_merge;
+  if (enable >= 0) g_cluster_merge = enable ? 1 : 0;
+  return old;
 }
 
 long long chitu_b200_set_flag_wait_cycles(long long cycles) {

@@ -753,6 +753,12 @@ def attn_fwd_exchange(
     _launched(1)
 
 
+def set_cluster_merge(enable: bool) -> bool:
+    """Merge two key ranges through a thread-block cluster's shared memory (default) or through the workspace;
+    returns the previous setting.  ``CHITU_B200_CLUSTER_MERGE=0`` at import time selects the workspace form."""
+    return bool(_lib.load().chitu_b200_set_cluster_merge(1 if enable else 0))
+
+
 def stamp(slots: torch.Tensor, index: int) -> None:
     """Enqueue a launch that writes the GPU's nanosecond timer into ``slots[index]`` (int64 tensor on the GPU);
     works inside a captured graph.  Not counted as a launch of the hot path."""

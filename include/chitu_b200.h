@@ -445,6 +445,14 @@ int chitu_b200_attn_fwd_exchange_push(const void* q, const void* k, const void* 
 long long chitu_b200_set_flag_wait_cycles(long long cycles);
 
 /*
+ * How two key ranges (n_splits = 2) are merged, process-wide, for launches made after the call: 1 (default) -
+ * the two CTAs of a query block form a thread-block cluster and the second hands its rows to the first
+ * through distributed shared memory; 0 - through the workspace, like every other split count.  Returns the
+ * previous setting; a negative argument only queries.  No reference counterpart.
+ */
+int chitu_b200_set_cluster_merge(int enable);
+
+/*
  * Measurement aid, no reference counterpart: a one-thread kernel that writes the GPU's nanosecond timer
  * (%globaltimer) into *slot.  Enqueued between the launches of a layer - also inside a captured graph,
  * where events cannot be read back - it gives the per-launch timeline that bench.py reports.

@@ -177,9 +177,12 @@ def test_linearity_in_v_at_full_size(backend):
     assert torch.isfinite(lse).all() and lse.min().item() > math.log(S) - 40
 
 
-@pytest.mark.parametrize("Sq,Sk,H,n_splits", [(200, 1000, 2, 3), (130, 4608, 3, 8), (64, 333, 1, 16), (256, 256, 1, 2)])
+@pytest.mark.parametrize("Sq,Sk,H,n_splits", [(200, 1000, 2, 3), (130, 4608, 3, 8), (64, 333, 1, 16), (256, 256, 1, 2),
+                                               (700, 1900, 3, 2)])
 def test_key_split_matches_oracle(backend, Sq, Sk, H, n_splits):
-    """Keys split over several CTAs + merge kernel (the path small grids take) against the oracle."""
+    """Keys split over several CTAs, merged inside the launch (the path small grids take) against the oracle:
+    through scratch memory by the CTA that finishes last, and - two ranges - through the shared memory of a
+    thread-block cluster as well."""
     from chitudiffusion_b200 import ops
 
     gen = torch.Generator().manual_seed(Sq + Sk)
@@ -191,6 +194,14 @@ def test_key_split_matches_oracle(backend, Sq, Sk, H, n_splits):
     _check(out, ref, lse, ref_lse)
     one, _ = ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), n_splits=1)
     assert (out.float() - one.float()).abs().max().item() <= 1e-2 * ref.abs().max().item()
+    if n_splits == 2:  # the launch above merged through the cluster; now the scratch form of the same split
+        assert ops.set_cluster_merge(False) is True
+        try:
+            out2, lse2 = ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), return_lse=True, n_splits=2)
+        finally:
+            ops.set_cluster_merge(True)
+        _check(out2, ref, lse2, ref_lse)
+        assert (out2.float() - out.float()).abs().max().item() <= 1e-2 * ref.abs().max().item()
     auto, _ = ops.attn_fwd(q.cuda(), k.cuda(), v.cuda())  # the heuristic picks a split for this small grid
     _check(auto, ref)
     assert ops.auto_key_splits(2, Sq, Sk, H) >= 1 and ops.auto_key_splits(1, 4608, 4608, 24) == 1
