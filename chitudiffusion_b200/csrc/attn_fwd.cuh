@@ -71,6 +71,7 @@ struct AttnParams {
   // the CTA of the second range writes its rows into the first one's shared memory (the K/V ring, idle by
   // then) and the first merges them with its own - no scratch memory, no counter.
   int cluster_merge;
+  int split_strided;  // split s takes key tiles s, s + n_splits, ... instead of a contiguous range
   int* split_count;
   float* part_o;
   float* part_lse;
@@ -453,17 +454,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int batch = bz / p.n_splits;
   const int split = bz - batch * p.n_splits;
   const int n_kv_total = (p.Sk + kTileN - 1) / kTileN;
-  const int kv0 = split * p.tiles_per_split;                      // first key tile of this CTA
-  const int n_kv = min(p.tiles_per_split, n_kv_total - kv0);      // >= 1 (the host sizes the splits)
+  // This CTA's key tiles: kv0 + kv_step * u for u in [0, n_kv).  A contiguous range (kv_step 1), or - with
+  // the fused exchange - every n_splits-th tile (split_strided): then each CTA of a query block holds some of
+  // this rank's own rows and can start at once, instead of one of them idling until a peer's rows land.
+  const int kv_step = p.split_strided ? p.n_splits : 1;
+  const int kv0 = p.split_strided ? split : split * p.tiles_per_split;
+  const int n_kv = p.split_strided ? (n_kv_total - split + p.n_splits - 1) / p.n_splits
+                                   : min(p.tiles_per_split, n_kv_total - kv0);  // >= 1 (the host sizes the splits)
   const int n_qt = (q0 + kTileM < p.Sq) ? 2 : 1;
-  // step j of this CTA works on key tile kv0 + (j + rot) % n_kv: with the fused exchange the walk
-  // starts at the first tile made only of this rank's own rows
+  // step j of this CTA works on its tile u = (j + rot) % n_kv: with the fused exchange the walk starts at the
+  // first of its tiles made only of this rank's own rows
   int rot = 0;
   if (p.in_flags != nullptr) {
-    const int first_local = (p.prefix_rows + p.local_src * p.rows_per_src + kTileN - 1) / kTileN;
-    if (first_local >= kv0 && first_local < kv0 + n_kv &&
-        (first_local + 1) * kTileN <= p.prefix_rows + (p.local_src + 1) * p.rows_per_src)
-      rot = first_local - kv0;
+    const int own_lo = p.prefix_rows + p.local_src * p.rows_per_src;
+    const int first_local = (own_lo + kTileN - 1) / kTileN;
+    const int u0 = first_local <= kv0 ? 0 : (first_local - kv0 + kv_step - 1) / kv_step;
+    const int tile0 = kv0 + kv_step * u0;
+    if (u0 < n_kv && tile0 * kTileN >= own_lo && (tile0 + 1) * kTileN <= own_lo + p.rows_per_src)
+      rot = u0;
     else if (p.rot_other < n_kv)
       rot = p.rot_other;
   }
@@ -543,8 +551,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (round > 0) mbar_wait(bar_kv_empty + 8 * slot, (round - 1) & 1, abort_flag, p.status, kDevTimeoutLoad);
       if (lane == 0) {
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
-        const int rel = (i >> 1) + rot;  // tile of this item relative to kv0, wrapped without a division
-        const int row = (kv0 + (rel >= n_kv ? rel - n_kv : rel)) * kTileN;
+        const int rel = (i >> 1) + rot;  // this item's tile among the CTA's own, wrapped without a division
+        const int row = (kv0 + kv_step * (rel >= n_kv ? rel - n_kv : rel)) * kTileN;
         wait_rows(p.in_flags, src_ready, row, row + kTileN, p.Sk);
         const uint32_t dst = kv_smem + slot * kTileBytes;
         const uint32_t bar = bar_kv_full + 8 * slot;
@@ -721,8 +729,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #else
 #define TICK(acc)
 #endif
-      int jt = rot;                                // key tile of step j relative to kv0 (advanced without a division)
-      const int last_rel = n_kv_total - 1 - kv0;   // the tile whose tail may need masking
+      int jt = rot;  // the CTA's tile of step j (advanced without a division)
+      // the tile whose tail may need masking, if it is one of this CTA's
+      const int last_rel = (n_kv_total - 1 - kv0) % kv_step == 0 ? (n_kv_total - 1 - kv0) / kv_step : -1;
       for (int j = 0; j < n_kv; ++j) {
 #ifdef CHITU_ATTN_TIMING
         c0 = clock64();

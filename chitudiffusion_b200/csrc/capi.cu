@@ -363,6 +363,8 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     p.signal_out = 1;
   }
   p.cluster_merge = (n_splits == 2 && g_cluster_merge) ? 1 : 0;
+  // with the fused exchange the key ranges interleave, so that every CTA of a query block holds own rows
+  p.split_strided = (ex.sync != nullptr && n_splits > 1) ? 1 : 0;
   p.push_ctas = p.grid_q = p.grid_h = p.grid_z = p.push_rounds = p.push_first = p.rot_other = 0;
   p.push_vecs = 0;
   p.q_flags = nullptr;
@@ -402,7 +404,7 @@ int attn_fwd_impl(const void* q, const void* k, const void* v, void* out, const 
     // Serve the peers in the order in which they will ask for this rank's rows: receiver d walks the source
     // ranks of a key range upwards, starting at itself where the range holds it, at the range's first
     // source otherwise.
-    const int ranges = (world % n_splits == 0) ? n_splits : 1;
+    const int ranges = (!p.split_strided && world % n_splits == 0) ? n_splits : 1;
     const int len = world / ranges;
     int pos[8], n = 0;
     for (int d = 0; d < world; ++d) {
