@@ -848,6 +848,8 @@ def run_ours(args):
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
     w = WORKLOADS[args.workload]
+    if args.heads:
+        w = dict(w, H=args.heads)
     if seq_len(w) % world or (w["kind"] == "joint" and (w["s_txt"] % world or w["s_img"] % world)):
         raise ValueError("sequence not divisible by the number of GPUs")
     pipe = Pipeline(w, rank, world, device, exchange=args.exchange, layout=args.layout, attn=args.attn)
@@ -1092,7 +1094,7 @@ def run_ours(args):
         roof = {
             "bound": "tensor", "kernel": "attn_fwd_kernel" if args.attn == "b200" else "q8 pre-pass + attn_q8_kernel",
             "achieved": round(achieved, 2), "peak": peak,
-            "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+            "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None if args.heads else NCU_TRAFFIC_BYTES.get(args.workload),
             "peak_source": f"{peak_kind} bf16_tflops (cuBLAS burst); sm clock sampled during this run: "
                            f"{clocks.get('sm_mhz') if clocks else None} MHz",
             "frac_of_sustained": round(achieved / sustained, 4), "peak_sustained": sustained,
@@ -1225,6 +1227,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--heads", type=int, default=0,
+                    help="override the workload's head count (e.g. 6 on 2 GPUs: the per-GPU attention grid of the "
+                         "24-head workload on 8 GPUs); the line's config says so")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: Ulysses exchange by peer stores fused into the kernels, or by NCCL all-to-all")
     ap.add_argument("--attn", default="b200", choices=["b200", "b200_q8"],
