@@ -261,6 +261,37 @@ def main():
                 err = (got[key].float() - ref.float()).abs().max().item() if ref.numel() else 0.0
                 ok = ok and same_meta and err <= tol * max(1.0, ref.float().abs().max().item() if ref.numel() else 1.0)
                 print(f"rank {rank} {mode} {key} dtype {got[key].dtype} err {err:.2e} ok={ok}", flush=True)
+        elif mode.startswith("imgolden:"):
+            # replay of a fixture that the reference's own ImageContextParallelAttention produced on gloo ranks
+            # (tests/golden/make_golden_imagecp.py), its environment switches included
+            from chitudiffusion_b200.image_cp import B200ImageContextParallel
+            sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+            from make_golden_imagecp import CASES as IMG_CASES, S_LOCAL
+
+            name = mode.split(":", 1)[1]
+            case = torch.load(os.path.join(ROOT, "tests", "golden", "imagecp_golden.pt"))[name]
+            assert case["ranks"] == world
+            env = IMG_CASES[name][3]
+            os.environ.update(env)
+            core = B200ImageContextParallel(wrapper, mode=case["mode"], ulysses_size=case["ulysses_size"],
+                                            merger_factory=wrapper._merger_factory)
+            for key in env:
+                os.environ.pop(key)
+            core.enable(wrapper.group)
+            inp = case["inputs"]
+            sl = slice(r * S_LOCAL, (r + 1) * S_LOCAL)
+            worst = 0.0
+            for step in range(case["steps"]):
+                if case["steps"] > 1:
+                    core.begin_forward(step, case["steps"], "cond")
+                t_out, i_out = core.attention(inp["txt_q"], inp["txt_k"], inp["txt_v"], inp["img_q"][:, sl].contiguous(),
+                                              inp["img_k"][step][:, sl].contiguous(), inp["img_v"][step][:, sl].contiguous())
+                want = case["per_rank"][r][step]
+                for got, ref in ((t_out, want["txt_out"]), (i_out, want["img_out"])):
+                    ok = ok and got.dtype == ref.dtype and tuple(got.shape) == tuple(ref.shape)
+                    worst = max(worst, (got.float() - ref.float()).abs().max().item())
+            ok = ok and worst < 2e-6
+            print(f"rank {rank} {mode} worst {worst:.2e} ok={ok}", flush=True)
         elif mode == "qwen":
             # the Qwen-Image processor mirror over the replicated-text layout: image tokens sharded with a zero-padded
             # tail, rotary rows taken at this rank's image offset (zero past the end), text replicated

@@ -25,12 +25,14 @@ def _run(nproc, cfg_size, up, cp_backend, mode):
     # Ulysses-2; producer-callback API (serial schedule on CPU); image-CP core in ring and all-gather-KV mode
     # every launch also replays the fixtures the reference's own CP wrapper produced for that layout ("golden:")
     (2, 1, 2, "ucp", "plain,fused,imagecp_ring,imagecp_agkv,golden:ulysses2,golden:ulysses2_bf16,golden:fulltxt_ulysses2"),
+    # fixtures produced by the reference's own image-CP core ("imgolden:"), its FP8 transfer and K/V cache included
+    (2, 1, 2, "ucp", "imgolden:agkv2,imgolden:ulysses2,imgolden:ring2,imgolden:agkv2_fp8,imgolden:agkv2_cache"),
     (2, 1, 1, "ucp", "plain,golden:ring2,golden:ring2_bf16,cached_ring"),  # ring-2; cached ring states
     # all-gather-KV, also with the replicated-text layout
     (2, 1, 2, "agcp", "plain,fulltxt,qwen,golden:agcp2,golden:agcp2_bf16,golden:fulltxt_agcp2"),
     # Ulysses-2 x ring-2; batch > 1 (unpack-copy path); Qwen layout with a padded tail; image-CP core, unified mode
     (4, 1, 2, "ucp", "plain,batch2,fulltxt,qwen,imagecp_unified,golden:usp_u2r2,golden:usp_u2r2_batch2,"
-                     "golden:usp_u2r2_bf16,golden:fulltxt_usp_u2r2"),
+                     "golden:usp_u2r2_bf16,golden:fulltxt_usp_u2r2,imgolden:unified4_u2"),
     (4, 1, 4, "ucp", "golden:ulysses4"),
     # ring-4; ring attention that reuses the states of skipped source blocks
     (4, 1, 1, "ucp", "golden:ring4,golden:fulltxt_ring4,cached_ring"),
