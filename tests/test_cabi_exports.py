@@ -50,6 +50,35 @@ def test_version_caps_and_argument_errors_need_no_gpu(lib):
     assert rc == -2 and b"head_dim" in lib.chitu_b200_last_error()
 
 
+def test_exchange_entries_validate_their_descriptors_without_a_gpu(lib):
+    from chitudiffusion_b200 import _lib
+
+    st = (ctypes.c_int64 * 4)(128, 128, 128, 1)
+    buf = ctypes.create_string_buffer(256)
+    p = ctypes.addressof(buf)
+    dests = _lib.ptr_array([p, p])
+    # push mode without its descriptors
+    rc = lib.chitu_b200_attn_fwd_exchange_push(p, p, p, dests, 2, 128, 128, 128, 0, 1, 256, 256, 1, 128, st, st, st,
+                                               1.0, 0, 1, None, 0, 128, None, None, None, None)
+    assert rc == -1 and b"descriptor" in lib.chitu_b200_last_error()
+    # the flag exchange without a sync block
+    rc = lib.chitu_b200_attn_fwd_exchange(p, p, p, dests, 2, 128, 128, 128, 0, 1, 256, 256, 1, 128, st, st, st, 1.0,
+                                          0, 1, None, 0, 128, 0, None, 0, 0, 0, None, None, None)
+    assert rc == -1 and b"sync" in lib.chitu_b200_last_error()
+    # a sync descriptor whose rank is outside the group
+    blocks = (ctypes.c_void_p * 2)(p, p)
+    bad = _lib.PeerSyncDesc(ctypes.cast(blocks, ctypes.POINTER(ctypes.c_void_p)), 5, 2)
+    assert lib.chitu_b200_peer_wait_outputs(ctypes.byref(bad), None, None) == -1
+    # the timer stamp wants an 8-byte aligned slot; the merge setting can be read back
+    assert lib.chitu_b200_stamp(None, None) == -1
+    assert lib.chitu_b200_stamp(p + 4, None) == -1
+    old = lib.chitu_b200_set_cluster_merge(-1)
+    assert old in (0, 1) and lib.chitu_b200_set_cluster_merge(old) == old
+    # split workspace: header of counters plus whole 128-row tiles of fp32 rows and log-sum-exps
+    assert lib.chitu_b200_attn_splitkv_workspace_bytes(1, 300, 3, 128, 1) == 0
+    assert lib.chitu_b200_attn_splitkv_workspace_bytes(1, 300, 3, 128, 2) == 65536 + 2 * (3 * 2 * 256) * 129 * 4
+
+
 def test_backend_construction_and_cpu_tensors_fail_loudly():
     import torch
 
