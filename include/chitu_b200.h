@@ -395,8 +395,8 @@ int chitu_b200_attn_fwd_exchange(const void* q, const void* k, const void* v, vo
 int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, void* stream);
 
 /*
- * Push mode: the same exchange with the transfer overlapped with the attention itself, for grids that
- * leave SMs idle (a few hundred query rows per rank: Flux on 4 or 8 GPUs).  (Same reference lines; what it
+ * Push mode: the same exchange with the key / value transfer overlapped with the attention itself, for small
+ * grids, where the exchange is a large share of a layer (Flux on 2 to 8 GPUs).  (Same reference lines; what it
  * replaces in addition is the overlap the reference gets from its side-stream all-to-all in
  * attention_fused, diffusion_attn_backend.py:638-737.)
  *
@@ -407,9 +407,10 @@ int chitu_b200_peer_wait_outputs(const chitu_b200_peer_sync* sync, int* status, 
  * chitu_b200_attn_fwd_exchange_push: chitu_b200_attn_fwd_exchange whose grid is extended by copy CTAs
  *   that move the staged blocks into the peers' buffers while the attention CTAs already run: key and
  *   value rows in the order in which the receivers walk their keys, in two stages announced by flags
- *   (stage[0] non-null: the query rows as well, first, for a staging launch that kept them local).  The attention CTAs wait per source rank for the
- *   query rows of their block and for each key / value block as they reach it; this rank's own rows are
- *   already in place.  The copy CTAs are the first CTAs of the (one-dimensional) grid and never wait, so
+ *   (stage[0] non-null: the query rows as well, first, for a staging launch that kept them local).  The
+ *   attention CTAs wait per source rank for the query rows of their block and for each key / value block
+ *   as they reach it; this rank's own rows are already in place.  With a key split under this exchange,
+ *   range s takes key tiles s, s + n_splits, ...: every CTA of a query block holds own rows to start on.  The copy CTAs are the first CTAs of the (one-dimensional) grid and never wait, so
  *   they are on the machine before any attention CTA can wait for a peer's; chitu_b200_push_ctas says
  *   how many a shape gets on the current device (40, or what fits beside the attention CTAs where those
  *   leave 8 or more SMs idle).  dest[t][d] is where this rank's block starts in rank d's gathered
